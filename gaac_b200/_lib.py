@@ -1,0 +1,90 @@
+"""ctypes binding of libgaac_b200.so (the C ABI declared in include/gaac_b200.h).
+
+There is no fallback: if the library is missing or a call fails, a RuntimeError is raised.
+"""
+from __future__ import annotations
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libgaac_b200.so")
+_lib = None
+
+vp, i32, i64, f32, sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
+
+
+class Side(C.Structure):
+    """gaac_side"""
+    _fields_ = [("sm", vp), ("codes", vp), ("flags", vp), ("tile_off", vp), ("ovf", vp), ("head_start", vp),
+                ("ovf_bytes", i64), ("base3", vp), ("base4", vp), ("tail", vp)]
+
+
+class Store(C.Structure):
+    """gaac_store"""
+    _fields_ = [("sm", vp), ("codes", vp), ("flags", vp), ("tile_off", vp), ("ovf", vp), ("ovf_used", vp), ("tail", vp),
+                ("base3", vp), ("base4", vp)]
+
+
+class Paged(C.Structure):
+    """gaac_paged"""
+    _fields_ = [("buf", vp), ("raw", vp), ("mt", vp), ("stack", vp), ("top", vp), ("err", vp),
+                ("b3k", vp), ("b4k", vp), ("b3v", vp), ("b4v", vp), ("n_kv", i32), ("TS", i32), ("ovf_slot", i32)]
+
+
+_SIGNATURES = {
+    "gaac_status_string": (C.c_char_p, [i32]),
+    "gaac_abi_version": (i32, []),
+    "gaac_encode_tiles": (i32, [vp, i64, i64, i64, i64, vp, vp, vp, i32, i32, vp, vp, vp, vp, vp, vp]),
+    "gaac_compact": (i32, [vp, vp, i64, i64, vp, vp, vp, i64, vp, vp]),
+    "gaac_decode_page": (i32, [vp, vp, vp, vp, i64, vp, vp, vp, vp, vp, i32, i32, i64, i64, i64, vp, vp]),
+    "gaac_exponent_hist": (i32, [vp, i64, i64, vp, vp]),
+    "gaac_bases_from_hist": (i32, [vp, i64, vp, vp, vp]),
+    "gaac_attn_workspace_bytes": (sz, [i32, i32, i32]),
+    "gaac_decode_attn": (i32, [C.POINTER(Side), C.POINTER(Side), vp, vp, i32, i32, i32, vp, i64, f32, i32, vp, i32, i32, vp, sz, vp, vp, vp]),
+    "gaac_decode_attn_partial": (i32, [C.POINTER(Side), C.POINTER(Side), vp, vp, i32, i32, i32, vp, i64, f32, i32, vp, i32, i32, vp, sz, vp, vp]),
+    "gaac_combine": (i32, [vp, vp, vp, i64, i32, vp, vp, vp]),
+    "gaac_append_kv": (i32, [C.POINTER(Store), C.POINTER(Store), vp, vp, vp, i32, i32, vp, vp, i64, i64, i32, vp]),
+    "gaac_paged_store": (i32, [C.POINTER(Paged), vp, vp, i64, i64, vp, i32, vp, vp]),
+    "gaac_paged_release": (i32, [C.POINTER(Paged), vp, i32, vp]),
+    "gaac_paged_decode_blocks": (i32, [C.POINTER(Paged), vp, i32, vp, vp, i64, vp]),
+    "gaac_paged_decode_attn": (i32, [C.POINTER(Paged), vp, i64, vp, vp, i32, i32, f32, i32, vp, sz, vp, vp, vp]),
+}
+# entry points added after ABI version 1 are bound when present
+_OPTIONAL = {
+    "gaac_decode_attn_static": (i32, [C.POINTER(Side), C.POINTER(Side), vp, vp, i32, i32, i32, vp, i64, f32, i32, vp, i32, i32, vp, vp, vp]),
+    "gaac_static_workspace_bytes": (sz, []),
+}
+EXPORTS = tuple(_SIGNATURES)
+
+
+def lib():
+    """The loaded library.  Raises RuntimeError when it has not been built (python -m gaac_b200.build)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m gaac_b200.build` (needs nvcc); there is no fallback path")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        for name, (res, args) in _OPTIONAL.items():
+            if hasattr(L, name):
+                fn = getattr(L, name)
+                fn.restype, fn.argtypes = res, args
+        _lib = L
+    return _lib
+
+
+def check(status: int, what: str):
+    if status != 0:
+        raise RuntimeError(f"{what}: {lib().gaac_status_string(status).decode()} (status {status})")
+
+
+def ptr(t):
+    """Device pointer of a tensor (None -> NULL)."""
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(device=None):
+    import torch
+    return torch.cuda.current_stream(device).cuda_stream

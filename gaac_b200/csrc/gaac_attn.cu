@@ -1,0 +1,558 @@
+// Fused decode attention over GAAC-compressed K/V (sm_100a): slot layout and paged layout in one kernel template.
+//
+// CTA = (batch row, kv head, context split), ATT_WARPS warps.  Every warp streams its own 16-token tiles through a private
+// two-stage shared-memory ring filled with cp.async (16-byte chunks, re-ordered so that the later LDS.128 reads are
+// bank-conflict free), rebuilds BF16 K/V fragments in registers (byte-SWAR, gaac_tile.h) and feeds mma.sync m16n8k16:
+//   S^T[16 tok x 8 heads] = K[16 x 128] . Q^T        O^T[128 dims x 8 heads] += V^T[128 x 16 tok] . P^T
+// with an fp32 online softmax in the exp2 domain.  Raw BF16 tiles (the slot layout's tail, the paged layout's filling block
+// and raw-fallback tiles) are read straight from global memory into the same fragments.  The warps of a CTA are merged in
+// shared memory, the CTA writes one partial (m, l, acc[128]) per query head, and the last CTA of a (row, kv head) to
+// finish merges the splits and writes the output, so one launch does the whole layer.
+//
+// Fragment conventions follow the reference kernel (gaac/kernel.py:62-66,160-194), whose storage order they mirror.
+#include <cuda_bf16.h>
+#include <math_constants.h>
+#include "gaac_api.cuh"
+#include "gaac_tile.h"
+
+namespace gaac {
+
+constexpr int ATT_WARPS = 8;
+constexpr int ATT_THREADS = ATT_WARPS * 32;
+constexpr int NSTAGE = 2;
+constexpr int ESC_WIN = 256;                         // escape bytes staged per tile and kind; longer tiles read the rest from global
+// stage layout (bytes)
+constexpr int ST_KSM = 0, ST_KCD = 2048, ST_VSM = 2816, ST_VCD = 4864, ST_KFL = 5632, ST_VFL = 5696, ST_KESC = 5760, ST_VESC = ST_KESC + ESC_WIN;
+constexpr int STAGE_BYTES = ST_VESC + ESC_WIN;       // 6272
+constexpr int ATT_SMEM = ATT_WARPS * NSTAGE * STAGE_BYTES;
+constexpr unsigned FULLM = 0xffffffffu;
+constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+
+struct AttnParams {
+  // slot layout
+  gaac_side K, V;
+  const int* slot; const int* seq_len; const int* tail_len; int tail_cap; long S_pad; int n_base_rows;
+  // paged layout
+  const uint8_t* buf; const uint16_t* raw; const int* mt; const int* bt; long bt_stride; int TS; int ovf_slot;
+  const uint8_t *b3k, *b4k, *b3v, *b4v;
+  // common
+  const uint16_t* q; int B, n_q, n_kv, G; float scale_log2; int nsplit;
+  int* counters; float* pm; float* pl; float* pa;
+  uint16_t* out; float* out_f32; float* part;
+};
+
+__device__ __forceinline__ void mma16816(float* c, const u32* a, u32 b0, u32 b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp16(u32 dst, const void* src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src)); }
+__device__ __forceinline__ void cp4(u32 dst, const void* src) { asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src)); }
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ float fast_exp2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+
+// Escape bytes of the tile being consumed: a window in shared memory backed by global memory for long tiles.
+struct WinEsc {
+  const uint8_t* win;     // shared-memory window, already advanced to the tile's first escape byte
+  const uint8_t* glob;    // global address of the tile's first escape byte
+  int lim;                // window bytes valid from `win`
+  __device__ __forceinline__ u32 byte(int pos) const { return pos < lim ? win[pos] : glob[pos]; }
+  __device__ __forceinline__ u64 bytes5(int pos) const {
+    const uint8_t* p = (pos + 5 <= lim) ? win + pos : glob + pos;
+    return (u64)p[0] | ((u64)p[1] << 8) | ((u64)p[2] << 16) | ((u64)p[3] << 24) | ((u64)p[4] << 32);
+  }
+};
+
+// Where the pieces of one tile live.
+struct TileRef {
+  const uint8_t *ksm, *kcd, *kfl, *kesc;      // compressed K (kesc = global address of its first escape byte)
+  const uint8_t *vsm, *vcd, *vfl, *vesc;
+  const uint16_t *kraw, *vraw;                // raw bf16 [16][128] when the side is raw
+  bool rawk, rawv;
+  int esc_lim_k, esc_lim_v;                   // bytes that may be staged from kesc / vesc (allocation bound)
+};
+
+// Escape bytes, counted from the tile's first escape byte `esc`, that the staged window holds: the window starts at the
+// 4-byte boundary below `esc`, is ESC_WIN bytes long at most, is copied in whole words and stays inside the allocation
+// (alloc_left = bytes from `esc` to the end of the escape buffer).
+__device__ __forceinline__ int esc_window_bytes(const uint8_t* esc, int alloc_left) {
+  const int wsh = (int)(reinterpret_cast<uintptr_t>(esc) & 3);
+  return max(0, min(ESC_WIN, (alloc_left + wsh) & ~3) - wsh);
+}
+
+// Issue the cp.async copies of one tile into a stage.  smem destinations of the sign/mantissa chunks are permuted:
+//   K: global chunk c (16 B) = (octet o = c>>6, lane l = (c>>1)&31, half = c&1)  ->  slot o*64 + half*32 + l
+//   V: global chunk c = (lane l = c>>2, token slot t = c&3)                      ->  slot t*32 + l
+__device__ __forceinline__ void issue_tile(u32 st, const TileRef& tr, int lane) {
+  if (!tr.rawk) {
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      int c = lane + 32 * k;
+      cp16(st + ST_KSM + 16 * ((c >> 6) * 64 + (c & 1) * 32 + ((c >> 1) & 31)), tr.ksm + 16 * c);
+    }
+    cp16(st + ST_KCD + 16 * lane, tr.kcd + 16 * lane);
+    if (lane < 16) cp16(st + ST_KCD + 16 * (32 + lane), tr.kcd + 16 * (32 + lane));
+    if (lane < 4) cp16(st + ST_KFL + 16 * lane, tr.kfl + 16 * lane);
+    const uint8_t* a = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(tr.kesc) & ~(uintptr_t)3);
+    const int lim = esc_window_bytes(tr.kesc, tr.esc_lim_k) + (int)(tr.kesc - a);
+#pragma unroll
+    for (int k = 0; k < ESC_WIN / 128; k++) { int off = 4 * lane + 128 * k; if (off < lim) cp4(st + ST_KESC + off, a + off); }
+  }
+  if (!tr.rawv) {
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      int c = lane + 32 * k;
+      cp16(st + ST_VSM + 16 * ((c & 3) * 32 + (c >> 2)), tr.vsm + 16 * c);
+    }
+    cp16(st + ST_VCD + 16 * lane, tr.vcd + 16 * lane);
+    if (lane >= 16) cp16(st + ST_VCD + 16 * (16 + lane), tr.vcd + 16 * (16 + lane));
+    if (lane >= 28) cp16(st + ST_VFL + 16 * (lane - 28), tr.vfl + 16 * (lane - 28));
+    const uint8_t* a = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(tr.vesc) & ~(uintptr_t)3);
+    const int lim = esc_window_bytes(tr.vesc, tr.esc_lim_v) + (int)(tr.vesc - a);
+#pragma unroll
+    for (int k = 0; k < ESC_WIN / 128; k++) { int off = 4 * lane + 128 * k; if (off < lim) cp4(st + ST_VESC + off, a + off); }
+  }
+}
+
+// Running state of one warp.
+struct WarpAcc {
+  float acc[8][4];       // m-tile mt: c0 = O[dim 16mt+r][head 2j], c1 = [..][2j+1], c2 = O[16mt+r+8][2j], c3 = [..][2j+1]
+  float m0, m1, l0, l1;  // heads 2j, 2j+1 (exp2 domain); l summed over this lane's tokens only
+};
+
+// Online softmax on the score fragment + P^T B-fragments for the PV product.
+__device__ __forceinline__ void softmax_step(WarpAcc& A, const float* sc, float scale_log2, int nvalid, int lane, u32& pb0, u32& pb1) {
+  const int j = lane & 3, r = lane >> 2;
+  const bool v0 = r < nvalid, v8 = r + 8 < nvalid;
+  const float s00 = v0 ? sc[0] * scale_log2 : -CUDART_INF_F, s01 = v0 ? sc[1] * scale_log2 : -CUDART_INF_F;
+  const float s80 = v8 ? sc[2] * scale_log2 : -CUDART_INF_F, s81 = v8 ? sc[3] * scale_log2 : -CUDART_INF_F;
+  float mt0 = fmaxf(s00, s80), mt1 = fmaxf(s01, s81);
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) { mt0 = fmaxf(mt0, __shfl_xor_sync(FULLM, mt0, o)); mt1 = fmaxf(mt1, __shfl_xor_sync(FULLM, mt1, o)); }
+  const float mn0 = fmaxf(A.m0, mt0), mn1 = fmaxf(A.m1, mt1);
+  const float mu0 = (mn0 == -CUDART_INF_F) ? 0.f : mn0, mu1 = (mn1 == -CUDART_INF_F) ? 0.f : mn1;
+  const float al0 = fast_exp2(A.m0 - mu0), al1 = fast_exp2(A.m1 - mu1);
+  const float p00 = fast_exp2(s00 - mu0), p80 = fast_exp2(s80 - mu0), p01 = fast_exp2(s01 - mu1), p81 = fast_exp2(s81 - mu1);
+  A.l0 = A.l0 * al0 + (p00 + p80); A.l1 = A.l1 * al1 + (p01 + p81); A.m0 = mn0; A.m1 = mn1;
+#pragma unroll
+  for (int n = 0; n < 8; n++) { A.acc[n][0] *= al0; A.acc[n][2] *= al0; A.acc[n][1] *= al1; A.acc[n][3] *= al1; }
+  // this lane publishes W0 = (P[tok r][2j], P[tok r][2j+1]), W8 = (P[tok r+8][2j], P[tok r+8][2j+1]);
+  // it needs b0 = (P[tok 2j][head r], P[tok 2j+1][head r]), b1 = the same for tokens 2j+8, 2j+9
+  __nv_bfloat162 x = __floats2bfloat162_rn(p00, p01), y = __floats2bfloat162_rn(p80, p81);
+  const u32 W0 = *reinterpret_cast<u32*>(&x), W8 = *reinterpret_cast<u32*>(&y);
+  const int srcA = 8 * j + (r >> 1), srcB = srcA + 4;
+  const u32 a0 = __shfl_sync(FULLM, W0, srcA), a8 = __shfl_sync(FULLM, W8, srcA), b0w = __shfl_sync(FULLM, W0, srcB), b8w = __shfl_sync(FULLM, W8, srcB);
+  const u32 sel = (r & 1) ? 0x7632u : 0x5410u;
+  pb0 = prmt(a0, b0w, sel); pb1 = prmt(a8, b8w, sel);
+}
+
+// PV for one pair of V words: tokens (2j, 2j+1, 2j+8, 2j+9) x elements (4w .. 4w+3).
+__device__ __forceinline__ void pv_words(WarpAcc& A, int w, const u32 (&u01)[4], const u32 (&u23)[4], u32 pb0, u32 pb1) {
+  u32 a[4];
+  a[0] = prmt(u01[0], u01[1], 0x5410); a[2] = prmt(u01[2], u01[3], 0x5410);     // dim 8(4w)+r
+  a[1] = prmt(u01[0], u01[1], 0x7632); a[3] = prmt(u01[2], u01[3], 0x7632);     // dim 8(4w+1)+r
+  mma16816(A.acc[2 * w], a, pb0, pb1);
+  a[0] = prmt(u23[0], u23[1], 0x5410); a[2] = prmt(u23[2], u23[3], 0x5410);     // dim 8(4w+2)+r
+  a[1] = prmt(u23[0], u23[1], 0x7632); a[3] = prmt(u23[2], u23[3], 0x7632);     // dim 8(4w+3)+r
+  mma16816(A.acc[2 * w + 1], a, pb0, pb1);
+}
+
+// Consume one tile: stage = shared-memory stage of the compressed sides, tr = its description, nvalid = valid tokens (1..16).
+__device__ __forceinline__ void process_tile(WarpAcc& A, const uint8_t* stage, const TileRef& tr, int nvalid, int lane,
+                                             const u32 (&qa)[8][2], const u32 (&kb3)[8], const u32 (&kd)[8], const u32 (&vb3)[4], const u32 (&vd)[4],
+                                             float scale_log2) {
+  const int j = lane & 3, r = lane >> 2;
+  // ---- row offsets of the escape bytes: lanes 0-15 scan the K rows, lanes 16-31 the V rows
+  int rowoff;
+  u32 flrow;
+  {
+    const int row = lane & 15;
+    const bool isv = lane >= 16;
+    const bool raw = isv ? tr.rawv : tr.rawk;
+    flrow = raw ? 0u : *reinterpret_cast<const u32*>(stage + (isv ? ST_VFL : ST_KFL) + 4 * row);
+    const int sz = row_esc_bytes(flrow);
+    int inc = sz;
+#pragma unroll
+    for (int d = 1; d < 16; d <<= 1) { int v = __shfl_up_sync(FULLM, inc, d, 16); if (row >= d) inc += v; }
+    rowoff = inc - sz;
+  }
+  // ---- scores
+  float sc[4] = {0.f, 0.f, 0.f, 0.f};
+  if (!tr.rawk) {
+    const int wsh = (int)(reinterpret_cast<uintptr_t>(tr.kesc) & 3);
+    const WinEsc esc{stage + ST_KESC + wsh, tr.kesc, esc_window_bytes(tr.kesc, tr.esc_lim_k)};
+    u32 fl[2]; int pos[2]; uint4 s0[2], s1[2]; u32 cd[2][3];
+#pragma unroll
+    for (int o = 0; o < 2; o++) {
+      fl[o] = __shfl_sync(FULLM, flrow, 8 * o + r);
+      pos[o] = __shfl_sync(FULLM, rowoff, 8 * o + r) + esc_prefix(fl[o], 8 * j);
+      s0[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + lane));
+      s1[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + 32 + lane));
+      const u32* c = reinterpret_cast<const u32*>(stage + ST_KCD + o * 384 + 12 * lane);
+      cd[o][0] = c[0]; cd[o][1] = c[1]; cd[o][2] = c[2];
+    }
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+      u32 f[2][4];
+#pragma unroll
+      for (int o = 0; o < 2; o++) {
+        const u32 smlo = g == 0 ? s0[o].x : g == 1 ? s0[o].z : g == 2 ? s1[o].x : s1[o].z;
+        const u32 smhi = g == 0 ? s0[o].y : g == 1 ? s0[o].w : g == 2 ? s1[o].y : s1[o].w;
+        decode_group(smlo, smhi, k_group_codes(cd[o], g), (fl[o] >> (8 * j + 2 * g)) & 3u, pos[o], esc, kb3[2 * g], kb3[2 * g + 1], kd[2 * g], kd[2 * g + 1], f[o]);
+      }
+      { const u32 a[4] = {f[0][0], f[1][0], f[0][1], f[1][1]}; mma16816(sc, a, qa[2 * g][0], qa[2 * g][1]); }
+      { const u32 a[4] = {f[0][2], f[1][2], f[0][3], f[1][3]}; mma16816(sc, a, qa[2 * g + 1][0], qa[2 * g + 1][1]); }
+    }
+  } else {
+#pragma unroll
+    for (int s = 0; s < 8; s++) {
+      u32 a[4];
+      const uint16_t* k0 = tr.kraw + r * D + 16 * s + 2 * j;
+      const uint16_t* k8 = k0 + 8 * D;
+      a[0] = r < nvalid ? *reinterpret_cast<const u32*>(k0) : 0u; a[2] = r < nvalid ? *reinterpret_cast<const u32*>(k0 + 8) : 0u;
+      a[1] = r + 8 < nvalid ? *reinterpret_cast<const u32*>(k8) : 0u; a[3] = r + 8 < nvalid ? *reinterpret_cast<const u32*>(k8 + 8) : 0u;
+      mma16816(sc, a, qa[s][0], qa[s][1]);
+    }
+  }
+  // ---- softmax, P^T
+  u32 pb0, pb1;
+  softmax_step(A, sc, scale_log2, nvalid, lane, pb0, pb1);
+  // ---- PV
+  if (!tr.rawv) {
+    const int wsh = (int)(reinterpret_cast<uintptr_t>(tr.vesc) & 3);
+    const WinEsc esc{stage + ST_VESC + wsh, tr.vesc, esc_window_bytes(tr.vesc, tr.esc_lim_v)};
+    u32 fl[4]; int pos[4]; uint4 sm[4]; u32 cd[6];
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+      const int tok = 2 * j + (t & 1) + 8 * (t >> 1);
+      fl[t] = __shfl_sync(FULLM, flrow, 16 + tok);
+      pos[t] = __shfl_sync(FULLM, rowoff, 16 + tok) + esc_prefix(fl[t], 4 * r);
+      sm[t] = *reinterpret_cast<const uint4*>(stage + ST_VSM + 16 * (t * 32 + lane));
+    }
+    {
+      const uint2* c2 = reinterpret_cast<const uint2*>(stage + ST_VCD + 24 * lane);
+      uint2 ca = c2[0], cb = c2[1], cc = c2[2];
+      cd[0] = ca.x; cd[1] = ca.y; cd[2] = cb.x; cd[3] = cb.y; cd[4] = cc.x; cd[5] = cc.y;
+    }
+#pragma unroll
+    for (int g = 0; g < 2; g++) {
+      u32 f[4][4];
+#pragma unroll
+      for (int t = 0; t < 4; t++) {
+        const u32 smlo = g == 0 ? sm[t].x : sm[t].z, smhi = g == 0 ? sm[t].y : sm[t].w;
+        decode_group(smlo, smhi, v_group_codes(cd, t, g), (fl[t] >> (4 * r + 2 * g)) & 3u, pos[t], esc, vb3[2 * g], vb3[2 * g + 1], vd[2 * g], vd[2 * g + 1], f[t]);
+      }
+#pragma unroll
+      for (int h = 0; h < 2; h++) {
+        const u32 u01[4] = {f[0][2 * h], f[1][2 * h], f[2][2 * h], f[3][2 * h]};
+        const u32 u23[4] = {f[0][2 * h + 1], f[1][2 * h + 1], f[2][2 * h + 1], f[3][2 * h + 1]};
+        pv_words(A, 2 * g + h, u01, u23, pb0, pb1);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int w = 0; w < 4; w++) {
+      u32 u01[4], u23[4];
+#pragma unroll
+      for (int t = 0; t < 4; t++) {
+        const int tok = 2 * j + (t & 1) + 8 * (t >> 1);
+        const uint16_t* vr = tr.vraw + tok * D + 8 * (4 * w) + r;
+        const bool ok = tok < nvalid;
+        const u32 e0 = ok ? vr[0] : 0u, e1 = ok ? vr[8] : 0u, e2 = ok ? vr[16] : 0u, e3 = ok ? vr[24] : 0u;
+        u01[t] = e0 | (e1 << 16); u23[t] = e2 | (e3 << 16);
+      }
+      pv_words(A, w, u01, u23, pb0, pb1);
+    }
+  }
+}
+
+template <bool PAGED>
+__global__ void __launch_bounds__(ATT_THREADS, 2) decode_attn_kernel(const __grid_constant__ AttnParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int bh = blockIdx.x, split = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, j = lane & 3, r = lane >> 2;
+  const int b = bh / p.n_kv, kvh = bh % p.n_kv, G = p.G;
+
+  // ---- which cache head, how many tokens
+  int S, ch = 0, TL = 0;
+  if (PAGED) { S = p.seq_len[b]; }
+  else {
+    const int sl = p.slot[b];
+    ch = (sl < 0 ? 0 : sl) * p.n_kv + kvh;
+    S = sl < 0 ? 0 : p.seq_len[ch];
+    TL = (sl < 0 || !p.tail_len) ? 0 : p.tail_len[ch];
+  }
+  const int ntiles = (S + 15) >> 4, chunk = (ntiles + p.nsplit - 1) / p.nsplit;
+  const int tlo = min(split * chunk, ntiles), thi = min(tlo + chunk, ntiles);
+
+  // ---- base words and query fragments
+  u32 kb3[8], kd[8], vb3[4], vd[4];
+  {
+    const int brow = PAGED ? kvh : ch % p.n_base_rows;
+    const uint8_t* b3k = (PAGED ? p.b3k : p.K.base3) + brow * D; const uint8_t* b4k = (PAGED ? p.b4k : p.K.base4) + brow * D;
+    const uint8_t* b3v = (PAGED ? p.b3v : p.V.base3) + brow * D; const uint8_t* b4v = (PAGED ? p.b4v : p.V.base4) + brow * D;
+    k_base_words(b3k, j, kb3); k_base_words(b4k, j, kd); v_base_words(b3v, r, vb3); v_base_words(b4v, r, vd);
+#pragma unroll
+    for (int i = 0; i < 8; i++) kd[i] -= kb3[i];
+#pragma unroll
+    for (int i = 0; i < 4; i++) vd[i] -= vb3[i];
+  }
+  u32 qa[8][2];
+  {
+    const bool ok = r < G;
+    const uint16_t* qp = p.q + ((long)b * p.n_q + kvh * G + (ok ? r : 0)) * D;
+#pragma unroll
+    for (int s = 0; s < 8; s++) {
+      qa[s][0] = ok ? *reinterpret_cast<const u32*>(qp + 16 * s + 2 * j) : 0u;
+      qa[s][1] = ok ? *reinterpret_cast<const u32*>(qp + 16 * s + 2 * j + 8) : 0u;
+    }
+  }
+  WarpAcc A;
+#pragma unroll
+  for (int n = 0; n < 8; n++) A.acc[n][0] = A.acc[n][1] = A.acc[n][2] = A.acc[n][3] = 0.f;
+  A.m0 = A.m1 = -CUDART_INF_F; A.l0 = A.l1 = 0.f;
+
+  // ---- tile addressing
+  uint8_t* ring = smem + warp * (NSTAGE * STAGE_BYTES);
+  const u32 ring_s = (u32)__cvta_generic_to_shared(ring);
+  const long smh = (long)ch * p.S_pad * D, cdh = (long)ch * p.S_pad * CB, rowb = (long)ch * p.S_pad, tileb = (long)ch * (p.S_pad >> 4);
+  int ohk = 0, ohv = 0;
+  if (!PAGED && S > 0) { ohk = p.K.head_start[ch]; ohv = p.V.head_start[ch]; }
+  // meta = what must be known before the copies of a tile can be issued: escape offsets (slot) or table entries (paged)
+  auto load_meta = [&](int tile, int& mk, int& mv) {
+    if (PAGED) { const int pc = p.bt[(long)b * p.bt_stride + tile] * (2 * p.n_kv) + 2 * kvh; mk = p.mt[pc]; mv = p.mt[pc + 1]; }
+    else { mk = p.K.tile_off[tileb + tile]; mv = p.V.tile_off[tileb + tile]; }
+  };
+  auto make_ref = [&](int tile, int mk, int mv, TileRef& tr) {
+    if (PAGED) {
+      tr.rawk = mk < 0; tr.rawv = mv < 0;
+      const long pk = tr.rawk ? ~mk : mk, pv = tr.rawv ? ~mv : mv;
+      const uint8_t* sk = p.buf + pk * p.TS; const uint8_t* sv = p.buf + pv * p.TS;
+      tr.ksm = sk; tr.kcd = sk + SLOT_CD_OFF; tr.kfl = sk + SLOT_FL_OFF; tr.kesc = sk + SLOT_OVF_OFF; tr.esc_lim_k = p.ovf_slot;
+      tr.vsm = sv; tr.vcd = sv + SLOT_CD_OFF; tr.vfl = sv + SLOT_FL_OFF; tr.vesc = sv + SLOT_OVF_OFF; tr.esc_lim_v = p.ovf_slot;
+      tr.kraw = p.raw + pk * (T * D); tr.vraw = p.raw + pv * (T * D);
+    } else {
+      tr.rawk = tr.rawv = false;
+      tr.ksm = p.K.sm + smh + (long)tile * TILE_SM; tr.kcd = p.K.codes + cdh + (long)tile * TILE_CD;
+      tr.kfl = reinterpret_cast<const uint8_t*>(p.K.flags + rowb + (long)tile * T);
+      tr.vsm = p.V.sm + smh + (long)tile * TILE_SM; tr.vcd = p.V.codes + cdh + (long)tile * TILE_CD;
+      tr.vfl = reinterpret_cast<const uint8_t*>(p.V.flags + rowb + (long)tile * T);
+      const long ek = (long)ohk + mk, ev = (long)ohv + mv;
+      tr.kesc = p.K.ovf + ek; tr.vesc = p.V.ovf + ev;
+      tr.esc_lim_k = (int)min((long)ESC_WIN, p.K.ovf_bytes - ek); tr.esc_lim_v = (int)min((long)ESC_WIN, p.V.ovf_bytes - ev);
+      tr.kraw = tr.vraw = nullptr;
+    }
+  };
+
+  // ---- the warp's tiles: tlo + warp, + ATT_WARPS, ...
+  int tile = tlo + warp;
+  TileRef cur, nxt;
+  int mk = 0, mv = 0;
+  if (tile < thi) {
+    load_meta(tile, mk, mv); make_ref(tile, mk, mv, cur);
+    issue_tile(ring_s, cur, lane);
+    if (tile + ATT_WARPS < thi) load_meta(tile + ATT_WARPS, mk, mv);
+  }
+  cp_commit();
+  int stg = 0;
+  for (; tile < thi; tile += ATT_WARPS) {
+    const int t1 = tile + ATT_WARPS;
+    if (t1 < thi) {
+      make_ref(t1, mk, mv, nxt);
+      issue_tile(ring_s + (stg ^ 1) * STAGE_BYTES, nxt, lane);
+      if (t1 + ATT_WARPS < thi) load_meta(t1 + ATT_WARPS, mk, mv);
+    }
+    cp_commit();
+    cp_wait<1>();
+    __syncwarp();
+    process_tile(A, ring + stg * STAGE_BYTES, cur, min(T, S - tile * T), lane, qa, kb3, kd, vb3, vd, p.scale_log2);
+    __syncwarp();
+    cur = nxt; stg ^= 1;
+  }
+  cp_wait<0>();
+  // ---- slot layout: the raw BF16 tail belongs to the last split's warp 0
+  if (!PAGED && TL > 0 && split == p.nsplit - 1 && warp == 0) {
+    TileRef tr; tr.rawk = tr.rawv = true;
+    tr.kraw = reinterpret_cast<const uint16_t*>(p.K.tail) + (long)ch * p.tail_cap * D;
+    tr.vraw = reinterpret_cast<const uint16_t*>(p.V.tail) + (long)ch * p.tail_cap * D;
+    for (int t0 = 0; t0 < TL; t0 += T) {
+      process_tile(A, ring, tr, min(T, TL - t0), lane, qa, kb3, kd, vb3, vd, p.scale_log2);
+      tr.kraw += T * D; tr.vraw += T * D;
+    }
+  }
+
+  // ---- merge the warps of the CTA (the ring is free now)
+  __syncthreads();
+  float* sh_m = reinterpret_cast<float*>(smem);                  // [W][8]
+  float* sh_l = sh_m + ATT_WARPS * 8;                            // [W][8]
+  float* sh_acc = sh_l + ATT_WARPS * 8;                          // [W][8][128]
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) { A.l0 += __shfl_xor_sync(FULLM, A.l0, o); A.l1 += __shfl_xor_sync(FULLM, A.l1, o); }
+  if (r == 0) { sh_m[warp * 8 + 2 * j] = A.m0; sh_l[warp * 8 + 2 * j] = A.l0; sh_m[warp * 8 + 2 * j + 1] = A.m1; sh_l[warp * 8 + 2 * j + 1] = A.l1; }
+#pragma unroll
+  for (int n = 0; n < 8; n++) {
+    float* a0 = sh_acc + ((warp * 8 + 2 * j) * D) + 16 * n + r;
+    a0[0] = A.acc[n][0]; a0[D] = A.acc[n][1]; a0[8] = A.acc[n][2]; a0[D + 8] = A.acc[n][3];
+  }
+  __syncthreads();
+  const int NS = p.nsplit;
+  {
+    const int d = tid & 127;
+    for (int g = tid >> 7; g < G; g += ATT_THREADS / 128) {
+      float M = -CUDART_INF_F;
+#pragma unroll
+      for (int w = 0; w < ATT_WARPS; w++) M = fmaxf(M, sh_m[w * 8 + g]);
+      float Lc = 0.f, Ac = 0.f;
+#pragma unroll
+      for (int w = 0; w < ATT_WARPS; w++) {
+        const float mw = sh_m[w * 8 + g];
+        const float f = (mw == -CUDART_INF_F) ? 0.f : fast_exp2(mw - M);
+        Lc += sh_l[w * 8 + g] * f; Ac += sh_acc[(w * 8 + g) * D + d] * f;
+      }
+      const long qh = (long)b * p.n_q + kvh * G + g, pidx = qh * NS + split;
+      if (d == 0) { p.pm[pidx] = M; p.pl[pidx] = Lc; }
+      p.pa[pidx * D + d] = Ac;
+    }
+  }
+  // ---- the last CTA of this (row, kv head) merges the splits
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int ticket = atomicAdd(&p.counters[bh], 1);
+    s_last = (ticket == NS - 1);
+    if (s_last) p.counters[bh] = 0;                 // leave the counter ready for the next call
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  {
+    const int d = tid & 127;
+    for (int g = tid >> 7; g < G; g += ATT_THREADS / 128) {
+      const long qh = (long)b * p.n_q + kvh * G + g;
+      float M = -CUDART_INF_F;
+      for (int s = 0; s < NS; s++) M = fmaxf(M, __ldcg(p.pm + qh * NS + s));
+      float L = 0.f, Ac = 0.f;
+      for (int s = 0; s < NS; s++) {
+        const float ms = __ldcg(p.pm + qh * NS + s);
+        const float f = (ms == -CUDART_INF_F) ? 0.f : fast_exp2(ms - M);
+        L += __ldcg(p.pl + qh * NS + s) * f; Ac += __ldcg(p.pa + (qh * NS + s) * D + d) * f;
+      }
+      if (p.part) {                                  // un-normalised partial for a cross-GPU merge: m in natural-log units
+        float* o = p.part + qh * 130;
+        if (d == 0) { o[0] = M * LN2; o[1] = L; }
+        o[2 + d] = Ac;
+      } else {
+        const float v = L > 0.f ? Ac / L : 0.f;
+        p.out[qh * D + d] = __bfloat16_as_ushort(__float2bfloat16(v));
+        if (p.out_f32) p.out_f32[qh * D + d] = v;
+      }
+    }
+  }
+}
+
+// Merge partials: pm, pl [n_heads, n_parts], pa [n_heads, n_parts, 128] (m in natural-log units).
+__global__ void __launch_bounds__(128) combine_kernel(const float* __restrict__ pm, const float* __restrict__ pl, const float* __restrict__ pa,
+                                                       int n_parts, uint16_t* __restrict__ out, float* __restrict__ out_f32) {
+  const long qh = blockIdx.x; const int d = threadIdx.x;
+  float M = -CUDART_INF_F;
+  for (int s = 0; s < n_parts; s++) M = fmaxf(M, pm[qh * n_parts + s]);
+  float L = 0.f, Ac = 0.f;
+  for (int s = 0; s < n_parts; s++) {
+    const float ms = pm[qh * n_parts + s];
+    const float f = (ms == -CUDART_INF_F) ? 0.f : __expf(ms - M);
+    L += pl[qh * n_parts + s] * f; Ac += pa[(qh * n_parts + s) * D + d] * f;
+  }
+  const float v = L > 0.f ? Ac / L : 0.f;
+  if (out) out[qh * D + d] = __bfloat16_as_ushort(__float2bfloat16(v));
+  if (out_f32) out_f32[qh * D + d] = v;
+}
+
+static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+static int carve_workspace(void* ws, size_t ws_bytes, int B, int n_q, int nsplit, AttnParams& p) {
+  const size_t n = (size_t)B * n_q * nsplit;
+  const size_t need = align256(4 * (size_t)B * n_q) + align256(4 * n) * 2 + align256(4 * n * D);
+  if (!ws || ws_bytes < need) return GAAC_E_WORKSPACE;
+  uint8_t* w = (uint8_t*)ws;
+  p.counters = (int*)w; w += align256(4 * (size_t)B * n_q);
+  p.pm = (float*)w; w += align256(4 * n);
+  p.pl = (float*)w; w += align256(4 * n);
+  p.pa = (float*)w;
+  return GAAC_OK;
+}
+
+template <bool PAGED>
+static int launch_attn(const AttnParams& p, cudaStream_t st) {
+  cudaFuncSetAttribute(decode_attn_kernel<PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+  dim3 grid((unsigned)(p.B * p.n_kv), (unsigned)p.nsplit);
+  decode_attn_kernel<PAGED><<<grid, ATT_THREADS, ATT_SMEM, st>>>(p);
+  return launch_status();
+}
+
+static int slot_attn(const gaac_side* K, const gaac_side* V, const void* q, const int32_t* slot, int B, int n_q, int n_kv, const int32_t* seq_len,
+                     int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap, int n_base_rows, void* ws, size_t ws_bytes,
+                     void* out, float* out_f32, float* part, void* stream) {
+  if (!K || !V || !q || !slot || !seq_len || (!out && !part)) return GAAC_E_ARG;
+  if (B <= 0 || n_q <= 0 || n_kv <= 0 || nsplit <= 0 || nsplit > 65535 || S_pad <= 0 || S_pad % T || n_base_rows <= 0) return GAAC_E_ARG;
+  if (n_q % n_kv || n_q / n_kv < 1 || n_q / n_kv > 8) return GAAC_E_UNSUPPORTED;
+  for (const gaac_side* s : {K, V}) {
+    if (!s->sm || !s->codes || !s->flags || !s->tile_off || !s->ovf || !s->head_start || !s->base3 || !s->base4 || s->ovf_bytes < 0) return GAAC_E_ARG;
+    if (!aligned16(s->sm) || !aligned16(s->codes) || !aligned16(s->flags) || (reinterpret_cast<uintptr_t>(s->ovf) & 3)) return GAAC_E_ALIGN;
+    if (tail_len && (!s->tail || (reinterpret_cast<uintptr_t>(s->tail) & 3))) return GAAC_E_ARG;
+  }
+  if (tail_len && tail_cap <= 0) return GAAC_E_ARG;
+  if (reinterpret_cast<uintptr_t>(q) & 3) return GAAC_E_ALIGN;
+  AttnParams p{};
+  p.K = *K; p.V = *V; p.slot = slot; p.seq_len = seq_len; p.tail_len = tail_len; p.tail_cap = tail_cap; p.S_pad = S_pad; p.n_base_rows = n_base_rows;
+  p.q = (const uint16_t*)q; p.B = B; p.n_q = n_q; p.n_kv = n_kv; p.G = n_q / n_kv; p.scale_log2 = scale * LOG2E; p.nsplit = nsplit;
+  p.out = (uint16_t*)out; p.out_f32 = out_f32; p.part = part;
+  if (int e = carve_workspace(ws, ws_bytes, B, n_q, nsplit, p)) return e;
+  return launch_attn<false>(p, (cudaStream_t)stream);
+}
+
+}  // namespace gaac
+
+using namespace gaac;
+
+extern "C" size_t gaac_attn_workspace_bytes(int B, int n_q, int nsplit) {
+  if (B <= 0 || n_q <= 0 || nsplit <= 0) return 0;
+  const size_t n = (size_t)B * n_q * nsplit;
+  return align256(4 * (size_t)B * n_q) + align256(4 * n) * 2 + align256(4 * n * D);
+}
+
+extern "C" int gaac_decode_attn(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
+                                const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
+                                int n_base_rows, void* workspace, size_t workspace_bytes, void* out_bf16, float* out_f32, void* stream) {
+  if (!out_bf16) return GAAC_E_ARG;
+  return slot_attn(K, V, q_bf16, slot, B, n_q, n_kv, seq_len, S_pad, scale, nsplit, tail_len, tail_cap, n_base_rows, workspace, workspace_bytes,
+                   out_bf16, out_f32, nullptr, stream);
+}
+
+extern "C" int gaac_decode_attn_partial(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
+                                        const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
+                                        int n_base_rows, void* workspace, size_t workspace_bytes, float* part, void* stream) {
+  if (!part) return GAAC_E_ARG;
+  return slot_attn(K, V, q_bf16, slot, B, n_q, n_kv, seq_len, S_pad, scale, nsplit, tail_len, tail_cap, n_base_rows, workspace, workspace_bytes,
+                   nullptr, nullptr, part, stream);
+}
+
+extern "C" int gaac_combine(const float* pm, const float* pl, const float* pa, int64_t n_heads, int n_parts, void* out_bf16, float* out_f32, void* stream) {
+  if (!pm || !pl || !pa || n_heads <= 0 || n_parts <= 0 || (!out_bf16 && !out_f32)) return GAAC_E_ARG;
+  combine_kernel<<<(unsigned)n_heads, 128, 0, (cudaStream_t)stream>>>(pm, pl, pa, n_parts, (uint16_t*)out_bf16, out_f32);
+  return launch_status();
+}
+
+extern "C" int gaac_paged_decode_attn(const gaac_paged* st, const int32_t* bt, int64_t bt_stride, const int32_t* seq_lens, const void* q_bf16,
+                                      int B, int n_q, float scale, int nsplit, void* workspace, size_t workspace_bytes,
+                                      void* out_bf16, float* out_f32, void* stream) {
+  if (!st || !bt || !seq_lens || !q_bf16 || !out_bf16 || !st->buf || !st->raw || !st->mt || !st->b3k || !st->b4k || !st->b3v || !st->b4v) return GAAC_E_ARG;
+  if (B <= 0 || n_q <= 0 || st->n_kv <= 0 || nsplit <= 0 || nsplit > 65535 || bt_stride <= 0) return GAAC_E_ARG;
+  if (n_q % st->n_kv || n_q / st->n_kv < 1 || n_q / st->n_kv > 8 || st->TS % 16 || st->TS != SLOT_OVF_OFF + st->ovf_slot) return GAAC_E_UNSUPPORTED;
+  if (!aligned16(st->buf) || (reinterpret_cast<uintptr_t>(st->raw) & 3) || (reinterpret_cast<uintptr_t>(q_bf16) & 3)) return GAAC_E_ALIGN;
+  AttnParams p{};
+  p.buf = st->buf; p.raw = (const uint16_t*)st->raw; p.mt = st->mt; p.bt = bt; p.bt_stride = bt_stride; p.TS = st->TS; p.ovf_slot = st->ovf_slot;
+  p.b3k = st->b3k; p.b4k = st->b4k; p.b3v = st->b3v; p.b4v = st->b4v; p.seq_len = seq_lens;
+  p.q = (const uint16_t*)q_bf16; p.B = B; p.n_q = n_q; p.n_kv = st->n_kv; p.G = n_q / st->n_kv; p.scale_log2 = scale * LOG2E; p.nsplit = nsplit;
+  p.out = (uint16_t*)out_bf16; p.out_f32 = out_f32; p.part = nullptr;
+  if (int e = carve_workspace(workspace, workspace_bytes, B, n_q, nsplit, p)) return e;
+  return launch_attn<true>(p, (cudaStream_t)stream);
+}

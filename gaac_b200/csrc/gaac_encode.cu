@@ -1,0 +1,218 @@
+// Block encoder, escape-stream compaction, page decoder and calibration kernels (sm_100a).
+#include "gaac_api.cuh"
+#include "gaac_warp.cuh"
+
+namespace gaac {
+
+constexpr int ENC_WARPS = 4;          // warps per CTA
+constexpr int ENC_TILES_PER_WARP = 4; // consecutive work items of one warp share the head's base words
+
+// One warp per (head, tile).  grid = (ceil(ntiles / (ENC_WARPS*ENC_TILES_PER_WARP)), H).
+template <int KIND_V>
+__global__ void __launch_bounds__(ENC_WARPS * 32) encode_tiles_kernel(
+    const uint16_t* __restrict__ x, long S, long S_in, long S_pad, const uint8_t* __restrict__ base3, const uint8_t* __restrict__ base4,
+    const int* __restrict__ bidx, int n_kv, uint8_t* __restrict__ sm, uint8_t* __restrict__ codes, int* __restrict__ flags,
+    uint8_t* __restrict__ slots, int* __restrict__ tile_bytes, int ntiles) {
+  __shared__ __align__(16) WarpScratch scratch[ENC_WARPS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long h = blockIdx.y;
+  WarpScratch& ws = scratch[warp];
+  const int brow = bidx ? bidx[h] : (int)(h % n_kv);
+  u32 b3w[8], b4w[8];
+  load_base_words<KIND_V>(base3 + (long)brow * D, base4 + (long)brow * D, lane, b3w, b4w);
+  const int tile0 = blockIdx.x * (ENC_WARPS * ENC_TILES_PER_WARP);
+  for (int i = 0; i < ENC_TILES_PER_WARP; i++) {
+    const int tile = tile0 + i * ENC_WARPS + warp;
+    if (tile >= ntiles) break;                       // warp-uniform
+    const long row0 = (long)tile * T;
+    const int nvalid = (int)min((long)T, S - row0);
+    stage_rows(ws, x + (h * S_in + row0) * D, D, nvalid, lane);
+    LaneTile lt;
+    const int total = encode_tile_warp<KIND_V>(ws, nvalid, b3w, b4w, lane, lt);
+    const long trow = h * S_pad + row0;
+    store_tile_payload<KIND_V>(lt, sm + trow * D, codes + trow * CB, lane);
+    if (lane < T) flags[trow + lane] = (int)ws.fl[lane];
+    store_tile_escapes<KIND_V>(ws, lt, slots + (h * ntiles + tile) * (long)TILE_MAX_ESC, lane);
+    if (lane == 0) tile_bytes[h * ntiles + tile] = total;
+  }
+}
+
+// Exclusive prefix of tile_bytes per head.  One CTA per head.
+__global__ void __launch_bounds__(256) tile_scan_kernel(const int* __restrict__ tile_bytes, int ntiles, int* __restrict__ tile_off,
+                                                         long tile_off_stride, int* __restrict__ head_bytes) {
+  __shared__ int wsum[8];
+  __shared__ int carry_s;
+  const long h = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) carry_s = 0;
+  __syncthreads();
+  for (int base = 0; base < ntiles; base += 256) {
+    const int i = base + tid;
+    const int v = i < ntiles ? tile_bytes[h * ntiles + i] : 0;
+    int inc = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) { int u = __shfl_up_sync(FULL, inc, d); if (lane >= d) inc += u; }
+    if (lane == 31) wsum[warp] = inc;
+    __syncthreads();
+    int woff = 0;
+    for (int w = 0; w < warp; w++) woff += wsum[w];
+    const int carry = carry_s;
+    if (i < ntiles) tile_off[h * tile_off_stride + i] = carry + woff + inc - v;
+    __syncthreads();
+    if (tid == 255) carry_s = carry + woff + inc;
+    __syncthreads();
+  }
+  if (tid == 0 && head_bytes) head_bytes[h] = carry_s;
+}
+
+// One warp per (head, tile): slot -> ovf[head_start[h] + tile_off[h, tile]].
+__global__ void __launch_bounds__(128) compact_copy_kernel(const uint8_t* __restrict__ slots, const int* __restrict__ tile_bytes, int ntiles,
+                                                            const int* __restrict__ tile_off, long tile_off_stride,
+                                                            const int* __restrict__ head_start, uint8_t* __restrict__ ovf, long n_items) {
+  const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (item >= n_items) return;
+  const int lane = threadIdx.x & 31;
+  const long h = item / ntiles, t = item % ntiles;
+  const int n = tile_bytes[item];
+  const uint8_t* src = slots + item * (long)TILE_MAX_ESC;
+  uint8_t* dst = ovf + (long)head_start[h] + tile_off[h * tile_off_stride + t];
+  for (int i = lane; i < n; i += 32) dst[i] = src[i];
+}
+
+// One warp per (head, tile): compressed tile -> bf16 rows.
+template <int KIND_V>
+__global__ void __launch_bounds__(ENC_WARPS * 32) decode_page_kernel(
+    const uint8_t* __restrict__ sm, const uint8_t* __restrict__ codes, const int* __restrict__ flags, const int* __restrict__ tile_off,
+    long tile_off_stride, const uint8_t* __restrict__ ovf, const int* __restrict__ head_start, const uint8_t* __restrict__ base3,
+    const uint8_t* __restrict__ base4, const int* __restrict__ bidx, int n_kv, long S, long S_pad, uint16_t* __restrict__ out, int ntiles) {
+  __shared__ __align__(16) WarpScratch scratch[ENC_WARPS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long h = blockIdx.y;
+  WarpScratch& ws = scratch[warp];
+  const int brow = bidx ? bidx[h] : (int)(h % n_kv);
+  u32 b3w[8], b4w[8];
+  load_base_deltas<KIND_V>(base3 + (long)brow * D, base4 + (long)brow * D, lane, b3w, b4w);
+  const int tile0 = blockIdx.x * (ENC_WARPS * ENC_TILES_PER_WARP);
+  for (int i = 0; i < ENC_TILES_PER_WARP; i++) {
+    const int tile = tile0 + i * ENC_WARPS + warp;
+    if (tile >= ntiles) break;
+    const long row0 = (long)tile * T, trow = h * S_pad + row0;
+    PtrEsc esc{ovf + (long)head_start[h] + tile_off[h * tile_off_stride + tile]};
+    __syncwarp();
+    decode_tile_warp<KIND_V>(ws, sm + trow * D, codes + trow * CB, reinterpret_cast<const u32*>(flags + trow), esc, b3w, b4w, lane);
+    unstage_rows(ws, out + (h * S + row0) * D, D, (int)min((long)T, S - row0), lane);
+  }
+}
+
+// Exponent histogram: x [N, n_ch] bf16, hist [n_ch, 256] int64.  grid = (ceil(n_ch/128), row chunks); a thread owns one
+// channel and keeps a private 256-bin histogram of 16-bit counters in shared memory, flushed with atomics.
+constexpr int HIST_ROWS = 2048;       // rows per CTA (16-bit counters cannot overflow)
+__global__ void __launch_bounds__(128) exponent_hist_kernel(const uint16_t* __restrict__ x, long N, long n_ch, unsigned long long* __restrict__ hist) {
+  extern __shared__ unsigned short bins[];           // [256][128]: bin-major so a warp's increments spread over banks
+  const int tid = threadIdx.x;
+  const long c = (long)blockIdx.x * 128 + tid;
+  for (int b = 0; b < 256; b++) bins[b * 128 + tid] = 0;
+  const long r0 = (long)blockIdx.y * HIST_ROWS, r1 = min(N, r0 + HIST_ROWS);
+  if (c < n_ch)
+    for (long r = r0; r < r1; r++) bins[((x[r * n_ch + c] >> 7) & 0xFF) * 128 + tid]++;
+  if (c < n_ch)
+    for (int b = 0; b < 256; b++) {
+      unsigned v = bins[b * 128 + tid];
+      if (v) atomicAdd(&hist[c * 256 + b], (unsigned long long)v);
+    }
+}
+
+// One warp per histogram row: densest 8- and 16-wide window, first maximum wins.
+__global__ void __launch_bounds__(128) bases_from_hist_kernel(const long long* __restrict__ hist, long n_rows, uint8_t* __restrict__ base3, uint8_t* __restrict__ base4) {
+  __shared__ long long cs[4][257];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long row = (long)blockIdx.x * 4 + warp;
+  if (row >= n_rows) return;
+  long long carry = 0;
+  if (lane == 0) cs[warp][0] = 0;
+  for (int b = 0; b < 256; b += 32) {
+    long long v = hist[row * 256 + b + lane], inc = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) { long long u = __shfl_up_sync(FULL, inc, d); if (lane >= d) inc += u; }
+    cs[warp][b + lane + 1] = carry + inc;
+    carry += __shfl_sync(FULL, inc, 31);
+  }
+  __syncwarp();
+  for (int k = 0; k < 2; k++) {
+    const int w = k ? 16 : 8;
+    long long best = -1; int besti = 0;
+    for (int s = lane; s <= 256 - w; s += 32) {
+      long long v = cs[warp][s + w] - cs[warp][s];
+      if (v > best) { best = v; besti = s; }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      long long ob = __shfl_xor_sync(FULL, best, d); int oi = __shfl_xor_sync(FULL, besti, d);
+      if (ob > best || (ob == best && oi < besti)) { best = ob; besti = oi; }
+    }
+    if (lane == 0) (k ? base4 : base3)[row] = (uint8_t)besti;
+  }
+}
+
+}  // namespace gaac
+
+using namespace gaac;
+
+extern "C" int gaac_encode_tiles(const void* x_bf16, int64_t H, int64_t S, int64_t S_in, int64_t S_pad,
+                                 const uint8_t* base3, const uint8_t* base4, const int32_t* bidx, int n_kv, int kind,
+                                 uint8_t* sm, uint8_t* codes, int32_t* flags, uint8_t* slots, int32_t* tile_bytes, void* stream) {
+  if (!x_bf16 || !base3 || !base4 || !sm || !codes || !flags || !slots || !tile_bytes) return GAAC_E_ARG;
+  if (H <= 0 || S <= 0 || S_in < S || S_pad < (S + T - 1) / T * T || S_pad % T || n_kv <= 0 || H > 65535 || (kind != GAAC_KIND_K && kind != GAAC_KIND_V)) return GAAC_E_ARG;
+  if (!aligned16(x_bf16) || !aligned16(sm) || !aligned16(codes)) return GAAC_E_ALIGN;
+  const int ntiles = (int)((S + T - 1) / T);
+  dim3 grid((ntiles + ENC_WARPS * ENC_TILES_PER_WARP - 1) / (ENC_WARPS * ENC_TILES_PER_WARP), (unsigned)H);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (kind == GAAC_KIND_K)
+    encode_tiles_kernel<0><<<grid, ENC_WARPS * 32, 0, st>>>((const uint16_t*)x_bf16, S, S_in, S_pad, base3, base4, bidx, n_kv, sm, codes, flags, slots, tile_bytes, ntiles);
+  else
+    encode_tiles_kernel<1><<<grid, ENC_WARPS * 32, 0, st>>>((const uint16_t*)x_bf16, S, S_in, S_pad, base3, base4, bidx, n_kv, sm, codes, flags, slots, tile_bytes, ntiles);
+  return launch_status();
+}
+
+extern "C" int gaac_compact(const uint8_t* slots, const int32_t* tile_bytes, int64_t H, int64_t ntiles, const int32_t* head_start,
+                            uint8_t* ovf, int32_t* tile_off, int64_t tile_off_stride, int32_t* head_bytes, void* stream) {
+  if (!tile_bytes || !tile_off || H <= 0 || ntiles <= 0 || tile_off_stride < ntiles) return GAAC_E_ARG;
+  if (head_start && (!ovf || !slots)) return GAAC_E_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  tile_scan_kernel<<<(unsigned)H, 256, 0, st>>>(tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_bytes);
+  if (head_start) {
+    const long n_items = H * ntiles;
+    compact_copy_kernel<<<(unsigned)((n_items + 3) / 4), 128, 0, st>>>(slots, tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_start, ovf, n_items);
+  }
+  return launch_status();
+}
+
+extern "C" int gaac_decode_page(const uint8_t* sm, const uint8_t* codes, const int32_t* flags, const int32_t* tile_off, int64_t tile_off_stride,
+                                const uint8_t* ovf, const int32_t* head_start, const uint8_t* base3, const uint8_t* base4, const int32_t* bidx,
+                                int n_kv, int kind, int64_t H, int64_t S, int64_t S_pad, void* out_bf16, void* stream) {
+  if (!sm || !codes || !flags || !tile_off || !ovf || !head_start || !base3 || !base4 || !out_bf16) return GAAC_E_ARG;
+  if (H <= 0 || S <= 0 || S_pad < (S + T - 1) / T * T || S_pad % T || n_kv <= 0 || H > 65535 || (kind != GAAC_KIND_K && kind != GAAC_KIND_V)) return GAAC_E_ARG;
+  if (!aligned16(sm) || !aligned16(codes) || !aligned16(out_bf16)) return GAAC_E_ALIGN;
+  const int ntiles = (int)((S + T - 1) / T);
+  dim3 grid((ntiles + ENC_WARPS * ENC_TILES_PER_WARP - 1) / (ENC_WARPS * ENC_TILES_PER_WARP), (unsigned)H);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (kind == GAAC_KIND_K)
+    decode_page_kernel<0><<<grid, ENC_WARPS * 32, 0, st>>>(sm, codes, flags, tile_off, tile_off_stride, ovf, head_start, base3, base4, bidx, n_kv, S, S_pad, (uint16_t*)out_bf16, ntiles);
+  else
+    decode_page_kernel<1><<<grid, ENC_WARPS * 32, 0, st>>>(sm, codes, flags, tile_off, tile_off_stride, ovf, head_start, base3, base4, bidx, n_kv, S, S_pad, (uint16_t*)out_bf16, ntiles);
+  return launch_status();
+}
+
+extern "C" int gaac_exponent_hist(const void* x_bf16, int64_t N, int64_t n_ch, long long* hist, void* stream) {
+  if (!x_bf16 || !hist || N <= 0 || n_ch <= 0) return GAAC_E_ARG;
+  cudaFuncSetAttribute(exponent_hist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 256 * 128 * 2);   // per device; cheap
+  dim3 grid((unsigned)((n_ch + 127) / 128), (unsigned)((N + HIST_ROWS - 1) / HIST_ROWS));
+  exponent_hist_kernel<<<grid, 128, 256 * 128 * 2, (cudaStream_t)stream>>>((const uint16_t*)x_bf16, N, n_ch, (unsigned long long*)hist);
+  return launch_status();
+}
+
+extern "C" int gaac_bases_from_hist(const long long* hist, int64_t n_rows, uint8_t* base3, uint8_t* base4, void* stream) {
+  if (!hist || !base3 || !base4 || n_rows <= 0) return GAAC_E_ARG;
+  bases_from_hist_kernel<<<(unsigned)((n_rows + 3) / 4), 128, 0, (cudaStream_t)stream>>>(hist, n_rows, base3, base4);
+  return launch_status();
+}

@@ -1,0 +1,118 @@
+"""Fused decode attention over the compressed KV (head_dim 128, GQA group size 1..8) on the B200 CUDA library.
+
+Mirror of gaac/kernel.py: `attention(q, kp, vp, scale, nsplit)` over two Pages, `choose_nsplit`, and `_ext()` whose
+`gaac_attn_launch` keeps the argument list of the reference launcher (gaac/kernel.py:296-300) so callers written against the
+reference (its slot cache) work unchanged.  One kernel launch does split-K flash decoding over compressed tiles, the raw BF16
+tail and the merge of the splits.
+"""
+from __future__ import annotations
+import torch
+from . import _lib
+
+_WS = {}        # (device index, stream) -> workspace tensor; the kernel leaves its counters zeroed, so the buffer is reusable
+SM_COUNT_B200 = 148
+ATT_WARPS = 8   # warps per CTA of the CUDA kernel
+
+
+def workspace(dev, B: int, n_q: int, nsplit: int) -> torch.Tensor:
+    need = _lib.lib().gaac_attn_workspace_bytes(B, n_q, nsplit)
+    key = (torch.device(dev).index, torch.cuda.current_stream(dev).cuda_stream)
+    ws = _WS.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+        _WS[key] = ws
+    return ws
+
+
+def choose_nsplit(B: int, n_kv: int, S: int, target_ctas: int = 96, min_tok: int = 512, cap: int = 48) -> int:
+    """Splits per (row, kv head), the reference's heuristic verbatim (gaac/kernel.py:340-342; tuned for a 48-SM GB10)."""
+    return min(max(1, target_ctas // (B * n_kv)), max(1, S // min_tok), cap)
+
+
+def choose_nsplit_sm100(B: int, n_kv: int, S: int, sm_count: int = SM_COUNT_B200, ctas_per_sm: int = 2, min_tiles_per_warp: int = 2) -> int:
+    """Splits per (row, kv head) for a B200: fill sm_count * ctas_per_sm CTAs, but keep at least min_tiles_per_warp
+    16-token tiles for each of the CTA's warps so the per-CTA prologue and merge stay amortised."""
+    rows = max(1, B * n_kv)
+    ntiles = max(1, (S + 15) // 16)
+    want = -(-(sm_count * ctas_per_sm) // rows)
+    most = max(1, ntiles // (ATT_WARPS * min_tiles_per_warp))
+    return max(1, min(want, most))
+
+
+def _side(sm, codes, flags, tile_off, ovf, head_start, base3, base4, tail) -> _lib.Side:
+    return _lib.Side(sm.data_ptr(), codes.data_ptr(), flags.data_ptr(), tile_off.data_ptr(), ovf.data_ptr(), head_start.data_ptr(),
+                     ovf.numel(), base3.data_ptr(), base4.data_ptr(), _lib.ptr(tail))
+
+
+class _Ext:
+    """Stand-in for the reference's JIT-built extension module."""
+
+    @staticmethod
+    def gaac_attn_launch(smk, ck, fk, tok, ovk, ohsk, b3k, b4k, smv, cv, fv, tov, ovv, ohsv, b3v, b4v,
+                         q, slot, n_q, n_kv, SL, S_pad, scale, nsplit, kt, vt, TL, TCAP, out_f32=None, partial=None):
+        """Same positional arguments as the reference launcher (gaac/kernel.py:296-300): 16 K/V buffers, q [B*n_q, 128] bf16,
+        slot int32 [B], n_q, n_kv, SL int32 [heads], S_pad, scale, nsplit, K/V tails [heads, TCAP, 128] bf16 (empty = none),
+        TL int32 [heads], TCAP.  Returns out [B*n_q, 128] bf16.  Extras: out_f32 (fp32 tensor to receive the un-rounded
+        result), partial ([B*n_q, 130] fp32 tensor: write (m, l, acc) there instead of the output)."""
+        D = 128
+        if q.size(-1) != D:
+            raise RuntimeError("head_dim must be 128")
+        G = n_q // max(1, n_kv)
+        if not (1 <= G <= 8 and G * n_kv == n_q):
+            raise RuntimeError("GQA group size must be 1..8")
+        if not q.is_cuda:
+            raise RuntimeError("gaac_b200 attention needs CUDA tensors: there is no CPU path")
+        dev = q.device
+        B = slot.size(0)
+        has_tail = kt.numel() > 0
+        K = _side(smk, ck, fk, tok, ovk, ohsk, b3k, b4k, kt if has_tail else None)
+        V = _side(smv, cv, fv, tov, ovv, ohsv, b3v, b4v, vt if has_tail else None)
+        ws = workspace(dev, B, n_q, nsplit)
+        L = _lib.lib()
+        common = (K, V, q.data_ptr(), slot.data_ptr(), B, n_q, n_kv, SL.data_ptr(), S_pad, float(scale), int(nsplit),
+                  TL.data_ptr() if has_tail else None, int(TCAP) if has_tail else 0, b3k.size(0), ws.data_ptr(), ws.numel())
+        if partial is not None:
+            _lib.check(L.gaac_decode_attn_partial(*common, partial.data_ptr(), _lib.stream_ptr(dev)), "gaac_decode_attn_partial")
+            return partial
+        out = torch.empty(B * n_q, D, dtype=q.dtype, device=dev)
+        _lib.check(L.gaac_decode_attn(*common, out.data_ptr(), _lib.ptr(out_f32), _lib.stream_ptr(dev)), "gaac_decode_attn")
+        return out
+
+
+_mod = None
+
+
+def _ext():
+    global _mod
+    if _mod is None:
+        _lib.lib()          # fail now, loudly, when the library has not been built
+        _mod = _Ext()
+    return _mod
+
+
+def attention(q, kp, vp, scale=None, nsplit=None, out_f32=None):
+    """Decode attention over two Pages (kinds 'k' / 'v', H = B*n_kv heads of equal length).
+    q: [B, n_q, D] bf16 (one query token per sequence) -> [B, n_q, D] bf16.  (gaac/kernel.py:345-359)
+    nsplit=None picks the B200 heuristic; an explicit nsplit is honoured as given."""
+    B, n_q, Dq = q.shape
+    n_kv = kp.H // B
+    dev = q.device
+    if nsplit is None: nsplit = choose_nsplit_sm100(B, n_kv, kp.S)
+    slots = torch.arange(B, dtype=torch.int32, device=dev)
+    SL = torch.full((kp.H,), kp.S, dtype=torch.int32, device=dev)
+    e = torch.empty(0, dtype=torch.int32, device=dev); eq = torch.empty(0, dtype=q.dtype, device=dev)
+    out = _ext().gaac_attn_launch(kp.sm, kp.codes, kp.flags, kp.tile_off, kp.ovf, kp.ovf_head_start, kp.base3, kp.base4,
+                                  vp.sm, vp.codes, vp.flags, vp.tile_off, vp.ovf, vp.ovf_head_start, vp.base3, vp.base4,
+                                  q.reshape(B * n_q, Dq).contiguous(), slots, n_q, n_kv, SL, kp.sm.shape[1] // 128,
+                                  scale if scale is not None else Dq ** -0.5, nsplit, eq, eq, e, 0, out_f32=out_f32)
+    return out.view(B, n_q, Dq)
+
+
+def combine(pm: torch.Tensor, pl: torch.Tensor, pa: torch.Tensor, out_f32: torch.Tensor | None = None) -> torch.Tensor:
+    """Merge partials pm, pl [n_heads, n_parts] and pa [n_heads, n_parts, 128] (fp32, m in natural-log units) -> [n_heads, 128] bf16
+    (gaac/kernel.py:281-294)."""
+    n_heads, n_parts = pm.shape
+    out = torch.empty(n_heads, 128, dtype=torch.bfloat16, device=pm.device)
+    _lib.check(_lib.lib().gaac_combine(pm.contiguous().data_ptr(), pl.contiguous().data_ptr(), pa.contiguous().data_ptr(), n_heads, n_parts,
+                                       out.data_ptr(), _lib.ptr(out_f32), _lib.stream_ptr(pm.device)), "gaac_combine")
+    return out

@@ -1,0 +1,163 @@
+/* gaac_b200 — C ABI of the B200 (sm_100a) implementation of the GAAC KV-codec and compressed-KV decode attention.
+ *
+ * Plain pointers and sizes only; every pointer is a DEVICE pointer unless its name ends in _host.  The library
+ * allocates nothing: outputs and workspaces are caller-provided.  Every call enqueues work on `stream` (a cudaStream_t
+ * passed as void*) and returns without synchronising, so a decode step stays CUDA-graph capturable.  Return value:
+ * 0 on success, otherwise a GAAC_E_* code (see gaac_status_string); nothing is launched when an argument check fails.
+ *
+ * Each entry point names the interface of the reference implementation (Intelligent-Microsystems-Lab/GAAC) that it
+ * replaces, as file:line of that project.
+ */
+#ifndef GAAC_B200_H
+#define GAAC_B200_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  GAAC_OK = 0,
+  GAAC_E_ARG = 1,          /* null pointer, non-positive size, inconsistent sizes */
+  GAAC_E_UNSUPPORTED = 2,  /* GQA group outside 1..8, head_dim != 128, tile stride not a multiple of 16 */
+  GAAC_E_ALIGN = 3,        /* a buffer that must be 16-byte aligned is not */
+  GAAC_E_LAUNCH = 4,       /* the CUDA runtime refused the launch (cudaGetLastError) */
+  GAAC_E_WORKSPACE = 5     /* workspace too small */
+};
+#define GAAC_KIND_K 0
+#define GAAC_KIND_V 1
+#define GAAC_TILE_MAX_ESC 1280   /* worst-case escape bytes of a 16-token tile; stride of the encoder's scratch slots */
+
+const char* gaac_status_string(int status);
+/* ABI version of this header (bumped on any signature change). */
+int gaac_abi_version(void);
+
+/* ---------------------------------------------------------------------------------------------- block encoder */
+
+/* Encode tiles 0..ceil(S/16)-1 of x [H, S_in, 128] bf16 into sm / codes / flags with a per-head token stride of S_pad;
+ * the escape bytes of tile (h, t) go to slots + (h*ntiles + t)*GAAC_TILE_MAX_ESC and their count to tile_bytes[h*ntiles+t].
+ * Head h uses base row bidx[h] when bidx != NULL, else h % n_kv.  Rows >= S of the last tile are stored as empty rows.
+ * Replaces TileEncoder.encode_tiles / the Triton kernel _encode_tile (gaac/encoder.py:16-66, 94-102). */
+int gaac_encode_tiles(const void* x_bf16, int64_t H, int64_t S, int64_t S_in, int64_t S_pad,
+                      const uint8_t* base3, const uint8_t* base4, const int32_t* bidx, int n_kv, int kind,
+                      uint8_t* sm, uint8_t* codes, int32_t* flags, uint8_t* slots, int32_t* tile_bytes, void* stream);
+
+/* tile_off[h, t] = exclusive prefix of tile_bytes[h, :] (row stride tile_off_stride), head_bytes[h] = its sum (may be
+ * NULL), then copy every scratch slot to ovf + head_start[h] + tile_off[h, t].  When head_start is NULL only the prefix
+ * sums are produced (first pass, used to size ovf).  Replaces TileEncoder.compact / _compact and the cumsum between
+ * them (gaac/encoder.py:69-76, 104-109). */
+int gaac_compact(const uint8_t* slots, const int32_t* tile_bytes, int64_t H, int64_t ntiles,
+                 const int32_t* head_start, uint8_t* ovf, int32_t* tile_off, int64_t tile_off_stride, int32_t* head_bytes, void* stream);
+
+/* Bit-exact reconstruction of H heads x S tokens into out [H, S, 128] bf16.  ovf_off is not needed: row positions are
+ * recomputed from the tag words.  Replaces Codec.decode (gaac/codec.py:186-218). */
+int gaac_decode_page(const uint8_t* sm, const uint8_t* codes, const int32_t* flags, const int32_t* tile_off, int64_t tile_off_stride,
+                     const uint8_t* ovf, const int32_t* head_start, const uint8_t* base3, const uint8_t* base4, const int32_t* bidx,
+                     int n_kv, int kind, int64_t H, int64_t S, int64_t S_pad, void* out_bf16, void* stream);
+
+/* hist[(c*256) + e] += number of rows of x [N, n_ch] bf16 whose channel c has exponent byte e (int64 counters, not
+ * cleared here).  Replaces exponent_hist (gaac/codec.py:80-84). */
+int gaac_exponent_hist(const void* x_bf16, int64_t N, int64_t n_ch, long long* hist, void* stream);
+
+/* base3 / base4 [n_rows] = start of the densest 8- / 16-wide window of hist [n_rows, 256] (first maximum wins).
+ * Replaces bases_from_hist (gaac/codec.py:70-77). */
+int gaac_bases_from_hist(const long long* hist, int64_t n_rows, uint8_t* base3, uint8_t* base4, void* stream);
+
+/* ---------------------------------------------------------------------------------------------- decode attention, slot layout */
+
+/* One side (K or V) of a compressed cache in the slot layout (gaac/kv_cache.py:99-119; Page, gaac/codec.py:87-102). */
+typedef struct {
+  const uint8_t* sm;          /* [heads, S_pad*128] */
+  const uint8_t* codes;       /* [heads, S_pad*48]  */
+  const int32_t* flags;       /* [heads, S_pad]     */
+  const int32_t* tile_off;    /* [heads, S_pad/16]  */
+  const uint8_t* ovf;         /* escape stream */
+  const int32_t* head_start;  /* [heads] offset of each head's escapes in ovf */
+  int64_t ovf_bytes;          /* size of the ovf allocation (reads never go past it) */
+  const uint8_t* base3;       /* [n_base_rows, 128] */
+  const uint8_t* base4;
+  const void* tail;           /* [heads, tail_cap, 128] bf16 raw tail, or NULL */
+} gaac_side;
+
+/* Bytes of workspace gaac_decode_attn / gaac_paged_decode_attn need for (B, n_q, nsplit). */
+size_t gaac_attn_workspace_bytes(int B, int n_q, int nsplit);
+
+/* Fused decode attention over compressed K/V.  q [B, n_q, 128] bf16; batch row b reads cache head slot[b]*n_kv + kvh
+ * (slot[b] < 0: padded row, output exactly 0); seq_len[cache head] compressed tokens; tail_len[cache head] raw tail tokens
+ * (NULL when there is no tail).  nsplit >= 1 context splits per (row, kv head).  out [B, n_q, 128] bf16; when out_f32 is
+ * non-NULL the un-rounded fp32 result is written there as well.  workspace: gaac_attn_workspace_bytes bytes, its first
+ * 4*B*n_kv bytes must be zero on the first use and are left zero by every call.  n_base_rows: rows of the base tables
+ * (cache head h uses row h % n_base_rows).  Replaces gaac_attn_launch = gaac_attn<G> + gaac_tail<G> + gaac_combine<128>
+ * (gaac/kernel.py:48-326). */
+int gaac_decode_attn(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
+                     const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
+                     int n_base_rows, void* workspace, size_t workspace_bytes, void* out_bf16, float* out_f32, void* stream);
+
+/* Merge n_parts partial results per query head: pm, pl [n_heads, n_parts], pa [n_heads, n_parts, 128] fp32 ->
+ * out [n_heads, 128] bf16 (and fp32 when out_f32 != NULL).  M = max m; L = sum l*exp(m-M); O = sum acc*exp(m-M)/L, 0 when
+ * L <= 0; parts with m = -inf are skipped.  Replaces gaac_combine<128> (gaac/kernel.py:281-294); also the merge step of
+ * the cross-GPU context split. */
+int gaac_combine(const float* pm, const float* pl, const float* pa, int64_t n_heads, int n_parts, void* out_bf16, float* out_f32, void* stream);
+
+/* As gaac_decode_attn, but stops after the per-(row, query head) merge of this GPU's splits and writes the un-normalised
+ * partial (m, l, acc[128]) of every query head to part [B*n_q, 130] fp32 instead of the output (context split across
+ * GPUs: the parts of all ranks are gathered and merged with gaac_combine).  No counterpart in the reference, which is
+ * single-GPU; the partial has the layout of one split of gaac_attn<G> (gaac/kernel.py:206-216). */
+int gaac_decode_attn_partial(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
+                             const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
+                             int n_base_rows, void* workspace, size_t workspace_bytes, float* part, void* stream);
+
+/* ---------------------------------------------------------------------------------------------- slot cache (layout A) append */
+
+/* Mutable side of the slot cache (gaac/kv_cache.py:99-119). */
+typedef struct {
+  uint8_t* sm; uint8_t* codes; int32_t* flags; int32_t* tile_off; uint8_t* ovf; int32_t* ovf_used; void* tail;
+  const uint8_t* base3; const uint8_t* base4;
+} gaac_store;
+
+/* One new token per batch row: k_new/v_new [B, n_kv, 128] bf16, row b goes to cache head slot[b]*n_kv + kvh (slot < 0:
+ * skipped).  Writes the token into the head's 16-token tail; when the tail fills, encodes it as tile seq_len/16, appends
+ * its escapes at ovf + h*ovf_cap + ovf_used[h], sets tile_off and advances ovf_used; finally advances tail_len / seq_len.
+ * Replaces _append_kv + _advance (gaac/kv_cache.py:22-96, 172-181). */
+int gaac_append_kv(const gaac_store* K, const gaac_store* V, const void* k_new, const void* v_new, const int32_t* slot, int B, int n_kv,
+                   int32_t* tail_len, int32_t* seq_len, int64_t S_cap, int64_t ovf_cap, int n_base_rows, void* stream);
+
+/* ---------------------------------------------------------------------------------------------- paged layout (layout B) */
+
+/* Paged store state of one layer (gaac/vllm/store.py:177-203).  Tile slot p = block*(2*n_kv) + 2*kvh + kind lives at
+ * buf + p*TS: [0,2048) sign/mantissa, [2048,2816) codes, [2816,2880) 16 tag words, [2880,TS) escapes.
+ * mt[p] == p: compressed in its slot; mt[p] == ~r: raw bf16 tile r of `raw` [raw_tiles,16,128]. */
+typedef struct {
+  uint8_t* buf; void* raw; int32_t* mt; int32_t* stack; int32_t* top; int32_t* err;
+  const uint8_t* b3k; const uint8_t* b4k; const uint8_t* b3v; const uint8_t* b4v;
+  int n_kv; int TS; int ovf_slot;
+} gaac_paged;
+
+/* Store this step's new rows.  key/value: [num_tokens, n_kv, 128] bf16 with row strides k_stride/v_stride (elements);
+ * ent [E,4] = (block, first row in key/value, offset in block, rows); block < 0: inactive entry.  freeq [E*2*n_kv] scratch.
+ * Filling blocks go to a raw tile (popped from the free stack on first touch); a block completed by this step is
+ * compressed into its slot when its escapes fit ovf_slot (its raw tile is queued in freeq and pushed back), else kept
+ * raw.  A failed pop increments *err.  Replaces _store_tiles + _free_tiles (gaac/vllm/store.py:22-114, 204-213). */
+int gaac_paged_store(const gaac_paged* st, const void* key, const void* value, int64_t k_stride, int64_t v_stride,
+                     const int32_t* ent, int E, int32_t* freeq, void* stream);
+
+/* Give the raw tiles of freed blocks back and reset their mode-table entries.  Replaces _release_blocks
+ * (gaac/vllm/store.py:166-174). */
+int gaac_paged_release(const gaac_paged* st, const int32_t* blocks, int F, void* stream);
+
+/* Expand blocks to bf16 rows of flat scratch tensors sk/sv [rows, n_kv, 128] (row stride in elements); pairs [P,3] =
+ * (block, first scratch row, valid rows).  Replaces _decode_tiles (gaac/vllm/store.py:117-163). */
+int gaac_paged_decode_blocks(const gaac_paged* st, const int32_t* pairs, int P, void* sk, void* sv, int64_t row_stride, void* stream);
+
+/* Fused decode attention over the paged buffer: q [B, n_q, 128] bf16, out [B, n_q*128] bf16, bt [B, bt_stride] block
+ * table, seq_lens [B] tokens per sequence (including the filling block).  Replaces gaac_vpaged_launch = gaac_vpaged<G> +
+ * gaac_combine2<128> (gaac/vllm/paged_kernel.py:42-276). */
+int gaac_paged_decode_attn(const gaac_paged* st, const int32_t* bt, int64_t bt_stride, const int32_t* seq_lens, const void* q_bf16,
+                           int B, int n_q, float scale, int nsplit, void* workspace, size_t workspace_bytes,
+                           void* out_bf16, float* out_f32, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GAAC_B200_H */

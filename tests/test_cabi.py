@@ -1,0 +1,71 @@
+"""The C-ABI library: it loads, exports every symbol the header declares, and rejects bad arguments without touching a GPU."""
+import ctypes, os, re
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from gaac_b200 import build, _lib
+    build.build()
+    return _lib.lib()
+
+
+def test_header_symbols_are_exported(lib):
+    hdr = open(os.path.join(ROOT, "include", "gaac_b200.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    names = sorted(set(re.findall(r"\b(gaac_[a-z0-9_]+)\s*\(", hdr)))
+    assert len(names) >= 16
+    for n in names:
+        assert hasattr(lib, n), n
+
+
+def test_status_strings(lib):
+    assert lib.gaac_status_string(0) == b"ok"
+    for s in range(1, 6):
+        assert len(lib.gaac_status_string(s)) > 4
+    assert lib.gaac_abi_version() >= 1
+
+
+def test_bad_arguments_are_rejected_before_any_launch(lib):
+    from gaac_b200 import _lib
+    z = ctypes.c_void_p(0)
+    assert lib.gaac_encode_tiles(z, 1, 16, 16, 16, z, z, z, 1, 0, z, z, z, z, z, z) == 1
+    assert lib.gaac_compact(z, z, 1, 1, z, z, z, 1, z, z) == 1
+    assert lib.gaac_decode_page(z, z, z, z, 1, z, z, z, z, z, 1, 0, 1, 16, 16, z, z) == 1
+    assert lib.gaac_exponent_hist(z, 1, 128, z, z) == 1
+    assert lib.gaac_combine(z, z, z, 1, 1, z, z, z) == 1
+    assert lib.gaac_attn_workspace_bytes(0, 32, 4) == 0
+    assert lib.gaac_attn_workspace_bytes(1, 32, 4) >= 4 * 32 * 4 * 130
+    fake = ctypes.c_void_p(0x1000)      # never dereferenced: the checks below fail first
+    side = _lib.Side(0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 64, 0x1000, 0x1000, None)
+    # GQA group of 9 is unsupported; n_q not a multiple of n_kv too
+    assert lib.gaac_decode_attn(side, side, fake, fake, 1, 9, 1, fake, 16, 0.1, 1, None, 0, 1, fake, 1 << 20, fake, None, None) == 2
+    assert lib.gaac_decode_attn(side, side, fake, fake, 1, 6, 4, fake, 16, 0.1, 1, None, 0, 1, fake, 1 << 20, fake, None, None) == 2
+    # S_pad must be a multiple of 16; workspace must be large enough; sm must be 16-byte aligned
+    assert lib.gaac_decode_attn(side, side, fake, fake, 1, 8, 2, fake, 17, 0.1, 1, None, 0, 1, fake, 1 << 20, fake, None, None) == 1
+    assert lib.gaac_decode_attn(side, side, fake, fake, 1, 8, 2, fake, 16, 0.1, 4, None, 0, 1, fake, 64, fake, None, None) == 5
+    bad = _lib.Side(0x1008, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 64, 0x1000, 0x1000, None)
+    assert lib.gaac_decode_attn(bad, side, fake, fake, 1, 8, 2, fake, 16, 0.1, 1, None, 0, 1, fake, 1 << 20, fake, None, None) == 3
+    pg = _lib.Paged(0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 2, 3000, 120)
+    assert lib.gaac_paged_decode_attn(pg, fake, 4, fake, fake, 1, 8, 0.1, 1, fake, 1 << 20, fake, None, None) == 2     # TS % 16
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    from gaac_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", "/nonexistent/libgaac_b200.so")
+    with pytest.raises(RuntimeError, match="no fallback"):
+        _lib.lib()
+
+
+def test_cpu_tensors_are_refused():
+    import torch
+    from gaac_b200 import Codec, TileEncoder
+    x = torch.zeros(2, 16, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        TileEncoder("k").encode_tiles(x, None, None, None, None, None, 16, 16, 2)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        from gaac_b200.codec import exponent_hist
+        exponent_hist(x, 2)

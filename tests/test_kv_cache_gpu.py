@@ -1,0 +1,146 @@
+"""Slot cache (layout A) on the GPU: prefill, append, attention with tails and padded rows, CUDA-graph decode step, and byte
+parity with the fixtures produced by the reference.  Cases follow the reference's tests/test_kv_cache.py:32-86."""
+import numpy as np
+import pytest
+from common import golden, sha, to_bf16_cuda, bits
+from oracle import gaac_oracle as O
+
+pytestmark = pytest.mark.gpu
+N_KV, G, SCALE = 4, 4, 128 ** -0.5
+
+
+def _tok(x16):                 # [n_kv, L, D] -> token-major [L, n_kv, D]
+    return np.ascontiguousarray(x16.transpose(1, 0, 2))
+
+
+def _bases(seed):
+    import torch
+    k, v = _tok(O.kv_like(N_KV, 4096, seed)), _tok(O.kv_like(N_KV, 4096, seed + 1))
+    k3, k4 = O.bases_from_hist(O.exponent_hist_fast(k, N_KV), N_KV); v3, v4 = O.bases_from_hist(O.exponent_hist_fast(v, N_KV), N_KV)
+    return {n: torch.from_numpy(a) for n, a in (("k3", k3), ("k4", k4), ("v3", v3), ("v4", v4))}
+
+
+def _check(cache, hist, slots_l, q16):
+    import torch
+    slots = torch.tensor(slots_l, dtype=torch.int32, device="cuda")
+    o32 = torch.empty(len(slots_l), N_KV * G, 128, dtype=torch.float32, device="cuda")
+    out = cache.attention(to_bf16_cuda(q16), slots, SCALE, out_f32=o32)
+    for b, s in enumerate(slots_l):
+        if s < 0:
+            assert out[b].abs().max().item() == 0
+            continue
+        k, v = hist[s]
+        ref = O.attention_ref(q16[b], k, v, SCALE)
+        assert np.abs(o32[b].cpu().numpy() - ref).max() <= 2e-3 * max(1.0, np.abs(ref).max())
+        assert np.abs(out[b].float().cpu().numpy() - ref).max() <= 2e-2 * np.abs(ref).max() + 1e-3
+        dk, dv = cache.decompress(s)
+        assert np.array_equal(bits(dk), k) and np.array_equal(bits(dv), v)
+
+
+@pytest.mark.parametrize("static_bases", [True, False])
+def test_slots_prefill_append(static_bases):
+    from gaac_b200 import CompressedKVCache
+    import torch
+    cache = CompressedKVCache(n_slots=4, n_kv=N_KV, capacity=1024, bases=_bases(10) if static_bases else None)
+    lens = {0: 37, 2: 500, 3: 16}
+    hist = {}
+    for s, L in lens.items():
+        k, v = _tok(O.kv_like(N_KV, L, 20 + s)), _tok(O.kv_like(N_KV, L, 40 + s))
+        cache.prefill(s, to_bf16_cuda(k), to_bf16_cuda(v)); hist[s] = (k, v)
+    rng = np.random.default_rng(0)
+    for step in range(40):
+        slots_l = [3, 0, 2, -1] if step % 3 else [2, 3, -1, 0]
+        slots = torch.tensor(slots_l, dtype=torch.int32, device="cuda")
+        k = O.f32_to_bf16((rng.standard_normal((4, N_KV, 128)) * 0.5).astype(np.float32))
+        v = O.f32_to_bf16((rng.standard_normal((4, N_KV, 128)) * 0.5).astype(np.float32))
+        cache.append(slots, to_bf16_cuda(k), to_bf16_cuda(v))
+        for b, s in enumerate(slots_l):
+            if s >= 0: hist[s] = (np.concatenate([hist[s][0], k[b:b + 1]]), np.concatenate([hist[s][1], v[b:b + 1]]))
+        if step % 16 == 15: cache.check_capacity()
+        if step % 13 == 0 or step == 39:
+            q16 = O.f32_to_bf16((rng.standard_normal((4, N_KV * G, 128)) * 0.1).astype(np.float32))
+            _check(cache, hist, slots_l, q16)
+    st = cache.stats()
+    assert st["tokens"] == sum(h[0].shape[0] for h in hist.values()) and st["ratio"] > 1.0
+    k, v = _tok(O.kv_like(N_KV, 64, 99)), _tok(O.kv_like(N_KV, 64, 98))      # slot reuse
+    cache.prefill(0, to_bf16_cuda(k), to_bf16_cuda(v)); hist[0] = (k, v)
+    _check(cache, hist, [0], O.f32_to_bf16((rng.standard_normal((1, N_KV * G, 128)) * 0.1).astype(np.float32)))
+
+
+@pytest.mark.parametrize("mode", ["static", "perseq"])
+def test_cache_bytes_match_reference_fixture(mode):
+    """Same prefill + 30 appends as the fixture script ran through the reference; every buffer byte-identical."""
+    import torch
+    from gaac_b200 import CompressedKVCache
+    g = golden("slot_cache")
+    bases = {b: torch.from_numpy(g[f"bases_{b}"]) for b in ("k3", "k4", "v3", "v4")} if mode == "static" else None
+    cache = CompressedKVCache(n_slots=2, n_kv=2, capacity=96, bases=bases)
+    cache.prefill(1, to_bf16_cuda(g[f"{mode}_prefill_k"]), to_bf16_cuda(g[f"{mode}_prefill_v"]))
+    slots = torch.tensor([1, -1], dtype=torch.int32, device="cuda")
+    kn, vn = g[f"{mode}_new_k"], g[f"{mode}_new_v"]
+    for step in range(kn.shape[0]):
+        cache.append(slots, to_bf16_cuda(kn[step]), to_bf16_cuda(vn[step]))
+    assert np.array_equal(cache.S.cpu().numpy(), g[f"{mode}_S"]) and np.array_equal(cache.tail_len.cpu().numpy(), g[f"{mode}_tail_len"])
+    for nm, st in (("k", cache.k), ("v", cache.v)):
+        assert st.ovf_cap == int(g[f"{mode}_{nm}_ovf_cap"])
+        for f in ("sm", "codes", "flags", "tile_off", "ovf", "ovf_used", "base3", "base4"):
+            assert sha(getattr(st, f).cpu().numpy()) == str(g[f"{mode}_{nm}_{f}_sha"]), (nm, f)
+        tl = int(cache.tail_len[2])
+        assert np.array_equal(bits(st.tail)[:, :tl], g[f"{mode}_{nm}_tail"][:, :tl])
+    s = cache.stats()
+    assert [s["tokens"], s["bytes_used"], s["bf16_bytes"]] == g[f"{mode}_stats"].tolist()
+    assert [CompressedKVCache.bytes_per_slot(2, 96), CompressedKVCache.bytes_per_slot(8, 1000, 64, False)] == g["bytes_per_slot"].tolist()
+
+
+def test_cuda_graph_decode_step():
+    """append + attention captured in one CUDA graph, 20 replays (tests/test_kv_cache.py:59-86)."""
+    import torch
+    from gaac_b200 import CompressedKVCache
+    cache = CompressedKVCache(n_slots=2, n_kv=N_KV, capacity=512, bases=_bases(11))
+    k0, v0 = _tok(O.kv_like(N_KV, 200, 5)), _tok(O.kv_like(N_KV, 200, 6))
+    cache.prefill(1, to_bf16_cuda(k0), to_bf16_cuda(v0))
+    slots = torch.tensor([1, -1], dtype=torch.int32, device="cuda")
+    q = torch.zeros(2, N_KV * G, 128, dtype=torch.bfloat16, device="cuda")
+    kn = torch.zeros(2, N_KV, 128, dtype=torch.bfloat16, device="cuda"); vn = torch.zeros_like(kn)
+    def step():
+        cache.append(slots, kn, vn); return cache.attention(q, slots, SCALE, max_len=512)
+    s = torch.cuda.Stream(); s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):          # warm up outside capture, on a padded batch
+        slots.fill_(-1); step()
+    torch.cuda.current_stream().wait_stream(s)
+    cache.growable = False
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        out = step()
+    slots.copy_(torch.tensor([1, -1], dtype=torch.int32))
+    hk, hv = k0, v0
+    rng = np.random.default_rng(3)
+    for _ in range(20):
+        k = O.f32_to_bf16((rng.standard_normal((2, N_KV, 128)) * 0.5).astype(np.float32)); v = O.f32_to_bf16((rng.standard_normal((2, N_KV, 128)) * 0.5).astype(np.float32))
+        q16 = O.f32_to_bf16((rng.standard_normal((2, N_KV * G, 128)) * 0.1).astype(np.float32))
+        kn.copy_(to_bf16_cuda(k)); vn.copy_(to_bf16_cuda(v)); q.copy_(to_bf16_cuda(q16))
+        g.replay(); torch.cuda.synchronize()
+        hk, hv = np.concatenate([hk, k[:1]]), np.concatenate([hv, v[:1]])
+        ref = O.attention_ref(q16[0], hk, hv, SCALE)
+        assert np.abs(out[0].float().cpu().numpy() - ref).max() <= 2e-2 * np.abs(ref).max() + 1e-3
+        assert out[1].abs().max().item() == 0
+    dk, dv = cache.decompress(1)
+    assert np.array_equal(bits(dk), hk) and np.array_equal(bits(dv), hv)
+
+
+def test_capacity_and_growth_rules():
+    import torch
+    from gaac_b200 import CompressedKVCache
+    cache = CompressedKVCache(n_slots=1, n_kv=2, capacity=64, bases=None, ovf_bytes_per_tile=16)
+    rng = np.random.default_rng(4)
+    junk = rng.integers(0, 65536, (64, 2, 128)).astype(np.uint16)
+    junk = np.where(((junk >> 7) & 0xFF) == 0xFF, junk & ~np.uint16(0x4000), junk)
+    cache.prefill(0, to_bf16_cuda(junk), to_bf16_cuda(junk))             # forces the escape stream to grow
+    assert cache.k.ovf_cap >= 4 * 1280
+    dk, dv = cache.decompress(0)
+    assert np.array_equal(bits(dk), junk) and np.array_equal(bits(dv), junk)
+    with pytest.raises(AssertionError):
+        cache.prefill(0, to_bf16_cuda(np.zeros((65, 2, 128), np.uint16)), to_bf16_cuda(np.zeros((65, 2, 128), np.uint16)))
+    cache.growable = False
+    with pytest.raises(RuntimeError, match="escape stream"):
+        cache.check_capacity(used=cache.k.ovf_cap)
