@@ -1,0 +1,326 @@
+"""Benchmark of the GAAC hot path on B200: fused decode attention over the compressed KV cache.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
+
+Workload (synthetic, see gaac_b200/synth.py): one decode-attention layer, batch 1, 32 query heads / 8 KV heads (GQA 4),
+head_dim 128, 65536-token context, KV fully encoded into the slot layout with a 0-token tail; softmax scale 1/sqrt(128).
+A step = one layer call.  Steps rotate over several independent KV sets whose total size exceeds the L2 cache, so every
+step streams its compressed bytes from HBM.  With N > 1 GPUs the context is split into N contiguous token ranges, each rank
+attends over its range and the per-rank partials (m, l, acc) are all-gathered over NCCL and merged (strong scaling).
+
+One JSON line on stdout (rank 0).  `value` is microseconds per layer, device-timed, inputs resident in HBM; `e2e` is the same
+call fed from pinned host memory with the result read back to the host every step.
+"""
+from __future__ import annotations
+import argparse, json, os, subprocess, sys, threading, time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_Q, N_KV, HEAD_DIM, CTX = 32, 8, 128, 65536
+N_SETS = 4                       # independent KV sets rotated over ("layers"): 4 x ~193 MB compressed > 126 MB of L2
+SCALE = HEAD_DIM ** -0.5
+WORKLOAD = "decode attention, batch 1, 32 q heads / 8 kv heads (GQA 4), head_dim 128, 65536-token context, slot layout, 0-token tail"
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_attn_kernel launch at this workload, from the ncu capture
+# summarised in profiles/; None until a capture exists.
+NCU_TRAFFIC_BYTES = None
+
+
+def measured_peak_gbs():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True); self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try: self.proc.wait(timeout=5)
+            except Exception: pass
+
+    def summary(self) -> dict:
+        mhz = sorted(int(r[0]) for r in self.rows if r and r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows if len(r) >= 6 for i in range(4) if r[2 + i].lower().startswith("active")})
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(mhz)}
+
+
+def page_bytes(pg) -> int:
+    return pg.nbytes
+
+
+# ------------------------------------------------------------------------------------------------ reference arm (CPU)
+class CpuPath:
+    """The reference's CPU path for this workload - decode the compressed cache (gaac/codec.py:186-218) and run softmax
+    attention on the decoded KV - restated in numpy (oracle/), run on a bounded sample and scaled to the full layer."""
+
+    def __init__(self, sample_heads: int, sample_tokens: int, threads: int):
+        import numpy as np
+        from oracle import gaac_oracle as O
+        self.np, self.O, self.threads, self.heads = np, O, threads, sample_heads
+        self.G = N_Q // N_KV
+        rng = np.random.default_rng(0)
+        k16, v16 = O.synth_kv("k", sample_heads, sample_tokens, 0), O.synth_kv("v", sample_heads, sample_tokens, 0)
+        kb3, kb4 = O.calibrate(k16[:, :2048], sample_heads); vb3, vb4 = O.calibrate(v16[:, :2048], sample_heads)
+        self.q16 = O.f32_to_bf16(rng.standard_normal((sample_heads * self.G, HEAD_DIM)).astype(np.float32))
+        chunk = max(256, (sample_tokens // max(1, threads)) // 16 * 16)
+        self.pages = []
+        for h in range(sample_heads):
+            for t0 in range(0, sample_tokens, chunk):
+                sl = slice(t0, t0 + chunk)
+                self.pages.append((h, O.encode(k16[h:h + 1, sl], kb3[h:h + 1], kb4[h:h + 1], "k", 1), O.encode(v16[h:h + 1, sl], vb3[h:h + 1], vb4[h:h + 1], "v", 1)))
+        self.frac = (sample_heads * sample_tokens) / (N_KV * CTX)
+        self.sample = f"{sample_heads} of {N_KV} kv heads x {sample_tokens} of {CTX} tokens (codec decode + softmax attention), time scaled by {1 / self.frac:.0f}"
+
+    def _work(self, item):
+        np, O = self.np, self.O
+        h, kp, vp = item
+        k = O.bf16_to_f64(O.decode(kp)[0]).astype(np.float32); v = O.bf16_to_f64(O.decode(vp)[0]).astype(np.float32)
+        q = O.bf16_to_f64(self.q16[h * self.G:(h + 1) * self.G]).astype(np.float32)
+        s = (q @ k.T) * SCALE
+        m = s.max(-1)
+        p = np.exp(s - m[:, None])
+        return h, m, p.sum(-1), p @ v
+
+    def step_us_per_layer(self) -> float:
+        from concurrent.futures import ThreadPoolExecutor
+        np, O = self.np, self.O
+        t = time.perf_counter()
+        with ThreadPoolExecutor(self.threads) as ex:
+            parts = list(ex.map(self._work, self.pages))
+        for h in range(self.heads):                   # merge the chunks of each head (same algebra as the split merge)
+            ph = [p for p in parts if p[0] == h]
+            O.combine_partials(np.stack([p[1] for p in ph], -1), np.stack([p[2] for p in ph], -1), np.stack([p[3] for p in ph], -2))
+        return (time.perf_counter() - t) / self.frac * 1e6
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    cpu = CpuPath(1, 16384, threads)
+    t_first = time.perf_counter(); cpu.step_us_per_layer(); t_first = time.perf_counter() - t_first
+    if t_first * (args.steps + args.warmup) > 150.0:          # keep the whole run within a few minutes
+        cpu = CpuPath(1, 4096, threads)
+    for _ in range(args.warmup): cpu.step_us_per_layer()
+    vals = [cpu.step_us_per_layer() for _ in range(args.steps)]
+    us = sum(vals) / len(vals)
+    line = {"impl": "reference", "metric": "decode_attn_us_per_layer_64k_ctx", "value": us, "unit": "us/layer", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "path": "CPU: numpy restatement (oracle/) of the reference codec decode + softmax attention; the reference is a Python/torch package that cannot travel to the GPU box"},
+            "cpu_baseline": {"value": us, "unit": "us/layer", "cores": threads, "kind": "port", "sample": cpu.sample},
+            "e2e": {"value": us, "unit": "us/layer", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------ our arm (GPU)
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from gaac_b200 import Codec, TileEncoder, _lib
+    from gaac_b200.kernel import _ext, choose_nsplit_sm100, combine, workspace
+    from gaac_b200.synth import synth_kv
+    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE {world}: launch with torch.distributed.run"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.lib()
+
+    # ---- this rank's share of the context: contiguous, tile aligned
+    tiles = CTX // 16
+    t_lo, t_hi = tiles * rank // world, tiles * (rank + 1) // world
+    S_loc = (t_hi - t_lo) * 16
+    sets = []
+    for i in range(N_SETS):
+        k = synth_kv("k", N_KV, CTX, seed=100 + i, device=dev); v = synth_kv("v", N_KV, CTX, seed=100 + i, device=dev)
+        ck, cv = Codec(N_KV, dev).calibrate(k[:, :2048]), Codec(N_KV, dev).calibrate(v[:, :2048])
+        kp = TileEncoder("k", dev).encode(ck, k[:, t_lo * 16:t_hi * 16].contiguous()); vp = TileEncoder("v", dev).encode(cv, v[:, t_lo * 16:t_hi * 16].contiguous())
+        sets.append((kp, vp))
+        del k, v
+    comp_bytes = sum(page_bytes(kp) + page_bytes(vp) for kp, vp in sets) / N_SETS
+    algo_bytes = comp_bytes + 2 * N_Q * HEAD_DIM * 2                                   # + q + out (bf16)
+    bf16_bytes = 2 * N_KV * S_loc * HEAD_DIM * 2
+    nsplit = choose_nsplit_sm100(1, N_KV, S_loc)
+    g = torch.Generator(device=dev).manual_seed(7)
+    q = torch.randn(1, N_Q, HEAD_DIM, generator=g, device=dev).to(torch.bfloat16)
+    slots = torch.zeros(1, dtype=torch.int32, device=dev)
+    SL = torch.full((N_KV,), S_loc, dtype=torch.int32, device=dev)
+    e32 = torch.empty(0, dtype=torch.int32, device=dev); ebf = torch.empty(0, dtype=torch.bfloat16, device=dev)
+    part = torch.empty(N_Q, 130, dtype=torch.float32, device=dev)
+    gathered = torch.empty(world, N_Q, 130, dtype=torch.float32, device=dev)
+    ext = _ext()
+
+    def layer(i, qq):
+        kp, vp = sets[i % N_SETS]
+        common = (kp.sm, kp.codes, kp.flags, kp.tile_off, kp.ovf, kp.ovf_head_start, kp.base3, kp.base4,
+                  vp.sm, vp.codes, vp.flags, vp.tile_off, vp.ovf, vp.ovf_head_start, vp.base3, vp.base4,
+                  qq.view(N_Q, HEAD_DIM), slots, N_Q, N_KV, SL, S_loc, SCALE, nsplit, ebf, ebf, e32, 0)
+        if world == 1:
+            return ext.gaac_attn_launch(*common)
+        ext.gaac_attn_launch(*common, partial=part)
+        dist.all_gather_into_tensor(gathered, part)
+        gt = gathered.permute(1, 0, 2)                                                 # [n_q, world, 130]
+        return combine(gt[:, :, 0].contiguous(), gt[:, :, 1].contiguous(), gt[:, :, 2:].contiguous())
+
+    launches_per_step = 1 if world == 1 else 5       # ours: attention (+ combine); the 3 small copies feeding combine are torch's
+
+    def barrier():
+        if world > 1: dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(3, args.warmup)):
+        layer(i, q)
+    barrier()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clk:
+        t0.record()
+        for i in range(args.steps):
+            ev[i][0].record(); layer(i, q); ev[i][1].record()
+        t1.record()
+        barrier()
+        # keep the GPU busy a little longer so the 100 ms sampler sees the loaded clocks
+        tb = time.perf_counter(); i = 0
+        while time.perf_counter() - tb < 1.0:
+            layer(i, q); i += 1
+        torch.cuda.synchronize()
+    total_ms = t0.elapsed_time(t1)
+    kern_ms = sorted(a.elapsed_time(b) for a, b in ev)
+    if world > 1:
+        tt = torch.tensor([total_ms], dtype=torch.float64, device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX); total_ms = float(tt)
+    us_per_layer = total_ms / args.steps * 1e3
+    kern_us = sum(kern_ms) / len(kern_ms) * 1e3                                         # mean event-bracketed call duration
+
+    # ---- end to end: q from pinned host memory, result back on the host, every step
+    q_host = q.cpu().pin_memory(); out_host = torch.empty(1, N_Q, HEAD_DIM, dtype=torch.bfloat16).pin_memory()
+    q_dev = torch.empty_like(q)
+    def e2e_step(i):
+        q_dev.copy_(q_host, non_blocking=True)
+        out = layer(i, q_dev)
+        out_host.copy_(out.view(1, N_Q, HEAD_DIM), non_blocking=True)
+        torch.cuda.synchronize()
+    for i in range(3): e2e_step(i)
+    barrier()
+    tb = time.perf_counter()
+    for i in range(args.steps): e2e_step(i)
+    barrier()
+    e2e_us = (time.perf_counter() - tb) / args.steps * 1e6
+    if world > 1:
+        tt = torch.tensor([e2e_us], dtype=torch.float64, device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX); e2e_us = float(tt)
+
+    extras = {}
+    if rank == 0 and world == 1:
+        extras = side_measurements(torch, dev, sets, q, args)
+    if rank == 0:
+        peak, which = measured_peak_gbs()
+        achieved = algo_bytes / (kern_us * 1e-6) / 1e9
+        line = {"metric": "decode_attn_us_per_layer_64k_ctx", "value": us_per_layer, "unit": "us/layer", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+                "ms_per_step": us_per_layer / 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": WORKLOAD, "l2": f"steps rotate over {N_SETS} KV sets ({comp_bytes * N_SETS / 1e6:.0f} MB compressed per rank) larger than L2",
+                           "nsplit": nsplit, "tokens_per_rank": S_loc, "parallelism": "single GPU" if world == 1 else f"context split x{world}, NCCL all-gather of [32,130] fp32 partials + merge"},
+                "hbm_gbs_compressed": achieved * (kern_us / us_per_layer) if world == 1 else world * algo_bytes / (us_per_layer * 1e-6) / 1e9,
+                "bf16_equiv_gbs": world * bf16_bytes / (us_per_layer * 1e-6) / 1e9,
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES,
+                             "peak_source": which, "algorithmic_bytes_per_launch": algo_bytes, "kernel_us": kern_us, "frac_of_8TBs_nominal": achieved / 8000.0},
+                "e2e": {"value": e2e_us, "unit": "us/layer", "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2},
+                "gpu_launches": launches_per_step * args.steps, "clocks": clk.summary()}
+        line.update(extras)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def side_measurements(torch, dev, sets, q, args) -> dict:
+    """Numbers reported beside the headline (outside its timed region): the CPU baseline on a bounded sample, the encoder's
+    throughput, and a library BF16-KV decode (flash-attn / SDPA) at the same shape for context."""
+    from gaac_b200 import Codec, TileEncoder
+    from gaac_b200.synth import synth_kv
+    out = {}
+    threads = os.cpu_count() or 1
+    cpu = CpuPath(1, 16384, threads)
+    cpu.step_us_per_layer()
+    tb, vals = time.perf_counter(), []
+    while time.perf_counter() - tb < 10.0: vals.append(cpu.step_us_per_layer())
+    out["cpu_baseline"] = {"value": sum(vals) / len(vals), "unit": "us/layer", "cores": threads, "kind": "port", "sample": cpu.sample + f", mean of {len(vals)} runs"}
+    # encoder: 8 x 65536 tokens per kind
+    try:
+        enc = {}
+        for kind in "kv":
+            x = synth_kv(kind, N_KV, CTX, seed=55, device=dev)
+            codec = Codec(N_KV, dev).calibrate(x[:, :2048]); te = TileEncoder(kind, dev)
+            xs = [x, x.clone(), x.clone()]
+            for i in range(3): te.encode(codec, xs[i % 3])
+            torch.cuda.synchronize(); ts = []
+            for i in range(9):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(); pg = te.encode(codec, xs[i % 3]); b.record(); torch.cuda.synchronize(); ts.append(a.elapsed_time(b))
+            ms = sorted(ts)[len(ts) // 2]
+            enc[kind] = {"ms": ms, "blocks_per_s": N_KV * (CTX // 16) / (ms * 1e-3), "gbs_in_plus_out": (x.numel() * 2 + pg.nbytes) / (ms * 1e-3) / 1e9, "ratio": pg.ratio}
+            del x, xs
+        out["encode"] = enc
+    except Exception as e:                                   # side number only
+        out["encode"] = {"error": repr(e)}
+    # library BF16-KV decode at the same shape (context, not our kernel)
+    try:
+        k = torch.randn(N_SETS, 1, CTX, N_KV, HEAD_DIM, device=dev).to(torch.bfloat16); v = torch.randn_like(k)
+        qq = q.view(1, 1, N_Q, HEAD_DIM)
+        try:
+            from flash_attn import flash_attn_with_kvcache
+            f = lambda i: flash_attn_with_kvcache(qq, k[i % N_SETS], v[i % N_SETS], softmax_scale=SCALE, causal=True); name = "flash_attn_with_kvcache"
+            f(0)
+        except Exception:
+            import torch.nn.functional as F
+            f = lambda i: F.scaled_dot_product_attention(qq.transpose(1, 2), k[i % N_SETS].transpose(1, 2), v[i % N_SETS].transpose(1, 2), scale=SCALE, enable_gqa=True); name = "sdpa"
+        for i in range(5): f(i)
+        torch.cuda.synchronize(); ts = []
+        for i in range(40):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); f(i); b.record(); torch.cuda.synchronize(); ts.append(a.elapsed_time(b))
+        out["bf16_kv_decode_library"] = {"name": name, "us": sorted(ts)[len(ts) // 2] * 1e3}
+    except Exception as e:
+        out["bf16_kv_decode_library"] = {"error": repr(e)}
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -98,9 +98,12 @@ def attention(q, kp, vp, scale=None, nsplit=None, out_f32=None):
     n_kv = kp.H // B
     dev = q.device
     if nsplit is None: nsplit = choose_nsplit_sm100(B, n_kv, kp.S)
-    slots = torch.arange(B, dtype=torch.int32, device=dev)
-    SL = torch.full((kp.H,), kp.S, dtype=torch.int32, device=dev)
-    e = torch.empty(0, dtype=torch.int32, device=dev); eq = torch.empty(0, dtype=q.dtype, device=dev)
+    cache = getattr(kp, "_attn_meta", None)          # identity slot map and per-head lengths, built once per Page
+    if cache is None or cache[0].device != dev or cache[0].numel() != B:
+        cache = (torch.arange(B, dtype=torch.int32, device=dev), torch.full((kp.H,), kp.S, dtype=torch.int32, device=dev),
+                 torch.empty(0, dtype=torch.int32, device=dev), torch.empty(0, dtype=q.dtype, device=dev))
+        kp._attn_meta = cache
+    slots, SL, e, eq = cache
     out = _ext().gaac_attn_launch(kp.sm, kp.codes, kp.flags, kp.tile_off, kp.ovf, kp.ovf_head_start, kp.base3, kp.base4,
                                   vp.sm, vp.codes, vp.flags, vp.tile_off, vp.ovf, vp.ovf_head_start, vp.base3, vp.base4,
                                   q.reshape(B * n_q, Dq).contiguous(), slots, n_q, n_kv, SL, kp.sm.shape[1] // 128,

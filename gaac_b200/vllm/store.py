@@ -45,7 +45,8 @@ class LayerState:
         (blk, tok0, off0, n); freeq: int32 [E*2*n_kv] scratch.  (gaac/vllm/store.py:204-213)"""
         E = ent.shape[0]
         if E == 0: return
-        assert key.stride(-1) == 1 and key.stride(1) == D and value.stride(-1) == 1 and value.stride(1) == D
+        assert key.stride(-1) == 1 and value.stride(-1) == 1
+        assert (key.shape[1] == 1 or key.stride(1) == D) and (value.shape[1] == 1 or value.stride(1) == D)
         _lib.check(_lib.lib().gaac_paged_store(self.c_state(buf), key.data_ptr(), value.data_ptr(), key.stride(0), value.stride(0),
                                                ent.data_ptr(), E, freeq.data_ptr(), _lib.stream_ptr(buf.device)), "gaac_paged_store")
 

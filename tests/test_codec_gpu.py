@@ -91,11 +91,12 @@ def test_calibration_kernels_match_oracle():
     b3, b4 = bases_from_hist(h, 6)
     r3, r4 = O.bases_from_hist(href, 6)
     assert np.array_equal(b3.cpu().numpy(), r3) and np.array_equal(b4.cpu().numpy(), r4)
-    flat = torch.zeros(3, 256, dtype=torch.int64, device="cuda")       # ties: the first maximum wins
-    flat[1, 200:] = 7
-    t3, t4 = bases_from_hist(flat, 3)
-    o3, o4 = O.bases_from_hist(flat.cpu().numpy(), 3)
-    assert np.array_equal(t3.cpu().numpy().reshape(-1), o3.reshape(-1)[:3]) and np.array_equal(t4.cpu().numpy().reshape(-1), o4.reshape(-1)[:3])
+    flat = torch.zeros(128, 256, dtype=torch.int64, device="cuda")     # ties: the first maximum wins
+    flat[1, 200:] = 7; flat[2, 37] = 1; flat[3, 255] = 5
+    t3, t4 = bases_from_hist(flat, 1)
+    o3, o4 = O.bases_from_hist(flat.cpu().numpy(), 1)
+    assert np.array_equal(t3.cpu().numpy(), o3) and np.array_equal(t4.cpu().numpy(), o4)
+    assert t3[0, 0] == 0 and t3[0, 1] == 200 and t4[0, 3] == 240
 
 
 def test_base_collector_matches_oracle(tmp_path):

@@ -1,7 +1,7 @@
 """Fused decode attention against the fp64 oracle (cases of the reference's tests/test_kernel.py:6-19 and more)."""
 import numpy as np
 import pytest
-from common import golden, to_bf16_cuda, bits
+from common import golden, to_bf16_cuda, bits, attn_tol
 from oracle import gaac_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -23,7 +23,7 @@ def _check(out, out32, q16, k16, v16, B, n_kv, scale):
         ref = O.attention_ref(q16[b], kb, vb, scale)
         mag = np.abs(ref).max()
         err32 = np.abs(o32[b] - ref).max()
-        assert err32 <= 2e-3 * max(1.0, mag), (b, err32, mag)                     # fp32 result: 2e-3 max-abs (relative when |o| > 1)
+        assert err32 <= attn_tol(ref, vb), (b, err32, mag)                        # fp32 result: 2e-3 max-abs at unit scale
         assert np.array_equal(o16[b], O.f32_to_bf16(o32[b]))                      # the bf16 output is the rounded fp32 result
         err16 = np.abs(O.bf16_to_f64(o16[b]) - ref).max()
         assert err16 <= 2e-2 * mag + 1e-3, (b, err16, mag)                        # the reference's own bound
@@ -58,7 +58,7 @@ def test_attention_matches_reference_fixture(tag):
     o32 = torch.empty(1, n_kv * G, 128, dtype=torch.float32, device="cuda")
     out = attention(to_bf16_cuda(q16[None]), kp, vp, SCALE, out_f32=o32)
     ref = g[f"o_{tag}"]
-    assert np.abs(o32[0].cpu().numpy() - ref).max() <= 2e-3 * max(1.0, np.abs(ref).max())
+    assert np.abs(o32[0].cpu().numpy() - ref).max() <= attn_tol(ref, v16)
     assert np.abs(out[0].float().cpu().numpy() - ref).max() <= 2e-2 * np.abs(ref).max() + 1e-3
 
 
@@ -77,8 +77,7 @@ def test_attention_long_escape_tiles_and_default_scale():
     o32 = torch.empty(1, 8, 128, dtype=torch.float32, device="cuda")
     out = attention(to_bf16_cuda(q16), kp, vp, out_f32=o32)
     ref = O.attention_ref(q16[0], k16.transpose(1, 0, 2), v16.transpose(1, 0, 2), SCALE)
-    mag = np.abs(ref).max()
-    assert np.abs(o32[0].cpu().numpy() - ref).max() <= 2e-3 * max(1.0, mag)
+    assert np.abs(o32[0].cpu().numpy() - ref).max() <= attn_tol(ref, v16)
     assert np.isfinite(out.float().cpu().numpy()).all()
 
 
@@ -122,4 +121,4 @@ def test_partial_mode_equals_full_attention():
     o32 = torch.empty(n_kv * G, 128, dtype=torch.float32, device="cuda")
     combine(allp[:, :, 0].contiguous(), allp[:, :, 1].contiguous(), allp[:, :, 2:].contiguous(), out_f32=o32)
     ref = O.attention_ref(q16[0], k16.transpose(1, 0, 2), v16.transpose(1, 0, 2), SCALE)
-    assert np.abs(o32.cpu().numpy() - ref).max() <= 2e-3 * max(1.0, np.abs(ref).max())
+    assert np.abs(o32.cpu().numpy() - ref).max() <= attn_tol(ref, v16)
