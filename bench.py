@@ -208,7 +208,7 @@ def run_ours(args):
         barrier()
         # keep the GPU busy a little longer so the 100 ms sampler sees the loaded clocks
         tb = time.perf_counter(); i = 0
-        while time.perf_counter() - tb < 1.0:
+        while not args.profile and time.perf_counter() - tb < 1.0:
             layer(i, q); i += 1
         torch.cuda.synchronize()
     total_ms = t0.elapsed_time(t1)
@@ -218,6 +218,10 @@ def run_ours(args):
     us_per_layer = total_ms / args.steps * 1e3
     kern_us = sum(kern_ms) / len(kern_ms) * 1e3                                         # mean event-bracketed call duration
 
+    if args.profile:
+        if rank == 0: print(json.dumps({"profile_run": True, "us_per_layer": us_per_layer, "kernel_us": kern_us, "nsplit": nsplit}), flush=True)
+        if world > 1: dist.destroy_process_group()
+        return
     # ---- end to end: q from pinned host memory, result back on the host, every step
     q_host = q.cpu().pin_memory(); out_host = torch.empty(1, N_Q, HEAD_DIM, dtype=torch.bfloat16).pin_memory()
     q_dev = torch.empty_like(q)
@@ -315,6 +319,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile", action="store_true", help="only the warm-up and the timed steps (no e2e, no side measurements): the command to run under ncu")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

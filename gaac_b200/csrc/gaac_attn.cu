@@ -24,7 +24,9 @@ constexpr int ESC_WIN = 256;                         // escape bytes staged per 
 // stage layout (bytes)
 constexpr int ST_KSM = 0, ST_KCD = 2048, ST_VSM = 2816, ST_VCD = 4864, ST_KFL = 5632, ST_VFL = 5696, ST_KESC = 5760, ST_VESC = ST_KESC + ESC_WIN;
 constexpr int STAGE_BYTES = ST_VESC + ESC_WIN;       // 6272
-constexpr int ATT_SMEM = ATT_WARPS * NSTAGE * STAGE_BYTES;
+// CTA-wide tables in front of the rings: escape-byte table, K base words [j][g], V base words [r][g], a zero word
+constexpr int TB_LUTX = 0, TB_KB = 2048, TB_VB = TB_KB + 256, TB_ZERO = TB_VB + 256, TABLE_BYTES = TB_ZERO + 16;
+constexpr int ATT_SMEM = TABLE_BYTES + ATT_WARPS * NSTAGE * STAGE_BYTES;
 constexpr unsigned FULLM = 0xffffffffu;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 
@@ -50,18 +52,6 @@ __device__ __forceinline__ void cp4(u32 dst, const void* src) { asm volatile("cp
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 __device__ __forceinline__ float fast_exp2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
-
-// Escape bytes of the tile being consumed: a window in shared memory backed by global memory for long tiles.
-struct WinEsc {
-  const uint8_t* win;     // shared-memory window, already advanced to the tile's first escape byte
-  const uint8_t* glob;    // global address of the tile's first escape byte
-  int lim;                // window bytes valid from `win`
-  __device__ __forceinline__ u32 byte(int pos) const { return pos < lim ? win[pos] : glob[pos]; }
-  __device__ __forceinline__ u64 bytes5(int pos) const {
-    const uint8_t* p = (pos + 5 <= lim) ? win + pos : glob + pos;
-    return (u64)p[0] | ((u64)p[1] << 8) | ((u64)p[2] << 16) | ((u64)p[3] << 24) | ((u64)p[4] << 32);
-  }
-};
 
 // Where the pieces of one tile live.
 struct TileRef {
@@ -157,13 +147,21 @@ __device__ __forceinline__ void pv_words(WarpAcc& A, int w, const u32 (&u01)[4],
   mma16816(A.acc[2 * w + 1], a, pb0, pb1);
 }
 
+// Escape bytes of the tile being consumed: the staged window when it holds all of them, else global memory.
+// need = escape bytes of the tile (+8 because a raw payload is read as aligned words).
+__device__ __forceinline__ const uint8_t* esc_source(const uint8_t* stage_win, const uint8_t* glob, int alloc_left, int need) {
+  const int wsh = (int)(reinterpret_cast<uintptr_t>(glob) & 3);
+  return need + 8 <= esc_window_bytes(glob, alloc_left) ? stage_win + wsh : glob;
+}
+
 // Consume one tile: stage = shared-memory stage of the compressed sides, tr = its description, nvalid = valid tokens (1..16).
-__device__ __forceinline__ void process_tile(WarpAcc& A, const uint8_t* stage, const TileRef& tr, int nvalid, int lane,
-                                             const u32 (&qa)[8][2], const u32 (&kb3)[8], const u32 (&kd)[8], const u32 (&vb3)[4], const u32 (&vd)[4],
-                                             float scale_log2) {
+__device__ __forceinline__ void process_tile(WarpAcc& A, const uint8_t* stage, const uint8_t* tables, const TileRef& tr, int nvalid, int lane,
+                                             const u32 (&qa)[8][2], float scale_log2) {
   const int j = lane & 3, r = lane >> 2;
+  const u32x2* lutx = reinterpret_cast<const u32x2*>(tables + TB_LUTX);
+  const uint8_t* zero = tables + TB_ZERO;
   // ---- row offsets of the escape bytes: lanes 0-15 scan the K rows, lanes 16-31 the V rows
-  int rowoff;
+  int rowoff, total;
   u32 flrow;
   {
     const int row = lane & 15;
@@ -174,18 +172,18 @@ __device__ __forceinline__ void process_tile(WarpAcc& A, const uint8_t* stage, c
     int inc = sz;
 #pragma unroll
     for (int d = 1; d < 16; d <<= 1) { int v = __shfl_up_sync(FULLM, inc, d, 16); if (row >= d) inc += v; }
-    rowoff = inc - sz;
+    rowoff = inc - sz; total = inc;
   }
   // ---- scores
   float sc[4] = {0.f, 0.f, 0.f, 0.f};
   if (!tr.rawk) {
-    const int wsh = (int)(reinterpret_cast<uintptr_t>(tr.kesc) & 3);
-    const WinEsc esc{stage + ST_KESC + wsh, tr.kesc, esc_window_bytes(tr.kesc, tr.esc_lim_k)};
-    u32 fl[2]; int pos[2]; uint4 s0[2], s1[2]; u32 cd[2][3];
+    const uint8_t* esc = esc_source(stage + ST_KESC, tr.kesc, tr.esc_lim_k, __shfl_sync(FULLM, total, 15));
+    u32 t8[2]; int pos[2]; uint4 s0[2], s1[2]; u32 cd[2][3];
 #pragma unroll
     for (int o = 0; o < 2; o++) {
-      fl[o] = __shfl_sync(FULLM, flrow, 8 * o + r);
-      pos[o] = __shfl_sync(FULLM, rowoff, 8 * o + r) + esc_prefix(fl[o], 8 * j);
+      const u32 fl = __shfl_sync(FULLM, flrow, 8 * o + r);
+      pos[o] = __shfl_sync(FULLM, rowoff, 8 * o + r) + esc_prefix(fl, 8 * j);
+      t8[o] = fl >> (8 * j);
       s0[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + lane));
       s1[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + 32 + lane));
       const u32* c = reinterpret_cast<const u32*>(stage + ST_KCD + o * 384 + 12 * lane);
@@ -193,12 +191,13 @@ __device__ __forceinline__ void process_tile(WarpAcc& A, const uint8_t* stage, c
     }
 #pragma unroll
     for (int g = 0; g < 4; g++) {
+      const u32x4 bw = *reinterpret_cast<const u32x4*>(tables + TB_KB + 16 * (4 * j + g));
       u32 f[2][4];
 #pragma unroll
       for (int o = 0; o < 2; o++) {
         const u32 smlo = g == 0 ? s0[o].x : g == 1 ? s0[o].z : g == 2 ? s1[o].x : s1[o].z;
         const u32 smhi = g == 0 ? s0[o].y : g == 1 ? s0[o].w : g == 2 ? s1[o].y : s1[o].w;
-        decode_group(smlo, smhi, k_group_codes(cd[o], g), (fl[o] >> (8 * j + 2 * g)) & 3u, pos[o], esc, kb3[2 * g], kb3[2 * g + 1], kd[2 * g], kd[2 * g + 1], f[o]);
+        decode_group_lut(smlo, smhi, k_group_codes(cd[o], g), (t8[o] >> (2 * g)) & 3u, pos[o], esc, zero, lutx, bw, f[o]);
       }
       { const u32 a[4] = {f[0][0], f[1][0], f[0][1], f[1][1]}; mma16816(sc, a, qa[2 * g][0], qa[2 * g][1]); }
       { const u32 a[4] = {f[0][2], f[1][2], f[0][3], f[1][3]}; mma16816(sc, a, qa[2 * g + 1][0], qa[2 * g + 1][1]); }
@@ -219,14 +218,14 @@ __device__ __forceinline__ void process_tile(WarpAcc& A, const uint8_t* stage, c
   softmax_step(A, sc, scale_log2, nvalid, lane, pb0, pb1);
   // ---- PV
   if (!tr.rawv) {
-    const int wsh = (int)(reinterpret_cast<uintptr_t>(tr.vesc) & 3);
-    const WinEsc esc{stage + ST_VESC + wsh, tr.vesc, esc_window_bytes(tr.vesc, tr.esc_lim_v)};
-    u32 fl[4]; int pos[4]; uint4 sm[4]; u32 cd[6];
+    const uint8_t* esc = esc_source(stage + ST_VESC, tr.vesc, tr.esc_lim_v, __shfl_sync(FULLM, total, 31));
+    u32 t4[4]; int pos[4]; uint4 sm[4]; u32 cd[6];
 #pragma unroll
     for (int t = 0; t < 4; t++) {
       const int tok = 2 * j + (t & 1) + 8 * (t >> 1);
-      fl[t] = __shfl_sync(FULLM, flrow, 16 + tok);
-      pos[t] = __shfl_sync(FULLM, rowoff, 16 + tok) + esc_prefix(fl[t], 4 * r);
+      const u32 fl = __shfl_sync(FULLM, flrow, 16 + tok);
+      pos[t] = __shfl_sync(FULLM, rowoff, 16 + tok) + esc_prefix(fl, 4 * r);
+      t4[t] = fl >> (4 * r);
       sm[t] = *reinterpret_cast<const uint4*>(stage + ST_VSM + 16 * (t * 32 + lane));
     }
     {
@@ -236,11 +235,12 @@ __device__ __forceinline__ void process_tile(WarpAcc& A, const uint8_t* stage, c
     }
 #pragma unroll
     for (int g = 0; g < 2; g++) {
+      const u32x4 bw = *reinterpret_cast<const u32x4*>(tables + TB_VB + 16 * (2 * r + g));
       u32 f[4][4];
 #pragma unroll
       for (int t = 0; t < 4; t++) {
         const u32 smlo = g == 0 ? sm[t].x : sm[t].z, smhi = g == 0 ? sm[t].y : sm[t].w;
-        decode_group(smlo, smhi, v_group_codes(cd, t, g), (fl[t] >> (4 * r + 2 * g)) & 3u, pos[t], esc, vb3[2 * g], vb3[2 * g + 1], vd[2 * g], vd[2 * g + 1], f[t]);
+        decode_group_lut(smlo, smhi, v_group_codes(cd, t, g), (t4[t] >> (2 * g)) & 3u, pos[t], esc, zero, lutx, bw, f[t]);
       }
 #pragma unroll
       for (int h = 0; h < 2; h++) {
@@ -284,18 +284,25 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) decode_attn_kernel(const __gri
   const int ntiles = (S + 15) >> 4, chunk = (ntiles + p.nsplit - 1) / p.nsplit;
   const int tlo = min(split * chunk, ntiles), thi = min(tlo + chunk, ntiles);
 
-  // ---- base words and query fragments
-  u32 kb3[8], kd[8], vb3[4], vd[4];
+  // ---- CTA tables: escape-byte table, per-lane-class base words {b3lo, b3hi, b4lo-b3lo, b4hi-b3hi} per group, a zero word
   {
     const int brow = PAGED ? kvh : ch % p.n_base_rows;
     const uint8_t* b3k = (PAGED ? p.b3k : p.K.base3) + brow * D; const uint8_t* b4k = (PAGED ? p.b4k : p.K.base4) + brow * D;
     const uint8_t* b3v = (PAGED ? p.b3v : p.V.base3) + brow * D; const uint8_t* b4v = (PAGED ? p.b4v : p.V.base4) + brow * D;
-    k_base_words(b3k, j, kb3); k_base_words(b4k, j, kd); v_base_words(b3v, r, vb3); v_base_words(b4v, r, vd);
-#pragma unroll
-    for (int i = 0; i < 8; i++) kd[i] -= kb3[i];
-#pragma unroll
-    for (int i = 0; i < 4; i++) vd[i] -= vb3[i];
+    fill_lutx(reinterpret_cast<u32x2*>(smem + TB_LUTX), tid);
+    if (tid < 16) {                                   // K: lane class jj, group gg -> words 2gg, 2gg+1
+      const int jj = tid >> 2, gg = tid & 3; u32 w3[8], w4[8];
+      k_base_words(b3k, jj, w3); k_base_words(b4k, jj, w4);
+      *reinterpret_cast<u32x4*>(smem + TB_KB + 16 * tid) = u32x4{w3[2 * gg], w3[2 * gg + 1], w4[2 * gg] - w3[2 * gg], w4[2 * gg + 1] - w3[2 * gg + 1]};
+    } else if (tid < 32) {                            // V: lane class rr, group gg
+      const int t = tid - 16, rr = t >> 1, gg = t & 1; u32 w3[4], w4[4];
+      v_base_words(b3v, rr, w3); v_base_words(b4v, rr, w4);
+      *reinterpret_cast<u32x4*>(smem + TB_VB + 16 * t) = u32x4{w3[2 * gg], w3[2 * gg + 1], w4[2 * gg] - w3[2 * gg], w4[2 * gg + 1] - w3[2 * gg + 1]};
+    } else if (tid == 32) {
+      *reinterpret_cast<uint4*>(smem + TB_ZERO) = make_uint4(0, 0, 0, 0);
+    }
   }
+  __syncthreads();
   u32 qa[8][2];
   {
     const bool ok = r < G;
@@ -312,7 +319,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) decode_attn_kernel(const __gri
   A.m0 = A.m1 = -CUDART_INF_F; A.l0 = A.l1 = 0.f;
 
   // ---- tile addressing
-  uint8_t* ring = smem + warp * (NSTAGE * STAGE_BYTES);
+  uint8_t* ring = smem + TABLE_BYTES + warp * (NSTAGE * STAGE_BYTES);
   const u32 ring_s = (u32)__cvta_generic_to_shared(ring);
   const long smh = (long)ch * p.S_pad * D, cdh = (long)ch * p.S_pad * CB, rowb = (long)ch * p.S_pad, tileb = (long)ch * (p.S_pad >> 4);
   int ohk = 0, ohv = 0;
@@ -364,7 +371,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) decode_attn_kernel(const __gri
     cp_commit();
     cp_wait<1>();
     __syncwarp();
-    process_tile(A, ring + stg * STAGE_BYTES, cur, min(T, S - tile * T), lane, qa, kb3, kd, vb3, vd, p.scale_log2);
+    process_tile(A, ring + stg * STAGE_BYTES, smem, cur, min(T, S - tile * T), lane, qa, p.scale_log2);
     __syncwarp();
     cur = nxt; stg ^= 1;
   }
@@ -375,14 +382,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) decode_attn_kernel(const __gri
     tr.kraw = reinterpret_cast<const uint16_t*>(p.K.tail) + (long)ch * p.tail_cap * D;
     tr.vraw = reinterpret_cast<const uint16_t*>(p.V.tail) + (long)ch * p.tail_cap * D;
     for (int t0 = 0; t0 < TL; t0 += T) {
-      process_tile(A, ring, tr, min(T, TL - t0), lane, qa, kb3, kd, vb3, vd, p.scale_log2);
+      process_tile(A, ring, smem, tr, min(T, TL - t0), lane, qa, p.scale_log2);
       tr.kraw += T * D; tr.vraw += T * D;
     }
   }
 
   // ---- merge the warps of the CTA (the ring is free now)
   __syncthreads();
-  float* sh_m = reinterpret_cast<float*>(smem);                  // [W][8]
+  float* sh_m = reinterpret_cast<float*>(smem + TABLE_BYTES);    // [W][8]
   float* sh_l = sh_m + ATT_WARPS * 8;                            // [W][8]
   float* sh_acc = sh_l + ATT_WARPS * 8;                          // [W][8][128]
 #pragma unroll

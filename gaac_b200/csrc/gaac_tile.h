@@ -105,6 +105,38 @@ GAAC_HD void decode_group(u32 sm_lo, u32 sm_hi, u32 c24, u32 tag, int& pos, cons
   bf16x4(sm_hi, e1, out[2], out[3]);
 }
 
+// Table-driven variant of decode_group for the fused attention kernel (fewer ALU instructions, no branch for the 4-bit window):
+//   lutx[b] = { spread_bit4(b & 15), spread_bit4(b >> 4) } for every escape byte value b (2 KiB, shared memory);
+//   esc: base of the tile's escape bytes (any address space), zero: address of a zero byte read by groups without an escape byte;
+//   bw = { b3lo, b3hi, dlo, dhi } base words of the group as in decode_group.
+// The raw tier (rare) is a divergent branch that reads its five bytes as two aligned words.
+struct u32x4 { u32 x, y, z, w; };
+struct u32x2 { u32 x, y; };
+GAAC_HD void fill_lutx(u32x2* lutx, int i) { lutx[i].x = spread_bit4((u32)i & 0xFu); lutx[i].y = spread_bit4((u32)i >> 4); }
+GAAC_HD void decode_group_lut(u32 sm_lo, u32 sm_hi, u32 c24, u32 tag, int& pos, const uint8_t* esc, const uint8_t* zero,
+                              const u32x2* lutx, const u32x4& bw, u32 out[4]) {
+  const u32 m1 = tag & 1u;
+  const uint8_t* pe = (tag == 1u) ? esc + pos : zero;
+  const u32x2 x = lutx[*pe];
+  u32 x0 = x.x, x1 = x.y;
+  const u32 blo = bw.x + m1 * bw.z, bhi = bw.y + m1 * bw.w;
+  if (tag & 2u) {                                   // raw exponents: e = code | hi5 << 3 (the base must not contribute)
+    const uint8_t* p = esc + pos;
+    const int sh = 8 * (int)(reinterpret_cast<uintptr_t>(p) & 3);
+    const u32* a = reinterpret_cast<const u32*>(reinterpret_cast<uintptr_t>(p) & ~(uintptr_t)3);
+    const u32 w0 = a[0], w1 = a[1];                                           // five bytes at offset <= 3 never leave two words
+    const u32 lo = funnel_r(w0, w1, sh), hi = w1 >> sh;                       // bytes 0-3 and byte 4 of the group's payload
+    x0 = spread_hi5(lo) - blo;
+    x1 = spread_hi5(funnel_r(lo, hi, 20)) - bhi;
+    pos += 4;
+  }
+  pos += (int)m1;
+  const u32 e0 = spread_codes4(c24) + blo + x0;
+  const u32 e1 = spread_codes4(c24 >> 12) + bhi + x1;
+  bf16x4(sm_lo, e0, out[0], out[1]);
+  bf16x4(sm_hi, e1, out[2], out[3]);
+}
+
 // 24 code bits of group g (0..3) of a K lane (96-bit string in cd[0..2])
 GAAC_HD u32 k_group_codes(const u32 cd[3], int g) {
   switch (g) {

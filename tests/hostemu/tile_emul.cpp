@@ -93,3 +93,49 @@ extern "C" void emu_decode_tile(int kind_v, const uint8_t* sm_in, const uint8_t*
     }
   }
 }
+
+// Same as emu_decode_tile through the table-driven group decoder of the fused attention kernel.
+// esc_in must be 4-byte aligned and readable 8 bytes past its last escape byte.
+extern "C" void emu_decode_tile_lut(int kind_v, const uint8_t* sm_in, const uint8_t* cd_in, const uint32_t* fl_in, const uint8_t* esc_in,
+                                    const uint8_t* b3row, const uint8_t* b4row, uint16_t* out) {
+  static u32x2 lutx[256]; static bool init = false;
+  if (!init) { for (int i = 0; i < 256; i++) fill_lutx(lutx, i); init = true; }
+  static const uint32_t zero_word = 0; const uint8_t* zero = reinterpret_cast<const uint8_t*>(&zero_word);
+  int rowoff[16], acc = 0;
+  for (int row = 0; row < 16; row++) { rowoff[row] = acc; acc += row_esc_bytes(fl_in[row]); }
+  for (int lane = 0; lane < 32; lane++) {
+    int j = lane & 3, r = lane >> 2;
+    if (!kind_v) {
+      u32 b3w[8], b4w[8]; k_base_words(b3row, j, b3w); k_base_words(b4row, j, b4w);
+      for (int o = 0; o < 2; o++) {
+        int row = 8 * o + r; u32 sm[8], cd[3];
+        memcpy(sm, sm_in + o * 1024 + 32 * lane, 32); memcpy(cd, cd_in + o * 384 + 12 * lane, 12);
+        u32 fl = fl_in[row]; int pos = rowoff[row] + esc_prefix(fl, 8 * j);
+        for (int g = 0; g < 4; g++) {
+          u32 o4[4]; u32x4 bw{b3w[2 * g], b3w[2 * g + 1], b4w[2 * g] - b3w[2 * g], b4w[2 * g + 1] - b3w[2 * g + 1]};
+          decode_group_lut(sm[2 * g], sm[2 * g + 1], k_group_codes(cd, g), (fl >> (8 * j + 2 * g)) & 3u, pos, esc_in, zero, lutx, bw, o4);
+          for (int h = 0; h < 2; h++) {
+            int s = 2 * g + h; uint16_t* p = out + row * 128 + 16 * s + 2 * j;
+            p[0] = (uint16_t)o4[2 * h]; p[1] = (uint16_t)(o4[2 * h] >> 16); p[8] = (uint16_t)o4[2 * h + 1]; p[9] = (uint16_t)(o4[2 * h + 1] >> 16);
+          }
+        }
+      }
+    } else {
+      u32 b3w[4], b4w[4]; v_base_words(b3row, r, b3w); v_base_words(b4row, r, b4w);
+      u32 cd[6]; memcpy(cd, cd_in + 24 * lane, 24);
+      for (int t = 0; t < 4; t++) {
+        int row = v_tok(j, t); u32 sm[4]; memcpy(sm, sm_in + 64 * lane + 16 * t, 16);
+        u32 fl = fl_in[row]; int pos = rowoff[row] + esc_prefix(fl, 4 * r);
+        for (int g = 0; g < 2; g++) {
+          u32 o4[4]; u32x4 bw{b3w[2 * g], b3w[2 * g + 1], b4w[2 * g] - b3w[2 * g], b4w[2 * g + 1] - b3w[2 * g + 1]};
+          decode_group_lut(sm[2 * g], sm[2 * g + 1], v_group_codes(cd, t, g), (fl >> (4 * r + 2 * g)) & 3u, pos, esc_in, zero, lutx, bw, o4);
+          for (int h = 0; h < 2; h++) {
+            int w = 2 * g + h; uint16_t* p = out + row * 128 + r;
+            p[8 * (4 * w)] = (uint16_t)o4[2 * h]; p[8 * (4 * w + 1)] = (uint16_t)(o4[2 * h] >> 16);
+            p[8 * (4 * w + 2)] = (uint16_t)o4[2 * h + 1]; p[8 * (4 * w + 3)] = (uint16_t)(o4[2 * h + 1] >> 16);
+          }
+        }
+      }
+    }
+  }
+}

@@ -40,3 +40,10 @@ def test_tile_encode_decode_matches_oracle(emu, trial):
     out = np.zeros((16, 128), np.uint16)
     emu.emu_decode_tile(trial % 2, P(sm), P(cd), P(fl), P(esc), P(b3), P(b4), P(out))
     assert np.array_equal(out[:nvalid], x[0, :nvalid])
+    for shift in (0, 1, 3):                          # the table-driven decoder reads raw payloads as aligned words: try every alignment
+        buf = np.zeros(1288 + 16, np.uint8).view(np.uint8)
+        base = (-buf.ctypes.data) % 4 + shift
+        buf[base:base + 1288] = esc
+        out2 = np.zeros((16, 128), np.uint16)
+        emu.emu_decode_tile_lut(trial % 2, P(sm), P(cd), P(fl), ctypes.c_void_p(buf.ctypes.data + base), P(b3), P(b4), P(out2))
+        assert np.array_equal(out2[:nvalid], x[0, :nvalid]), shift
