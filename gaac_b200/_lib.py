@@ -7,7 +7,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libgaac_b200.so")
+LIB_PATH = os.environ.get("GAAC_B200_LIB") or os.path.join(_HERE, "libgaac_b200.so")     # GAAC_B200_LIB: use a library built elsewhere
 _lib = None
 
 vp, i32, i64, f32, sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t

@@ -17,15 +17,19 @@
 
 namespace gaac {
 
-constexpr int ATT_WARPS = 8;
+constexpr int ATT_WARPS = 16;
 constexpr int ATT_THREADS = ATT_WARPS * 32;
 constexpr int NSTAGE = 2;
 constexpr int ESC_WIN = 256;                         // escape bytes staged per tile and kind; longer tiles read the rest from global
 // stage layout (bytes)
-constexpr int ST_KSM = 0, ST_KCD = 2048, ST_VSM = 2816, ST_VCD = 4864, ST_KFL = 5632, ST_VFL = 5696, ST_KESC = 5760, ST_VESC = ST_KESC + ESC_WIN;
-constexpr int STAGE_BYTES = ST_VESC + ESC_WIN;       // 6272
+// stage layout (bytes); each escape window is preceded by 16 bytes that stay zero: a group without an escape byte reads one of them
+constexpr int ZPAD = 16;
+constexpr int ST_KSM = 0, ST_KCD = 2048, ST_VSM = 2816, ST_VCD = 4864, ST_KFL = 5632, ST_VFL = 5696;
+constexpr int ST_KZ = 5760, ST_KESC = ST_KZ + ZPAD, ST_VZ = ST_KESC + ESC_WIN, ST_VESC = ST_VZ + ZPAD;
+constexpr int STAGE_BYTES = ST_VESC + ESC_WIN;       // 6304
 // CTA-wide tables in front of the rings: escape-byte table, K base words [j][g], V base words [r][g], a zero word
-constexpr int TB_LUTX = 0, TB_KB = 2048, TB_VB = TB_KB + 256, TB_ZERO = TB_VB + 256, TABLE_BYTES = TB_ZERO + 16;
+constexpr int META_TILES = 1024;                     // tiles of a CTA's range whose metadata is staged (longer ranges read the rest from global)
+constexpr int TB_LUTX = 0, TB_KB = 2048, TB_VB = TB_KB + 256, TB_META = TB_VB + 256, TABLE_BYTES = TB_META + 2 * META_TILES * 4;
 constexpr int ATT_SMEM = TABLE_BYTES + ATT_WARPS * NSTAGE * STAGE_BYTES;
 constexpr unsigned FULLM = 0xffffffffu;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
@@ -147,19 +151,146 @@ __device__ __forceinline__ void pv_words(WarpAcc& A, int w, const u32 (&u01)[4],
   mma16816(A.acc[2 * w + 1], a, pb0, pb1);
 }
 
-// Escape bytes of the tile being consumed: the staged window when it holds all of them, else global memory.
-// need = escape bytes of the tile (+8 because a raw payload is read as aligned words).
-__device__ __forceinline__ const uint8_t* esc_source(const uint8_t* stage_win, const uint8_t* glob, int alloc_left, int need) {
-  const int wsh = (int)(reinterpret_cast<uintptr_t>(glob) & 3);
-  return need + 8 <= esc_window_bytes(glob, alloc_left) ? stage_win + wsh : glob;
+// Escape bytes of one tile as read by the group decoder.
+//   staged window (WIN): zp = shared-memory address 16 bytes below the tile's first escape byte; the bytes from zp up to the
+//     window are zero, so a group without an escape byte reads zp[0] and a 4-bit-window group reads zp[16 + pos]: one
+//     multiply-add, no branch.
+//   global memory (!WIN, tiles whose escapes exceed the window): plain loads at glob[pos].
+template <bool WIN> struct EscSrc { const uint8_t* zp; const uint8_t* glob; };
+
+// ---- byte-SWAR pieces written for the pipes of the SM: logic ops (LOP3 / PRMT) run on the ALU pipe, whose rate is half the
+// issue rate, so every shift that can be merged with an add is written as a multiply-add, which runs on the FMA pipe.
+#ifndef GAAC_SWAR_MAD
+#define GAAC_SWAR_MAD 1
+#endif
+template <u32 K> __device__ __forceinline__ u32 mad_k(u32 a, u32 c) {
+  u32 d; asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "n"(K), "r"(c)); return d;
+}
+// four 3-bit codes at bits 0..11 of v (v < 4096) -> one code per byte, plus `addend` (the base word and the escape addend)
+__device__ __forceinline__ u32 spread_codes4_add(u32 v, u32 addend) {
+#if GAAC_SWAR_MAD
+  const u32 y = mad_k<1024u>(v & 0xFC0u, v);                        // bits 0-11: c0..c3, bits 16-21: c2, c3
+  return mad_k<32u>(y & 0x00380038u, (y & 0x00070007u) + addend);   // c1, c3 move up 5 bits into bytes 1 and 3
+#else
+  return spread_codes4(v) + addend;
+#endif
+}
+__device__ __forceinline__ void bf16x4_dev(u32 sm4, u32 e4, u32& p01, u32& p23) {
+#if GAAC_SWAR_MAD
+  const u32 eh = __umulhi(e4, 0x80000000u);                          // e4 >> 1
+  const u32 el = mad_k<128u>(e4, 0u);                                // e4 << 7
+  const u32 h4 = (sm4 & 0x80808080u) | (eh & 0x7F7F7F7Fu);
+  const u32 l4 = (el & 0x80808080u) | (sm4 & 0x7F7F7F7Fu);
+  p01 = prmt(l4, h4, 0x5140); p23 = prmt(l4, h4, 0x7362);
+#else
+  bf16x4(sm4, e4, p01, p23);
+#endif
+}
+
+// Rebuild one group (two sign/mantissa words) into four bf16x2 words.  Same results as decode_group_lut (gaac_tile.h);
+// pos16 = 16 + escape position of the group, advanced past it on return.
+template <bool WIN>
+__device__ __forceinline__ void decode_group_dev(u32 sm_lo, u32 sm_hi, u32 c24, u32 tg, int& pos16, const EscSrc<WIN>& es,
+                                                 const u32x2* lutx, const u32x4& bw, u32 out[4]) {
+  const u32 m1 = tg & 1u;                             // promoted (tags are 0, 1 or 3)
+  u32 xe;
+  if (WIN) xe = es.zp[m1 * (u32)pos16];               // raw groups read a payload byte here; their addends are replaced below
+  else xe = m1 ? es.glob[pos16 - 16] : 0u;
+  const u32x2 x = lutx[xe];
+  u32 x0 = x.x, x1 = x.y;
+  const u32 blo = bw.x + m1 * bw.z, bhi = bw.y + m1 * bw.w;
+  if (tg & 2u) {                                      // raw exponents: e = code | hi5 << 3 (the base must not contribute)
+    const uint8_t* p = WIN ? es.zp + pos16 : es.glob + (pos16 - 16);
+    const int sh = 8 * (int)(reinterpret_cast<uintptr_t>(p) & 3);
+    const u32* a = reinterpret_cast<const u32*>(reinterpret_cast<uintptr_t>(p) & ~(uintptr_t)3);
+    const u32 w0 = a[0], w1 = a[1];
+    const u32 lo = funnel_r(w0, w1, sh), hi = w1 >> sh;
+    x0 = spread_hi5(lo) - blo;
+    x1 = spread_hi5(funnel_r(lo, hi, 20)) - bhi;
+    pos16 += 4;
+  }
+  pos16 += (int)m1;
+  const u32 e0 = spread_codes4_add(c24 & 0xFFFu, blo + x0);
+  const u32 e1 = spread_codes4_add((c24 >> 12) & 0xFFFu, bhi + x1);
+  bf16x4_dev(sm_lo, e0, out[0], out[1]);
+  bf16x4_dev(sm_hi, e1, out[2], out[3]);
+}
+
+// Scores of one compressed K tile: sc += K . Q^T.  flrow / rowoff: tag word and escape offset of row (lane & 15) held by
+// lanes 0-15.
+template <bool WIN>
+__device__ __forceinline__ void k_scores(float* sc, const uint8_t* stage, const uint8_t* tables, const EscSrc<WIN>& es, u32 flrow, int rowoff,
+                                         int lane, const u32 (&qa)[8][2]) {
+  const int j = lane & 3, r = lane >> 2;
+  const u32x2* lutx = reinterpret_cast<const u32x2*>(tables + TB_LUTX);
+  u32 t8[2]; int pos[2]; uint4 s0[2], s1[2]; u32 cd[2][3];
+#pragma unroll
+  for (int o = 0; o < 2; o++) {
+    const u32 fl = __shfl_sync(FULLM, flrow, 8 * o + r);
+    pos[o] = __shfl_sync(FULLM, rowoff, 8 * o + r) + esc_prefix(fl, 8 * j) + 16;
+    t8[o] = fl >> (8 * j);
+    s0[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + lane));
+    s1[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + 32 + lane));
+    const u32* c = reinterpret_cast<const u32*>(stage + ST_KCD + o * 384 + 12 * lane);
+    cd[o][0] = c[0]; cd[o][1] = c[1]; cd[o][2] = c[2];
+  }
+#pragma unroll
+  for (int g = 0; g < 4; g++) {
+    const u32x4 bw = *reinterpret_cast<const u32x4*>(tables + TB_KB + 16 * (4 * j + g));
+    u32 f[2][4];
+#pragma unroll
+    for (int o = 0; o < 2; o++) {
+      const u32 smlo = g == 0 ? s0[o].x : g == 1 ? s0[o].z : g == 2 ? s1[o].x : s1[o].z;
+      const u32 smhi = g == 0 ? s0[o].y : g == 1 ? s0[o].w : g == 2 ? s1[o].y : s1[o].w;
+      decode_group_dev<WIN>(smlo, smhi, k_group_codes(cd[o], g), t8[o] >> (2 * g), pos[o], es, lutx, bw, f[o]);
+    }
+    { const u32 a[4] = {f[0][0], f[1][0], f[0][1], f[1][1]}; mma16816(sc, a, qa[2 * g][0], qa[2 * g][1]); }
+    { const u32 a[4] = {f[0][2], f[1][2], f[0][3], f[1][3]}; mma16816(sc, a, qa[2 * g + 1][0], qa[2 * g + 1][1]); }
+  }
+}
+
+// O^T += V^T . P^T for one compressed V tile.  flrow / rowoff of V row (lane & 15) are held by lanes 16-31.
+template <bool WIN>
+__device__ __forceinline__ void v_accum(WarpAcc& A, const uint8_t* stage, const uint8_t* tables, const EscSrc<WIN>& es, u32 flrow, int rowoff,
+                                        int lane, u32 pb0, u32 pb1) {
+  const int j = lane & 3, r = lane >> 2;
+  const u32x2* lutx = reinterpret_cast<const u32x2*>(tables + TB_LUTX);
+  u32 t4[4]; int pos[4]; uint4 sm[4]; u32 cd[6];
+#pragma unroll
+  for (int t = 0; t < 4; t++) {
+    const int tok = 2 * j + (t & 1) + 8 * (t >> 1);
+    const u32 fl = __shfl_sync(FULLM, flrow, 16 + tok);
+    pos[t] = __shfl_sync(FULLM, rowoff, 16 + tok) + esc_prefix(fl, 4 * r) + 16;
+    t4[t] = fl >> (4 * r);
+    sm[t] = *reinterpret_cast<const uint4*>(stage + ST_VSM + 16 * (t * 32 + lane));
+  }
+  {
+    const uint2* c2 = reinterpret_cast<const uint2*>(stage + ST_VCD + 24 * lane);
+    uint2 ca = c2[0], cb = c2[1], cc = c2[2];
+    cd[0] = ca.x; cd[1] = ca.y; cd[2] = cb.x; cd[3] = cb.y; cd[4] = cc.x; cd[5] = cc.y;
+  }
+#pragma unroll
+  for (int g = 0; g < 2; g++) {
+    const u32x4 bw = *reinterpret_cast<const u32x4*>(tables + TB_VB + 16 * (2 * r + g));
+    u32 f[4][4];
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+      const u32 smlo = g == 0 ? sm[t].x : sm[t].z, smhi = g == 0 ? sm[t].y : sm[t].w;
+      decode_group_dev<WIN>(smlo, smhi, v_group_codes(cd, t, g), t4[t] >> (2 * g), pos[t], es, lutx, bw, f[t]);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const u32 u01[4] = {f[0][2 * h], f[1][2 * h], f[2][2 * h], f[3][2 * h]};
+      const u32 u23[4] = {f[0][2 * h + 1], f[1][2 * h + 1], f[2][2 * h + 1], f[3][2 * h + 1]};
+      pv_words(A, 2 * g + h, u01, u23, pb0, pb1);
+    }
+  }
 }
 
 // Consume one tile: stage = shared-memory stage of the compressed sides, tr = its description, nvalid = valid tokens (1..16).
 __device__ __forceinline__ void process_tile(WarpAcc& A, const uint8_t* stage, const uint8_t* tables, const TileRef& tr, int nvalid, int lane,
                                              const u32 (&qa)[8][2], float scale_log2) {
   const int j = lane & 3, r = lane >> 2;
-  const u32x2* lutx = reinterpret_cast<const u32x2*>(tables + TB_LUTX);
-  const uint8_t* zero = tables + TB_ZERO;
   // ---- row offsets of the escape bytes: lanes 0-15 scan the K rows, lanes 16-31 the V rows
   int rowoff, total;
   u32 flrow;
@@ -177,31 +308,11 @@ __device__ __forceinline__ void process_tile(WarpAcc& A, const uint8_t* stage, c
   // ---- scores
   float sc[4] = {0.f, 0.f, 0.f, 0.f};
   if (!tr.rawk) {
-    const uint8_t* esc = esc_source(stage + ST_KESC, tr.kesc, tr.esc_lim_k, __shfl_sync(FULLM, total, 15));
-    u32 t8[2]; int pos[2]; uint4 s0[2], s1[2]; u32 cd[2][3];
-#pragma unroll
-    for (int o = 0; o < 2; o++) {
-      const u32 fl = __shfl_sync(FULLM, flrow, 8 * o + r);
-      pos[o] = __shfl_sync(FULLM, rowoff, 8 * o + r) + esc_prefix(fl, 8 * j);
-      t8[o] = fl >> (8 * j);
-      s0[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + lane));
-      s1[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + 32 + lane));
-      const u32* c = reinterpret_cast<const u32*>(stage + ST_KCD + o * 384 + 12 * lane);
-      cd[o][0] = c[0]; cd[o][1] = c[1]; cd[o][2] = c[2];
-    }
-#pragma unroll
-    for (int g = 0; g < 4; g++) {
-      const u32x4 bw = *reinterpret_cast<const u32x4*>(tables + TB_KB + 16 * (4 * j + g));
-      u32 f[2][4];
-#pragma unroll
-      for (int o = 0; o < 2; o++) {
-        const u32 smlo = g == 0 ? s0[o].x : g == 1 ? s0[o].z : g == 2 ? s1[o].x : s1[o].z;
-        const u32 smhi = g == 0 ? s0[o].y : g == 1 ? s0[o].w : g == 2 ? s1[o].y : s1[o].w;
-        decode_group_lut(smlo, smhi, k_group_codes(cd[o], g), (t8[o] >> (2 * g)) & 3u, pos[o], esc, zero, lutx, bw, f[o]);
-      }
-      { const u32 a[4] = {f[0][0], f[1][0], f[0][1], f[1][1]}; mma16816(sc, a, qa[2 * g][0], qa[2 * g][1]); }
-      { const u32 a[4] = {f[0][2], f[1][2], f[0][3], f[1][3]}; mma16816(sc, a, qa[2 * g + 1][0], qa[2 * g + 1][1]); }
-    }
+    const int wsh = (int)(reinterpret_cast<uintptr_t>(tr.kesc) & 3);
+    if (__shfl_sync(FULLM, total, 15) + 8 <= esc_window_bytes(tr.kesc, tr.esc_lim_k))        // +8: a raw payload is read as two aligned words
+      k_scores<true>(sc, stage, tables, EscSrc<true>{stage + ST_KESC + wsh - ZPAD, nullptr}, flrow, rowoff, lane, qa);
+    else
+      k_scores<false>(sc, stage, tables, EscSrc<false>{nullptr, tr.kesc}, flrow, rowoff, lane, qa);
   } else {
 #pragma unroll
     for (int s = 0; s < 8; s++) {
@@ -218,37 +329,11 @@ __device__ __forceinline__ void process_tile(WarpAcc& A, const uint8_t* stage, c
   softmax_step(A, sc, scale_log2, nvalid, lane, pb0, pb1);
   // ---- PV
   if (!tr.rawv) {
-    const uint8_t* esc = esc_source(stage + ST_VESC, tr.vesc, tr.esc_lim_v, __shfl_sync(FULLM, total, 31));
-    u32 t4[4]; int pos[4]; uint4 sm[4]; u32 cd[6];
-#pragma unroll
-    for (int t = 0; t < 4; t++) {
-      const int tok = 2 * j + (t & 1) + 8 * (t >> 1);
-      const u32 fl = __shfl_sync(FULLM, flrow, 16 + tok);
-      pos[t] = __shfl_sync(FULLM, rowoff, 16 + tok) + esc_prefix(fl, 4 * r);
-      t4[t] = fl >> (4 * r);
-      sm[t] = *reinterpret_cast<const uint4*>(stage + ST_VSM + 16 * (t * 32 + lane));
-    }
-    {
-      const uint2* c2 = reinterpret_cast<const uint2*>(stage + ST_VCD + 24 * lane);
-      uint2 ca = c2[0], cb = c2[1], cc = c2[2];
-      cd[0] = ca.x; cd[1] = ca.y; cd[2] = cb.x; cd[3] = cb.y; cd[4] = cc.x; cd[5] = cc.y;
-    }
-#pragma unroll
-    for (int g = 0; g < 2; g++) {
-      const u32x4 bw = *reinterpret_cast<const u32x4*>(tables + TB_VB + 16 * (2 * r + g));
-      u32 f[4][4];
-#pragma unroll
-      for (int t = 0; t < 4; t++) {
-        const u32 smlo = g == 0 ? sm[t].x : sm[t].z, smhi = g == 0 ? sm[t].y : sm[t].w;
-        decode_group_lut(smlo, smhi, v_group_codes(cd, t, g), (t4[t] >> (2 * g)) & 3u, pos[t], esc, zero, lutx, bw, f[t]);
-      }
-#pragma unroll
-      for (int h = 0; h < 2; h++) {
-        const u32 u01[4] = {f[0][2 * h], f[1][2 * h], f[2][2 * h], f[3][2 * h]};
-        const u32 u23[4] = {f[0][2 * h + 1], f[1][2 * h + 1], f[2][2 * h + 1], f[3][2 * h + 1]};
-        pv_words(A, 2 * g + h, u01, u23, pb0, pb1);
-      }
-    }
+    const int wsh = (int)(reinterpret_cast<uintptr_t>(tr.vesc) & 3);
+    if (__shfl_sync(FULLM, total, 31) + 8 <= esc_window_bytes(tr.vesc, tr.esc_lim_v))
+      v_accum<true>(A, stage, tables, EscSrc<true>{stage + ST_VESC + wsh - ZPAD, nullptr}, flrow, rowoff, lane, pb0, pb1);
+    else
+      v_accum<false>(A, stage, tables, EscSrc<false>{nullptr, tr.vesc}, flrow, rowoff, lane, pb0, pb1);
   } else {
 #pragma unroll
     for (int w = 0; w < 4; w++) {
@@ -267,12 +352,13 @@ __device__ __forceinline__ void process_tile(WarpAcc& A, const uint8_t* stage, c
 }
 
 template <bool PAGED>
-__global__ void __launch_bounds__(ATT_THREADS, 2) decode_attn_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ int s_next, s_last;
   const int bh = blockIdx.x, split = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, j = lane & 3, r = lane >> 2;
   const int b = bh / p.n_kv, kvh = bh % p.n_kv, G = p.G;
 
-  // ---- which cache head, how many tokens
+  // ---- which cache head, how many tokens, this CTA's tile range [tlo, thi)
   int S, ch = 0, TL = 0;
   if (PAGED) { S = p.seq_len[b]; }
   else {
@@ -283,26 +369,40 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) decode_attn_kernel(const __gri
   }
   const int ntiles = (S + 15) >> 4, chunk = (ntiles + p.nsplit - 1) / p.nsplit;
   const int tlo = min(split * chunk, ntiles), thi = min(tlo + chunk, ntiles);
+  const long smh = (long)ch * p.S_pad * D, cdh = (long)ch * p.S_pad * CB, rowb = (long)ch * p.S_pad, tileb = (long)ch * (p.S_pad >> 4);
+  int ohk = 0, ohv = 0;
+  if (!PAGED && S > 0) { ohk = p.K.head_start[ch]; ohv = p.V.head_start[ch]; }
 
-  // ---- CTA tables: escape-byte table, per-lane-class base words {b3lo, b3hi, b4lo-b3lo, b4hi-b3hi} per group, a zero word
+  // ---- per-tile metadata of the range, staged once: escape offsets (slot layout) or mode-table entries (paged layout),
+  // so the main loop never waits on a dependent global load
+  int* metak = reinterpret_cast<int*>(smem + TB_META);
+  int* metav = metak + META_TILES;
+  const int nstaged = min(thi - tlo, META_TILES);
+  for (int i = tid; i < nstaged; i += ATT_THREADS) {
+    if (PAGED) { const int pc = p.bt[(long)b * p.bt_stride + tlo + i] * (2 * p.n_kv) + 2 * kvh; metak[i] = p.mt[pc]; metav[i] = p.mt[pc + 1]; }
+    else { metak[i] = p.K.tile_off[tileb + tlo + i]; metav[i] = p.V.tile_off[tileb + tlo + i]; }
+  }
+  // ---- CTA tables: escape-byte table, per-lane-class base words {b3lo, b3hi, b4lo-b3lo, b4hi-b3hi} per group, zero pads
   {
     const int brow = PAGED ? kvh : ch % p.n_base_rows;
     const uint8_t* b3k = (PAGED ? p.b3k : p.K.base3) + brow * D; const uint8_t* b4k = (PAGED ? p.b4k : p.K.base4) + brow * D;
     const uint8_t* b3v = (PAGED ? p.b3v : p.V.base3) + brow * D; const uint8_t* b4v = (PAGED ? p.b4v : p.V.base4) + brow * D;
-    fill_lutx(reinterpret_cast<u32x2*>(smem + TB_LUTX), tid);
-    if (tid < 16) {                                   // K: lane class jj, group gg -> words 2gg, 2gg+1
-      const int jj = tid >> 2, gg = tid & 3; u32 w3[8], w4[8];
+    if (tid < 256) fill_lutx(reinterpret_cast<u32x2*>(smem + TB_LUTX), tid);
+    if (tid >= 256 && tid < 272) {                    // K: lane class jj, group gg -> words 2gg, 2gg+1
+      const int t = tid - 256, jj = t >> 2, gg = t & 3; u32 w3[8], w4[8];
       k_base_words(b3k, jj, w3); k_base_words(b4k, jj, w4);
-      *reinterpret_cast<u32x4*>(smem + TB_KB + 16 * tid) = u32x4{w3[2 * gg], w3[2 * gg + 1], w4[2 * gg] - w3[2 * gg], w4[2 * gg + 1] - w3[2 * gg + 1]};
-    } else if (tid < 32) {                            // V: lane class rr, group gg
-      const int t = tid - 16, rr = t >> 1, gg = t & 1; u32 w3[4], w4[4];
+      *reinterpret_cast<u32x4*>(smem + TB_KB + 16 * t) = u32x4{w3[2 * gg], w3[2 * gg + 1], w4[2 * gg] - w3[2 * gg], w4[2 * gg + 1] - w3[2 * gg + 1]};
+    } else if (tid >= 288 && tid < 304) {             // V: lane class rr, group gg
+      const int t = tid - 288, rr = t >> 1, gg = t & 1; u32 w3[4], w4[4];
       v_base_words(b3v, rr, w3); v_base_words(b4v, rr, w4);
       *reinterpret_cast<u32x4*>(smem + TB_VB + 16 * t) = u32x4{w3[2 * gg], w3[2 * gg + 1], w4[2 * gg] - w3[2 * gg], w4[2 * gg + 1] - w3[2 * gg + 1]};
-    } else if (tid == 32) {
-      *reinterpret_cast<uint4*>(smem + TB_ZERO) = make_uint4(0, 0, 0, 0);
     }
+    if (tid >= 320 && tid < 320 + ATT_WARPS * NSTAGE * 2) {      // the 16 zero bytes in front of every escape window
+      const int t = tid - 320, st = t >> 1;
+      *reinterpret_cast<uint4*>(smem + TABLE_BYTES + st * STAGE_BYTES + ((t & 1) ? ST_VZ : ST_KZ)) = make_uint4(0, 0, 0, 0);
+    }
+    if (tid == 0) s_next = tlo + ATT_WARPS;           // tiles tlo .. tlo+W-1 go to warps 0..W-1, the rest is handed out on demand
   }
-  __syncthreads();
   u32 qa[8][2];
   {
     const bool ok = r < G;
@@ -317,19 +417,16 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) decode_attn_kernel(const __gri
 #pragma unroll
   for (int n = 0; n < 8; n++) A.acc[n][0] = A.acc[n][1] = A.acc[n][2] = A.acc[n][3] = 0.f;
   A.m0 = A.m1 = -CUDART_INF_F; A.l0 = A.l1 = 0.f;
+  __syncthreads();
 
   // ---- tile addressing
   uint8_t* ring = smem + TABLE_BYTES + warp * (NSTAGE * STAGE_BYTES);
   const u32 ring_s = (u32)__cvta_generic_to_shared(ring);
-  const long smh = (long)ch * p.S_pad * D, cdh = (long)ch * p.S_pad * CB, rowb = (long)ch * p.S_pad, tileb = (long)ch * (p.S_pad >> 4);
-  int ohk = 0, ohv = 0;
-  if (!PAGED && S > 0) { ohk = p.K.head_start[ch]; ohv = p.V.head_start[ch]; }
-  // meta = what must be known before the copies of a tile can be issued: escape offsets (slot) or table entries (paged)
-  auto load_meta = [&](int tile, int& mk, int& mv) {
-    if (PAGED) { const int pc = p.bt[(long)b * p.bt_stride + tile] * (2 * p.n_kv) + 2 * kvh; mk = p.mt[pc]; mv = p.mt[pc + 1]; }
+  auto make_ref = [&](int tile, TileRef& tr) {
+    int mk, mv;
+    if (tile - tlo < META_TILES) { mk = metak[tile - tlo]; mv = metav[tile - tlo]; }
+    else if (PAGED) { const int pc = p.bt[(long)b * p.bt_stride + tile] * (2 * p.n_kv) + 2 * kvh; mk = p.mt[pc]; mv = p.mt[pc + 1]; }
     else { mk = p.K.tile_off[tileb + tile]; mv = p.V.tile_off[tileb + tile]; }
-  };
-  auto make_ref = [&](int tile, int mk, int mv, TileRef& tr) {
     if (PAGED) {
       tr.rawk = mk < 0; tr.rawv = mv < 0;
       const long pk = tr.rawk ? ~mk : mk, pv = tr.rawv ? ~mv : mv;
@@ -349,31 +446,28 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) decode_attn_kernel(const __gri
       tr.kraw = tr.vraw = nullptr;
     }
   };
+  auto grab = [&]() -> int {                          // next unassigned tile of the CTA's range (>= thi when none is left)
+    int t = 0;
+    if (lane == 0) t = atomicAdd(&s_next, 1);
+    return __shfl_sync(FULLM, t, 0);
+  };
 
-  // ---- the warp's tiles: tlo + warp, + ATT_WARPS, ...
+  // ---- main loop: the warp's first tile is tlo + warp; every further tile is taken from the CTA's counter when its
+  // copies are issued, one tile ahead of its use, so fast and slow warps finish within about one tile of each other
   int tile = tlo + warp;
   TileRef cur, nxt;
-  int mk = 0, mv = 0;
-  if (tile < thi) {
-    load_meta(tile, mk, mv); make_ref(tile, mk, mv, cur);
-    issue_tile(ring_s, cur, lane);
-    if (tile + ATT_WARPS < thi) load_meta(tile + ATT_WARPS, mk, mv);
-  }
+  if (tile < thi) { make_ref(tile, cur); issue_tile(ring_s, cur, lane); }
   cp_commit();
   int stg = 0;
-  for (; tile < thi; tile += ATT_WARPS) {
-    const int t1 = tile + ATT_WARPS;
-    if (t1 < thi) {
-      make_ref(t1, mk, mv, nxt);
-      issue_tile(ring_s + (stg ^ 1) * STAGE_BYTES, nxt, lane);
-      if (t1 + ATT_WARPS < thi) load_meta(t1 + ATT_WARPS, mk, mv);
-    }
+  while (tile < thi) {
+    const int t1 = grab();
+    if (t1 < thi) { make_ref(t1, nxt); issue_tile(ring_s + (stg ^ 1) * STAGE_BYTES, nxt, lane); }
     cp_commit();
     cp_wait<1>();
     __syncwarp();
     process_tile(A, ring + stg * STAGE_BYTES, smem, cur, min(T, S - tile * T), lane, qa, p.scale_log2);
     __syncwarp();
-    cur = nxt; stg ^= 1;
+    cur = nxt; stg ^= 1; tile = t1;
   }
   cp_wait<0>();
   // ---- slot layout: the raw BF16 tail belongs to the last split's warp 0
@@ -387,7 +481,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) decode_attn_kernel(const __gri
     }
   }
 
-  // ---- merge the warps of the CTA (the ring is free now)
+  // ---- merge the warps of the CTA (the rings are free now)
   __syncthreads();
   float* sh_m = reinterpret_cast<float*>(smem + TABLE_BYTES);    // [W][8]
   float* sh_l = sh_m + ATT_WARPS * 8;                            // [W][8]
@@ -421,7 +515,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) decode_attn_kernel(const __gri
     }
   }
   // ---- the last CTA of this (row, kv head) merges the splits
-  __shared__ int s_last;
   __threadfence();
   __syncthreads();
   if (tid == 0) {
@@ -432,18 +525,56 @@ __global__ void __launch_bounds__(ATT_THREADS, 2) decode_attn_kernel(const __gri
   __syncthreads();
   if (!s_last) return;
   __threadfence();
+  // All loads below are independent of one another (no per-split dependent chain): scale factors first, then the weighted sum
+  // with one warp per split and 16-byte loads, then a cross-warp sum in shared memory.
   {
+    float* c_f = reinterpret_cast<float*>(smem + TABLE_BYTES);           // [G][NS]  m, then exp2(m - M)
+    float* c_l = c_f + 8 * NS;                                            // [G][NS]  l
+    float* c_ML = c_l + 8 * NS;                                           // [8][2]   M, L per head
+    float* c_red = c_ML + 16;                                             // [W][G][128] (NS <= 1024 keeps this inside the ring area)
+    const long qh0 = (long)b * p.n_q + kvh * G;
+    for (int i = tid; i < G * NS; i += ATT_THREADS) { c_f[i] = __ldcg(p.pm + qh0 * NS + i); c_l[i] = __ldcg(p.pl + qh0 * NS + i); }
+    __syncthreads();
+    if (warp < G) {
+      float M = -CUDART_INF_F;
+      for (int s2 = lane; s2 < NS; s2 += 32) M = fmaxf(M, c_f[warp * NS + s2]);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(FULLM, M, o));
+      float L = 0.f;
+      for (int s2 = lane; s2 < NS; s2 += 32) {
+        const float ms = c_f[warp * NS + s2];
+        const float f = (ms == -CUDART_INF_F) ? 0.f : fast_exp2(ms - M);
+        c_f[warp * NS + s2] = f; L += c_l[warp * NS + s2] * f;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(FULLM, L, o);
+      if (lane == 0) { c_ML[2 * warp] = M; c_ML[2 * warp + 1] = L; }
+    }
+    __syncthreads();
+    float4 acc4[8];
+#pragma unroll
+    for (int g = 0; g < 8; g++) acc4[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s2 = warp; s2 < NS; s2 += ATT_WARPS) {
+#pragma unroll
+      for (int g = 0; g < 8; g++) {
+        if (g < G) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(p.pa + ((qh0 + g) * NS + s2) * D) + lane);
+          const float f = c_f[g * NS + s2];
+          acc4[g].x += v.x * f; acc4[g].y += v.y * f; acc4[g].z += v.z * f; acc4[g].w += v.w * f;
+        }
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < 8; g++)
+      if (g < G) *reinterpret_cast<float4*>(c_red + ((warp * 8 + g) * D) + 4 * lane) = acc4[g];
+    __syncthreads();
     const int d = tid & 127;
     for (int g = tid >> 7; g < G; g += ATT_THREADS / 128) {
-      const long qh = (long)b * p.n_q + kvh * G + g;
-      float M = -CUDART_INF_F;
-      for (int s = 0; s < NS; s++) M = fmaxf(M, __ldcg(p.pm + qh * NS + s));
-      float L = 0.f, Ac = 0.f;
-      for (int s = 0; s < NS; s++) {
-        const float ms = __ldcg(p.pm + qh * NS + s);
-        const float f = (ms == -CUDART_INF_F) ? 0.f : fast_exp2(ms - M);
-        L += __ldcg(p.pl + qh * NS + s) * f; Ac += __ldcg(p.pa + (qh * NS + s) * D + d) * f;
-      }
+      float Ac = 0.f;
+#pragma unroll
+      for (int w = 0; w < ATT_WARPS; w++) Ac += c_red[(w * 8 + g) * D + d];
+      const float M = c_ML[2 * g], L = c_ML[2 * g + 1];
+      const long qh = qh0 + g;
       if (p.part) {                                  // un-normalised partial for a cross-GPU merge: m in natural-log units
         float* o = p.part + qh * 130;
         if (d == 0) { o[0] = M * LN2; o[1] = L; }
@@ -499,7 +630,7 @@ static int slot_attn(const gaac_side* K, const gaac_side* V, const void* q, cons
                      int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap, int n_base_rows, void* ws, size_t ws_bytes,
                      void* out, float* out_f32, float* part, void* stream) {
   if (!K || !V || !q || !slot || !seq_len || (!out && !part)) return GAAC_E_ARG;
-  if (B <= 0 || n_q <= 0 || n_kv <= 0 || nsplit <= 0 || nsplit > 65535 || S_pad <= 0 || S_pad % T || n_base_rows <= 0) return GAAC_E_ARG;
+  if (B <= 0 || n_q <= 0 || n_kv <= 0 || nsplit <= 0 || nsplit > 1024 || S_pad <= 0 || S_pad % T || n_base_rows <= 0) return GAAC_E_ARG;
   if (n_q % n_kv || n_q / n_kv < 1 || n_q / n_kv > 8) return GAAC_E_UNSUPPORTED;
   for (const gaac_side* s : {K, V}) {
     if (!s->sm || !s->codes || !s->flags || !s->tile_off || !s->ovf || !s->head_start || !s->base3 || !s->base4 || s->ovf_bytes < 0) return GAAC_E_ARG;
@@ -552,7 +683,7 @@ extern "C" int gaac_paged_decode_attn(const gaac_paged* st, const int32_t* bt, i
                                       int B, int n_q, float scale, int nsplit, void* workspace, size_t workspace_bytes,
                                       void* out_bf16, float* out_f32, void* stream) {
   if (!st || !bt || !seq_lens || !q_bf16 || !out_bf16 || !st->buf || !st->raw || !st->mt || !st->b3k || !st->b4k || !st->b3v || !st->b4v) return GAAC_E_ARG;
-  if (B <= 0 || n_q <= 0 || st->n_kv <= 0 || nsplit <= 0 || nsplit > 65535 || bt_stride <= 0) return GAAC_E_ARG;
+  if (B <= 0 || n_q <= 0 || st->n_kv <= 0 || nsplit <= 0 || nsplit > 1024 || bt_stride <= 0) return GAAC_E_ARG;
   if (n_q % st->n_kv || n_q / st->n_kv < 1 || n_q / st->n_kv > 8 || st->TS % 16 || st->TS != SLOT_OVF_OFF + st->ovf_slot) return GAAC_E_UNSUPPORTED;
   if (!aligned16(st->buf) || (reinterpret_cast<uintptr_t>(st->raw) & 3) || (reinterpret_cast<uintptr_t>(q_bf16) & 3)) return GAAC_E_ALIGN;
   AttnParams p{};

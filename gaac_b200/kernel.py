@@ -11,7 +11,7 @@ from . import _lib
 
 _WS = {}        # (device index, stream) -> workspace tensor; the kernel leaves its counters zeroed, so the buffer is reusable
 SM_COUNT_B200 = 148
-ATT_WARPS = 8   # warps per CTA of the CUDA kernel
+ATT_WARPS = 16  # warps per CTA of the CUDA kernel (one CTA per SM)
 
 
 def workspace(dev, B: int, n_q: int, nsplit: int) -> torch.Tensor:
@@ -29,12 +29,13 @@ def choose_nsplit(B: int, n_kv: int, S: int, target_ctas: int = 96, min_tok: int
     return min(max(1, target_ctas // (B * n_kv)), max(1, S // min_tok), cap)
 
 
-def choose_nsplit_sm100(B: int, n_kv: int, S: int, sm_count: int = SM_COUNT_B200, ctas_per_sm: int = 2, min_tiles_per_warp: int = 2) -> int:
-    """Splits per (row, kv head) for a B200: fill sm_count * ctas_per_sm CTAs, but keep at least min_tiles_per_warp
-    16-token tiles for each of the CTA's warps so the per-CTA prologue and merge stay amortised."""
+def choose_nsplit_sm100(B: int, n_kv: int, S: int, sm_count: int = SM_COUNT_B200, min_tiles_per_warp: int = 2) -> int:
+    """Splits per (row, kv head) for a B200.  The kernel runs one 16-warp CTA per SM, so the grid B*n_kv*nsplit should fill
+    the SMs in one wave without spilling into a second one, while every warp of a CTA keeps at least min_tiles_per_warp
+    16-token tiles so the per-CTA prologue and merge stay amortised."""
     rows = max(1, B * n_kv)
     ntiles = max(1, (S + 15) // 16)
-    want = -(-(sm_count * ctas_per_sm) // rows)
+    want = max(1, sm_count // rows)
     most = max(1, ntiles // (ATT_WARPS * min_tiles_per_warp))
     return max(1, min(want, most))
 
