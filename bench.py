@@ -174,7 +174,7 @@ def run_ours(args):
     SL = torch.full((N_KV,), S_loc, dtype=torch.int32, device=dev)
     e32 = torch.empty(0, dtype=torch.int32, device=dev); ebf = torch.empty(0, dtype=torch.bfloat16, device=dev)
     part = torch.empty(N_Q, 130, dtype=torch.float32, device=dev)
-    gathered = torch.empty(world, N_Q, 130, dtype=torch.float32, device=dev)
+    gathered = torch.empty(world * N_Q, 130, dtype=torch.float32, device=dev)
     ext = _ext()
 
     def layer(i, qq):
@@ -186,7 +186,7 @@ def run_ours(args):
             return ext.gaac_attn_launch(*common)
         ext.gaac_attn_launch(*common, partial=part)
         dist.all_gather_into_tensor(gathered, part)
-        gt = gathered.permute(1, 0, 2)                                                 # [n_q, world, 130]
+        gt = gathered.view(world, N_Q, 130).permute(1, 0, 2)                           # [n_q, world, 130]
         return combine(gt[:, :, 0].contiguous(), gt[:, :, 1].contiguous(), gt[:, :, 2:].contiguous())
 
     launches_per_step = 1 if world == 1 else 5       # ours: attention (+ combine); the 3 small copies feeding combine are torch's

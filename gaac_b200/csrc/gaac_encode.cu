@@ -65,18 +65,54 @@ __global__ void __launch_bounds__(256) tile_scan_kernel(const int* __restrict__ 
   if (tid == 0 && head_bytes) head_bytes[h] = carry_s;
 }
 
-// One warp per (head, tile): slot -> ovf[head_start[h] + tile_off[h, tile]].
+// head_start[0..H] = exclusive prefix of head_bytes (one small CTA; H is the number of cache heads).
+__global__ void __launch_bounds__(256) head_prefix_kernel(const int* __restrict__ head_bytes, int H, int* __restrict__ head_start) {
+  __shared__ int wsum[8];
+  __shared__ int carry_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) { carry_s = 0; head_start[0] = 0; }
+  __syncthreads();
+  for (int base = 0; base < H; base += 256) {
+    const int i = base + tid;
+    const int v = i < H ? head_bytes[i] : 0;
+    int inc = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) { int u = __shfl_up_sync(FULL, inc, d); if (lane >= d) inc += u; }
+    if (lane == 31) wsum[warp] = inc;
+    __syncthreads();
+    int woff = 0;
+    for (int w = 0; w < warp; w++) woff += wsum[w];
+    const int carry = carry_s;
+    if (i < H) head_start[i + 1] = carry + woff + inc;
+    __syncthreads();
+    if (tid == 255) carry_s = carry + woff + inc;
+    __syncthreads();
+  }
+}
+
+// One warp per (head, tile): slot -> ovf[head_start[h] + tile_off[h, tile]]; optionally the per-row escape offsets
+// ovf_off[h, row] = tile_off[h, tile] + (escape bytes of the tile's earlier rows), recomputed from the tag words.
 __global__ void __launch_bounds__(128) compact_copy_kernel(const uint8_t* __restrict__ slots, const int* __restrict__ tile_bytes, int ntiles,
                                                             const int* __restrict__ tile_off, long tile_off_stride,
-                                                            const int* __restrict__ head_start, uint8_t* __restrict__ ovf, long n_items) {
+                                                            const int* __restrict__ head_start, uint8_t* __restrict__ ovf, long n_items,
+                                                            const int* __restrict__ flags, long S, long S_pad, int* __restrict__ ovf_off) {
   const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (item >= n_items) return;
   const int lane = threadIdx.x & 31;
   const long h = item / ntiles, t = item % ntiles;
   const int n = tile_bytes[item];
+  const int toff = tile_off[h * tile_off_stride + t];
   const uint8_t* src = slots + item * (long)TILE_MAX_ESC;
-  uint8_t* dst = ovf + (long)head_start[h] + tile_off[h * tile_off_stride + t];
+  uint8_t* dst = ovf + (long)head_start[h] + toff;
   for (int i = lane; i < n; i += 32) dst[i] = src[i];
+  if (ovf_off) {
+    const long row = t * T + (lane & 15);
+    const int sz = (lane < T && row < S) ? row_esc_bytes((u32)flags[h * S_pad + row]) : 0;
+    int inc = sz;
+#pragma unroll
+    for (int d = 1; d < T; d <<= 1) { int v = __shfl_up_sync(FULL, inc, d); if (lane >= d) inc += v; }
+    if (lane < T && row < S) ovf_off[h * S + row] = toff + inc - sz;
+  }
 }
 
 // One warp per (head, tile): compressed tile -> bf16 rows.
@@ -175,15 +211,24 @@ extern "C" int gaac_encode_tiles(const void* x_bf16, int64_t H, int64_t S, int64
 }
 
 extern "C" int gaac_compact(const uint8_t* slots, const int32_t* tile_bytes, int64_t H, int64_t ntiles, const int32_t* head_start,
-                            uint8_t* ovf, int32_t* tile_off, int64_t tile_off_stride, int32_t* head_bytes, void* stream) {
+                            uint8_t* ovf, int32_t* tile_off, int64_t tile_off_stride, int32_t* head_bytes,
+                            const int32_t* flags, int64_t S, int64_t S_pad, int32_t* ovf_off, void* stream) {
   if (!tile_bytes || !tile_off || H <= 0 || ntiles <= 0 || tile_off_stride < ntiles) return GAAC_E_ARG;
   if (head_start && (!ovf || !slots)) return GAAC_E_ARG;
+  if (ovf_off && (!head_start || !flags || S <= 0 || S_pad < S)) return GAAC_E_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   tile_scan_kernel<<<(unsigned)H, 256, 0, st>>>(tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_bytes);
   if (head_start) {
     const long n_items = H * ntiles;
-    compact_copy_kernel<<<(unsigned)((n_items + 3) / 4), 128, 0, st>>>(slots, tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_start, ovf, n_items);
+    compact_copy_kernel<<<(unsigned)((n_items + 3) / 4), 128, 0, st>>>(slots, tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_start, ovf, n_items,
+                                                                    flags, S, S_pad, ovf_off);
   }
+  return launch_status();
+}
+
+extern "C" int gaac_head_prefix(const int32_t* head_bytes, int64_t H, int32_t* head_start, void* stream) {
+  if (!head_bytes || !head_start || H <= 0) return GAAC_E_ARG;
+  head_prefix_kernel<<<1, 256, 0, (cudaStream_t)stream>>>(head_bytes, (int)H, head_start);
   return launch_status();
 }
 

@@ -1,0 +1,89 @@
+"""Multi-GPU partitioning of the compressed-KV decode path (one process per GPU, torch.distributed).
+
+The reference runs compressed KV on a single GPU (nanovllm/config.py:37 asserts tensor_parallel_size == 1); this module is
+what a multi-GPU deployment of the same path needs:
+
+  * shard_sequences / shard_heads: batched decode and kv-head sharding - independent shards, no collective on the path;
+  * split_context + ContextSplitAttention: batch-1 long context - every rank attends over its contiguous, tile-aligned token
+    range and writes an un-normalised partial (m, l, acc[128]) per query head; the partials are all-gathered (NCCL over
+    NVLink on GPUs) and merged with the split-merge algebra of gaac/kernel.py:281-294.
+"""
+from __future__ import annotations
+import torch
+import torch.distributed as dist
+
+T = 16
+
+
+def shard_sequences(seq_lens, world: int) -> list[list[int]]:
+    """Sequence indices per rank, balanced by token count (longest first onto the lightest rank)."""
+    order = sorted(range(len(seq_lens)), key=lambda i: -int(seq_lens[i]))
+    load = [0] * world
+    out: list[list[int]] = [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda k: (load[k], k))
+        out[r].append(i); load[r] += int(seq_lens[i])
+    return [sorted(x) for x in out]
+
+
+def shard_heads(n_kv: int, world: int, rank: int) -> range:
+    """KV heads of `rank` (contiguous, as even as possible).  Query heads kvh*G .. kvh*G+G-1 go with their kv head."""
+    base, extra = divmod(n_kv, world)
+    lo = rank * base + min(rank, extra)
+    return range(lo, lo + base + (1 if rank < extra else 0))
+
+
+def split_context(S: int, world: int, rank: int) -> tuple[int, int]:
+    """Token range [lo, hi) of `rank`: contiguous, aligned to 16-token tiles; the ragged end belongs to the last rank."""
+    tiles = (S + T - 1) // T
+    lo, hi = tiles * rank // world, tiles * (rank + 1) // world
+    return lo * T, min(hi * T, S)
+
+
+def merge_partials(part: torch.Tensor, group=None, combine_fn=None, out_f32: torch.Tensor | None = None) -> torch.Tensor:
+    """part: [n_heads, 130] fp32 (m in natural-log units, l, acc[128]) of this rank -> merged output [n_heads, 128] on every rank.
+    combine_fn(pm, pl, pa) merges [n_heads, world] / [n_heads, world, 128]; default: the CUDA merge kernel (gaac_combine)."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        gathered = part.unsqueeze(0)
+    else:
+        gathered = torch.empty(world * part.shape[0], *part.shape[1:], dtype=part.dtype, device=part.device)   # concatenated along dim 0
+        dist.all_gather_into_tensor(gathered, part.contiguous(), group=group)
+        gathered = gathered.view(world, *part.shape)
+    g = gathered.permute(1, 0, 2)                                   # [n_heads, world, 130]
+    pm, pl, pa = g[:, :, 0].contiguous(), g[:, :, 1].contiguous(), g[:, :, 2:].contiguous()
+    if combine_fn is None:
+        from .kernel import combine
+        return combine(pm, pl, pa, out_f32=out_f32)
+    return combine_fn(pm, pl, pa)
+
+
+class ContextSplitAttention:
+    """Batch-1 decode attention with the context split across the ranks of a process group.
+
+    Every rank holds the Pages of its own token range (kp, vp: kinds 'k' / 'v', H = n_kv heads).  __call__(q) runs the fused
+    kernel in partial mode and merges the ranks' partials; every rank returns the full [n_q, 128] output."""
+
+    def __init__(self, kp, vp, n_q: int, scale: float | None = None, nsplit: int | None = None, group=None):
+        from .kernel import choose_nsplit_sm100
+        self.kp, self.vp, self.n_q, self.group = kp, vp, n_q, group
+        self.n_kv = kp.H
+        self.scale = scale if scale is not None else 128 ** -0.5
+        self.nsplit = nsplit or choose_nsplit_sm100(1, self.n_kv, max(kp.S, 1))
+        dev = kp.sm.device
+        self._slots = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._SL = torch.full((self.n_kv,), kp.S, dtype=torch.int32, device=dev)
+        self._e32 = torch.empty(0, dtype=torch.int32, device=dev); self._ebf = torch.empty(0, dtype=torch.bfloat16, device=dev)
+        self._part = torch.empty(n_q, 130, dtype=torch.float32, device=dev)
+
+    def partial(self, q: torch.Tensor) -> torch.Tensor:
+        from .kernel import _ext
+        kp, vp = self.kp, self.vp
+        _ext().gaac_attn_launch(kp.sm, kp.codes, kp.flags, kp.tile_off, kp.ovf, kp.ovf_head_start, kp.base3, kp.base4,
+                                vp.sm, vp.codes, vp.flags, vp.tile_off, vp.ovf, vp.ovf_head_start, vp.base3, vp.base4,
+                                q.reshape(self.n_q, 128), self._slots, self.n_q, self.n_kv, self._SL, kp.sm.shape[1] // 128, self.scale, self.nsplit,
+                                self._ebf, self._ebf, self._e32, 0, partial=self._part)
+        return self._part
+
+    def __call__(self, q: torch.Tensor, out_f32: torch.Tensor | None = None) -> torch.Tensor:
+        return merge_partials(self.partial(q), self.group, out_f32=out_f32)

@@ -59,18 +59,19 @@ class TileEncoder:
         tile_off = torch.empty_like(tile_bytes); head_bytes = torch.zeros(H, dtype=torch.int32, device=tile_bytes.device)
         if H and ntiles:
             _lib.check(_lib.lib().gaac_compact(None, tile_bytes.data_ptr(), H, ntiles, None, None, tile_off.data_ptr(), ntiles,
-                                               head_bytes.data_ptr(), _lib.stream_ptr(tile_bytes.device)), "gaac_compact")
+                                               head_bytes.data_ptr(), None, 0, 0, None, _lib.stream_ptr(tile_bytes.device)), "gaac_compact")
         return tile_off, head_bytes
 
-    def compact(self, tile_bytes, head_start, ovf) -> torch.Tensor:
+    def compact(self, tile_bytes, head_start, ovf, flags=None, S=0, S_pad=0, ovf_off=None) -> torch.Tensor:
         """Pack the scratch slots into ovf at head_start[h] + tile_off[h, t]; returns tile_off int32 [H, ntiles].
-        (gaac/encoder.py:104-109)"""
+        (gaac/encoder.py:104-109)  With flags / S / S_pad / ovf_off the per-row escape offsets are written too."""
         H, ntiles = tile_bytes.shape
         tile_off = torch.empty_like(tile_bytes)
         if H and ntiles:
             head_start = head_start.contiguous()
             _lib.check(_lib.lib().gaac_compact(self._slots.data_ptr(), tile_bytes.data_ptr(), H, ntiles, head_start.data_ptr(), ovf.data_ptr(),
-                                               tile_off.data_ptr(), ntiles, None, _lib.stream_ptr(tile_bytes.device)), "gaac_compact")
+                                               tile_off.data_ptr(), ntiles, None, _lib.ptr(flags), S, S_pad, _lib.ptr(ovf_off),
+                                               _lib.stream_ptr(tile_bytes.device)), "gaac_compact")
         return tile_off
 
     def encode(self, codec: Codec, x: torch.Tensor) -> Page:
@@ -79,10 +80,12 @@ class TileEncoder:
         S_pad = (S + T - 1) // T * T
         sm = torch.empty(H, S_pad * D, dtype=torch.uint8, device=dev)
         cd = torch.empty(H, S_pad * CB, dtype=torch.uint8, device=dev)
-        flags = torch.zeros(H, S_pad, dtype=torch.int32, device=dev)
+        flags = torch.empty(H, S_pad, dtype=torch.int32, device=dev)          # every row of every tile is written, padded rows as 0
         tile_bytes = self.encode_tiles(x, codec.base3, codec.base4, sm, cd, flags, S, S_pad, codec.n_kv)
         _, head_bytes = self.tile_offsets(tile_bytes)
-        head_start = torch.cat([torch.zeros(1, dtype=torch.int64, device=dev), torch.cumsum(head_bytes, 0)]).to(torch.int32).contiguous()
+        head_start = torch.empty(H + 1, dtype=torch.int32, device=dev)
+        _lib.check(_lib.lib().gaac_head_prefix(head_bytes.data_ptr(), H, head_start.data_ptr(), _lib.stream_ptr(dev)), "gaac_head_prefix")
         ovf = torch.zeros(int(head_start[-1]) + 8, dtype=torch.uint8, device=dev)     # host sync: sizes the escape stream
-        tile_off = self.compact(tile_bytes, head_start, ovf)
-        return Page(sm, cd, flags, row_offsets(flags, S), ovf, head_start, tile_off, codec.base3, codec.base4, H, S, codec.n_kv, self.kind)
+        ovf_off = torch.empty(H, S, dtype=torch.int32, device=dev)
+        tile_off = self.compact(tile_bytes, head_start, ovf, flags, S, S_pad, ovf_off)
+        return Page(sm, cd, flags, ovf_off, ovf, head_start, tile_off, codec.base3, codec.base4, H, S, codec.n_kv, self.kind)

@@ -45,10 +45,16 @@ int gaac_encode_tiles(const void* x_bf16, int64_t H, int64_t S, int64_t S_in, in
 
 /* tile_off[h, t] = exclusive prefix of tile_bytes[h, :] (row stride tile_off_stride), head_bytes[h] = its sum (may be
  * NULL), then copy every scratch slot to ovf + head_start[h] + tile_off[h, t].  When head_start is NULL only the prefix
- * sums are produced (first pass, used to size ovf).  Replaces TileEncoder.compact / _compact and the cumsum between
- * them (gaac/encoder.py:69-76, 104-109). */
+ * sums are produced (first pass, used to size ovf).  When ovf_off is non-NULL the per-row offsets within each head's escape
+ * stream, ovf_off [H, S], are written as well (from flags [H, S_pad]).  Replaces TileEncoder.compact / _compact, the cumsum
+ * between them (gaac/encoder.py:69-76, 104-109) and row_offsets (gaac/codec.py:221-225). */
 int gaac_compact(const uint8_t* slots, const int32_t* tile_bytes, int64_t H, int64_t ntiles,
-                 const int32_t* head_start, uint8_t* ovf, int32_t* tile_off, int64_t tile_off_stride, int32_t* head_bytes, void* stream);
+                 const int32_t* head_start, uint8_t* ovf, int32_t* tile_off, int64_t tile_off_stride, int32_t* head_bytes,
+                 const int32_t* flags, int64_t S, int64_t S_pad, int32_t* ovf_off, void* stream);
+
+/* head_start[0..H] = exclusive prefix of head_bytes[0..H-1] (int32).  Replaces the head-level cumsum of
+ * TileEncoder.encode (gaac/encoder.py:119-120). */
+int gaac_head_prefix(const int32_t* head_bytes, int64_t H, int32_t* head_start, void* stream);
 
 /* Bit-exact reconstruction of H heads x S tokens into out [H, S, 128] bf16.  ovf_off is not needed: row positions are
  * recomputed from the tag words.  Replaces Codec.decode (gaac/codec.py:186-218). */

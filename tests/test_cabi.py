@@ -32,7 +32,8 @@ def test_bad_arguments_are_rejected_before_any_launch(lib):
     from gaac_b200 import _lib
     z = ctypes.c_void_p(0)
     assert lib.gaac_encode_tiles(z, 1, 16, 16, 16, z, z, z, 1, 0, z, z, z, z, z, z) == 1
-    assert lib.gaac_compact(z, z, 1, 1, z, z, z, 1, z, z) == 1
+    assert lib.gaac_compact(z, z, 1, 1, z, z, z, 1, z, z, 0, 0, z, z) == 1
+    assert lib.gaac_head_prefix(z, 1, z, z) == 1
     assert lib.gaac_decode_page(z, z, z, z, 1, z, z, z, z, z, 1, 0, 1, 16, 16, z, z) == 1
     assert lib.gaac_exponent_hist(z, 1, 128, z, z) == 1
     assert lib.gaac_combine(z, z, z, 1, 1, z, z, z) == 1
