@@ -100,6 +100,19 @@ int gaac_decode_attn(const gaac_side* K, const gaac_side* V, const void* q_bf16,
                      const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
                      int n_base_rows, void* workspace, size_t workspace_bytes, void* out_bf16, float* out_f32, void* stream);
 
+/* gaac_decode_attn for callers that cannot allocate device memory (a serving loop whose HBM was all handed to the cache
+ * pool, a plugin host that forbids allocator calls on its hot path, a caller without an allocator of its own): same
+ * arguments and results, but the workspace is a fixed 8 MiB array inside the library instead of a caller buffer.  No
+ * counterpart in the reference, whose launcher allocates its partials with torch on every call (gaac/kernel.py:306-307).
+ * Limits: gaac_attn_workspace_bytes(B, n_q, nsplit) must not exceed gaac_static_workspace_bytes(), else GAAC_E_WORKSPACE;
+ * every GPU that loads the library holds the array until the process exits; all calls on a GPU share it, so calls that
+ * overlap on one GPU race (serialise them, or use gaac_decode_attn with one workspace each).  The first call on a device
+ * resolves the array's device address; make that call outside of any stream capture. */
+size_t gaac_static_workspace_bytes(void);
+int gaac_decode_attn_static(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
+                            const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
+                            int n_base_rows, void* out_bf16, float* out_f32, void* stream);
+
 /* Merge n_parts partial results per query head: pm, pl [n_heads, n_parts], pa [n_heads, n_parts, 128] fp32 ->
  * out [n_heads, 128] bf16 (and fp32 when out_f32 != NULL).  M = max m; L = sum l*exp(m-M); O = sum acc*exp(m-M)/L, 0 when
  * L <= 0; parts with m = -inf are skipped.  Replaces gaac_combine<128> (gaac/kernel.py:281-294); also the merge step of
