@@ -150,7 +150,8 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=90))     # fail fast instead of hanging
     _lib.lib()
 
     # ---- this rank's share of the context: contiguous, tile aligned
@@ -206,10 +207,10 @@ def run_ours(args):
             ev[i][0].record(); layer(i, q); ev[i][1].record()
         t1.record()
         barrier()
-        # keep the GPU busy a little longer so the 100 ms sampler sees the loaded clocks
-        tb = time.perf_counter(); i = 0
-        while not args.profile and time.perf_counter() - tb < 1.0:
-            layer(i, q); i += 1
+        # keep the GPU busy a little longer so the 100 ms sampler sees the loaded clocks (the same number of calls on every
+        # rank: the calls contain a collective when N > 1)
+        for i in range(0 if args.profile else 4000):
+            layer(i, q)
         torch.cuda.synchronize()
     total_ms = t0.elapsed_time(t1)
     kern_ms = sorted(a.elapsed_time(b) for a, b in ev)
