@@ -24,7 +24,7 @@ SCALE = HEAD_DIM ** -0.5
 WORKLOAD = "decode attention, batch 1, 32 q heads / 8 kv heads (GQA 4), head_dim 128, 65536-token context, slot layout, 0-token tail"
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_attn_kernel launch at this workload, from the ncu capture
 # summarised in profiles/; None until a capture exists.
-NCU_TRAFFIC_BYTES = None
+NCU_TRAFFIC_BYTES = 201.2e6
 
 
 def measured_peak_gbs():
@@ -262,6 +262,24 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_encode_only(args):
+    import torch
+    from gaac_b200 import Codec, TileEncoder
+    from gaac_b200.synth import synth_kv
+    dev = torch.device("cuda", 0)
+    out = {}
+    for kind in "kv":
+        x = synth_kv(kind, N_KV, CTX, seed=55, device=dev)
+        codec = Codec(N_KV, dev).calibrate(x[:, :2048]); te = TileEncoder(kind, dev)
+        for _ in range(max(1, args.warmup)): te.encode(codec, x)
+        torch.cuda.synchronize(); ts = []
+        for _ in range(args.steps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); pg = te.encode(codec, x); b.record(); torch.cuda.synchronize(); ts.append(a.elapsed_time(b))
+        out[kind] = {"encode_ms_median": sorted(ts)[len(ts) // 2], "tiles": N_KV * (CTX // 16), "ratio": pg.ratio}
+    print(json.dumps({"profile_encode": out}), flush=True)
+
+
 def side_measurements(torch, dev, sets, q, args) -> dict:
     """Numbers reported beside the headline (outside its timed region): the CPU baseline on a bounded sample, the encoder's
     throughput, and a library BF16-KV decode (flash-attn / SDPA) at the same shape for context."""
@@ -321,8 +339,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--profile", action="store_true", help="only the warm-up and the timed steps (no e2e, no side measurements): the command to run under ncu")
+    ap.add_argument("--profile-encode", action="store_true", help="only the block encoder on [8, 65536, 128] K and V, --steps times each: the command to run under ncu")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile_encode:
+        run_encode_only(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
