@@ -28,8 +28,11 @@ constexpr int ST_KSM = 0, ST_KCD = 2048, ST_VSM = 2816, ST_VCD = 4864, ST_KFL = 
 constexpr int ST_KZ = 5760, ST_KESC = ST_KZ + ZPAD, ST_VZ = ST_KESC + ESC_WIN, ST_VESC = ST_VZ + ZPAD;
 constexpr int STAGE_BYTES = ST_VESC + ESC_WIN;       // 6304
 // CTA-wide tables in front of the rings: escape-byte table, K base words [j][g], V base words [r][g], a zero word
-constexpr int META_TILES = 1024;                     // tiles of a CTA's range whose metadata is staged (longer ranges read the rest from global)
-constexpr int TB_LUTX = 0, TB_KB = 2048, TB_VB = TB_KB + 256, TB_META = TB_VB + 256, TABLE_BYTES = TB_META + 2 * META_TILES * 4;
+constexpr int META_TILES = 512;                      // tiles of a CTA's range whose metadata is staged (longer ranges read the rest from global)
+// CTA tables: escape-byte table (2 KiB), K / V base words, per-tile metadata, and the code table: four 3-bit codes -> four bytes
+// for all 4096 values of a 12-bit field (16 KiB).  The table turns four logic instructions per lookup into one shared-memory load.
+constexpr int TB_LUTX = 0, TB_KB = 2048, TB_VB = TB_KB + 256, TB_META = TB_VB + 256, TB_LUTC = TB_META + 2 * META_TILES * 4;
+constexpr int TABLE_BYTES = TB_LUTC + 4096 * 4;
 constexpr int ATT_SMEM = TABLE_BYTES + ATT_WARPS * NSTAGE * STAGE_BYTES;
 constexpr unsigned FULLM = 0xffffffffu;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
@@ -158,62 +161,60 @@ __device__ __forceinline__ void pv_words(WarpAcc& A, int w, const u32 (&u01)[4],
 //   global memory (!WIN, tiles whose escapes exceed the window): plain loads at glob[pos].
 template <bool WIN> struct EscSrc { const uint8_t* zp; const uint8_t* glob; };
 
-// ---- byte-SWAR pieces written for the pipes of the SM: logic ops (LOP3 / PRMT) run on the ALU pipe, whose rate is half the
-// issue rate, so every shift that can be merged with an add is written as a multiply-add, which runs on the FMA pipe.
-#ifndef GAAC_SWAR_MAD
-#define GAAC_SWAR_MAD 1
-#endif
+// ---- byte-SWAR pieces written for the pipes of the SM: logic ops (LOP3 / PRMT / SHF) run on the ALU pipe, whose rate is half
+// the issue rate, so shifts that can be merged with an add are written as multiply-adds (FMA pipe) and the 3-bit -> byte
+// spreading of the codes is a table lookup (load/store pipe).
 template <u32 K> __device__ __forceinline__ u32 mad_k(u32 a, u32 c) {
   u32 d; asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "n"(K), "r"(c)); return d;
 }
-// four 3-bit codes at bits 0..11 of v (v < 4096) -> one code per byte, plus `addend` (the base word and the escape addend)
-__device__ __forceinline__ u32 spread_codes4_add(u32 v, u32 addend) {
-#if GAAC_SWAR_MAD
-  const u32 y = mad_k<1024u>(v & 0xFC0u, v);                        // bits 0-11: c0..c3, bits 16-21: c2, c3
-  return mad_k<32u>(y & 0x00380038u, (y & 0x00070007u) + addend);   // c1, c3 move up 5 bits into bytes 1 and 3
-#else
-  return spread_codes4(v) + addend;
-#endif
-}
 __device__ __forceinline__ void bf16x4_dev(u32 sm4, u32 e4, u32& p01, u32& p23) {
-#if GAAC_SWAR_MAD
   const u32 eh = __umulhi(e4, 0x80000000u);                          // e4 >> 1
   const u32 el = mad_k<128u>(e4, 0u);                                // e4 << 7
   const u32 h4 = (sm4 & 0x80808080u) | (eh & 0x7F7F7F7Fu);
   const u32 l4 = (el & 0x80808080u) | (sm4 & 0x7F7F7F7Fu);
   p01 = prmt(l4, h4, 0x5140); p23 = prmt(l4, h4, 0x7362);
-#else
-  bf16x4(sm4, e4, p01, p23);
-#endif
+}
+// four 5-bit fields at bits 0..19 of u -> field << 3 per byte (raw-tier exponent high bits); same result as spread_hi5
+__device__ __forceinline__ u32 spread_hi5_dev(u32 u) {
+  const u32 y = mad_k<64u>(u & 0xFFC00u, u & 0x3FFu);               // fields 0,1 at bits 0-9, fields 2,3 at bits 16-25
+  return mad_k<64u>(y & 0x03E003E0u, (y & 0x001F001Fu) << 3);       // odd fields up 3 more bits, everything << 3
 }
 
 // Rebuild one group (two sign/mantissa words) into four bf16x2 words.  Same results as decode_group_lut (gaac_tile.h);
-// pos16 = 16 + escape position of the group, advanced past it on return.
+// pos16 = 16 + escape position of the group, advanced past it on return; lutc = the 4096-entry code table.
 template <bool WIN>
 __device__ __forceinline__ void decode_group_dev(u32 sm_lo, u32 sm_hi, u32 c24, u32 tg, int& pos16, const EscSrc<WIN>& es,
-                                                 const u32x2* lutx, const u32x4& bw, u32 out[4]) {
+                                                 const u32x2* lutx, const uint8_t* lutc, const u32x4& bw, u32 out[4]) {
   const u32 m1 = tg & 1u;                             // promoted (tags are 0, 1 or 3)
   u32 xe;
   if (WIN) xe = es.zp[m1 * (u32)pos16];               // raw groups read a payload byte here; their addends are replaced below
   else xe = m1 ? es.glob[pos16 - 16] : 0u;
   const u32x2 x = lutx[xe];
   u32 x0 = x.x, x1 = x.y;
+  const u32 c_lo = *reinterpret_cast<const u32*>(lutc + ((c24 << 2) & 0x3FFCu));
+  const u32 c_hi = *reinterpret_cast<const u32*>(lutc + ((c24 >> 10) & 0x3FFCu));
   const u32 blo = bw.x + m1 * bw.z, bhi = bw.y + m1 * bw.w;
   if (tg & 2u) {                                      // raw exponents: e = code | hi5 << 3 (the base must not contribute)
-    const uint8_t* p = WIN ? es.zp + pos16 : es.glob + (pos16 - 16);
-    const int sh = 8 * (int)(reinterpret_cast<uintptr_t>(p) & 3);
-    const u32* a = reinterpret_cast<const u32*>(reinterpret_cast<uintptr_t>(p) & ~(uintptr_t)3);
-    const u32 w0 = a[0], w1 = a[1];
-    const u32 lo = funnel_r(w0, w1, sh), hi = w1 >> sh;
-    x0 = spread_hi5(lo) - blo;
-    x1 = spread_hi5(funnel_r(lo, hi, 20)) - bhi;
+    u32 w0, w1; int sh;
+    if (WIN) {
+      const u32 a = (u32)__cvta_generic_to_shared(es.zp) + (u32)pos16;
+      sh = 8 * (int)(a & 3u);
+      asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w0) : "r"(a & ~3u) : "memory");
+      asm volatile("ld.shared.u32 %0, [%1+4];" : "=r"(w1) : "r"(a & ~3u) : "memory");
+    } else {
+      const uint8_t* p = es.glob + (pos16 - 16);
+      sh = 8 * (int)(reinterpret_cast<uintptr_t>(p) & 3);
+      const u32* a = reinterpret_cast<const u32*>(reinterpret_cast<uintptr_t>(p) & ~(uintptr_t)3);
+      w0 = a[0]; w1 = a[1];
+    }
+    const u32 lo = funnel_r(w0, w1, sh), hi = w1 >> sh;              // bytes 0-3 and byte 4 of the payload
+    x0 = spread_hi5_dev(lo & 0xFFFFFu) - blo;
+    x1 = spread_hi5_dev(funnel_r(lo, hi, 20) & 0xFFFFFu) - bhi;
     pos16 += 4;
   }
   pos16 += (int)m1;
-  const u32 e0 = spread_codes4_add(c24 & 0xFFFu, blo + x0);
-  const u32 e1 = spread_codes4_add((c24 >> 12) & 0xFFFu, bhi + x1);
-  bf16x4_dev(sm_lo, e0, out[0], out[1]);
-  bf16x4_dev(sm_hi, e1, out[2], out[3]);
+  bf16x4_dev(sm_lo, c_lo + blo + x0, out[0], out[1]);
+  bf16x4_dev(sm_hi, c_hi + bhi + x1, out[2], out[3]);
 }
 
 // Scores of one compressed K tile: sc += K . Q^T.  flrow / rowoff: tag word and escape offset of row (lane & 15) held by
@@ -242,7 +243,7 @@ __device__ __forceinline__ void k_scores(float* sc, const uint8_t* stage, const 
     for (int o = 0; o < 2; o++) {
       const u32 smlo = g == 0 ? s0[o].x : g == 1 ? s0[o].z : g == 2 ? s1[o].x : s1[o].z;
       const u32 smhi = g == 0 ? s0[o].y : g == 1 ? s0[o].w : g == 2 ? s1[o].y : s1[o].w;
-      decode_group_dev<WIN>(smlo, smhi, k_group_codes(cd[o], g), t8[o] >> (2 * g), pos[o], es, lutx, bw, f[o]);
+      decode_group_dev<WIN>(smlo, smhi, k_group_codes(cd[o], g), t8[o] >> (2 * g), pos[o], es, lutx, tables + TB_LUTC, bw, f[o]);
     }
     { const u32 a[4] = {f[0][0], f[1][0], f[0][1], f[1][1]}; mma16816(sc, a, qa[2 * g][0], qa[2 * g][1]); }
     { const u32 a[4] = {f[0][2], f[1][2], f[0][3], f[1][3]}; mma16816(sc, a, qa[2 * g + 1][0], qa[2 * g + 1][1]); }
@@ -276,7 +277,7 @@ __device__ __forceinline__ void v_accum(WarpAcc& A, const uint8_t* stage, const 
 #pragma unroll
     for (int t = 0; t < 4; t++) {
       const u32 smlo = g == 0 ? sm[t].x : sm[t].z, smhi = g == 0 ? sm[t].y : sm[t].w;
-      decode_group_dev<WIN>(smlo, smhi, v_group_codes(cd, t, g), t4[t] >> (2 * g), pos[t], es, lutx, bw, f[t]);
+      decode_group_dev<WIN>(smlo, smhi, v_group_codes(cd, t, g), t4[t] >> (2 * g), pos[t], es, lutx, tables + TB_LUTC, bw, f[t]);
     }
 #pragma unroll
     for (int h = 0; h < 2; h++) {
@@ -388,6 +389,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     const uint8_t* b3k = (PAGED ? p.b3k : p.K.base3) + brow * D; const uint8_t* b4k = (PAGED ? p.b4k : p.K.base4) + brow * D;
     const uint8_t* b3v = (PAGED ? p.b3v : p.V.base3) + brow * D; const uint8_t* b4v = (PAGED ? p.b4v : p.V.base4) + brow * D;
     if (tid < 256) fill_lutx(reinterpret_cast<u32x2*>(smem + TB_LUTX), tid);
+    for (int i = tid; i < 4096; i += ATT_THREADS) reinterpret_cast<u32*>(smem + TB_LUTC)[i] = spread_codes4((u32)i);
     if (tid >= 256 && tid < 272) {                    // K: lane class jj, group gg -> words 2gg, 2gg+1
       const int t = tid - 256, jj = t >> 2, gg = t & 3; u32 w3[8], w4[8];
       k_base_words(b3k, jj, w3); k_base_words(b4k, jj, w4);
