@@ -1,13 +1,25 @@
 // Fused decode attention over GAAC-compressed K/V (sm_100a): slot layout and paged layout in one kernel template.
 //
-// CTA = (batch row, kv head, context split), ATT_WARPS warps.  Every warp streams its own 16-token tiles through a private
-// two-stage shared-memory ring filled with cp.async (16-byte chunks, re-ordered so that the later LDS.128 reads are
-// bank-conflict free), rebuilds BF16 K/V fragments in registers (byte-SWAR, gaac_tile.h) and feeds mma.sync m16n8k16:
+// CTA = (batch row, kv head, context split), ATT_WARPS warps, one CTA per SM.  Every warp streams its own 16-token tiles
+// through a private two-stage shared-memory ring filled with cp.async, rebuilds BF16 K/V fragments in registers (byte-SWAR,
+// gaac_tile.h) and feeds mma.sync m16n8k16:
 //   S^T[16 tok x 8 heads] = K[16 x 128] . Q^T        O^T[128 dims x 8 heads] += V^T[128 x 16 tok] . P^T
-// with an fp32 online softmax in the exp2 domain.  Raw BF16 tiles (the slot layout's tail, the paged layout's filling block
-// and raw-fallback tiles) are read straight from global memory into the same fragments.  The warps of a CTA are merged in
-// shared memory, the CTA writes one partial (m, l, acc[128]) per query head, and the last CTA of a (row, kv head) to
-// finish merges the splits and writes the output, so one launch does the whole layer.
+// with an fp32 online softmax in the exp2 domain whose maximum is raised lazily.  Raw BF16 tiles (the slot layout's tail, the
+// paged layout's filling block and raw-fallback tiles) are read straight from global memory into the same fragments.  Tiles
+// are handed to the warps of a CTA from a shared counter.  The warps of a CTA are merged in shared memory, the CTA writes
+// one partial (m, l, acc[128]) per query head, and the last CTA of a (row, kv head) to finish merges the splits and writes
+// the output, so one launch does the whole layer.
+//
+// What the measurements on B200 say about the copies (they shaped the code below):
+//  * cp.async.cg (L1 bypass) sends one 32-byte sector request per LANE over the crossbar and writes shared memory one lane
+//    chunk per wavefront: twice the L2->SM traffic and ~6x the shared-memory write wavefronts of cp.async.ca, which
+//    coalesces the lanes of a warp.  The 16-byte copies therefore use .ca (GAAC_CP16_CA).
+//  * the 16-byte chunks of the sign/mantissa planes are stored XOR-swizzled (GAAC_SWZ) so that both the cp.async writes
+//    (32 consecutive global chunks per instruction) and the later 16-byte fragment reads (stride-2 / stride-4 chunks per
+//    lane) touch eight different bank groups per quarter-warp.
+//  * the kernel is bound by instruction issue (ALU pipe) and by the shared-memory pipe, not by HBM: the 4096-entry code
+//    table (GAAC_LUTC) trades four logic instructions per lookup for one load with ~3.5-way bank conflicts; both settings
+//    run within 2 % of each other.
 //
 // Fragment conventions follow the reference kernel (gaac/kernel.py:62-66,160-194), whose storage order they mirror.
 #include <cuda_bf16.h>
@@ -17,6 +29,15 @@
 
 namespace gaac {
 
+#ifndef GAAC_CP16_CA
+#define GAAC_CP16_CA 1
+#endif
+#ifndef GAAC_LUTC
+#define GAAC_LUTC 1
+#endif
+#ifndef GAAC_SWZ
+#define GAAC_SWZ 1
+#endif
 constexpr int ATT_WARPS = 16;
 constexpr int ATT_THREADS = ATT_WARPS * 32;
 constexpr int NSTAGE = 2;
@@ -32,7 +53,7 @@ constexpr int META_TILES = 512;                      // tiles of a CTA's range w
 // CTA tables: escape-byte table (2 KiB), K / V base words, per-tile metadata, and the code table: four 3-bit codes -> four bytes
 // for all 4096 values of a 12-bit field (16 KiB).  The table turns four logic instructions per lookup into one shared-memory load.
 constexpr int TB_LUTX = 0, TB_KB = 2048, TB_VB = TB_KB + 256, TB_META = TB_VB + 256, TB_LUTC = TB_META + 2 * META_TILES * 4;
-constexpr int TABLE_BYTES = TB_LUTC + 4096 * 4;
+constexpr int TABLE_BYTES = TB_LUTC + (GAAC_LUTC ? 4096 * 4 : 0);
 constexpr int ATT_SMEM = TABLE_BYTES + ATT_WARPS * NSTAGE * STAGE_BYTES;
 constexpr unsigned FULLM = 0xffffffffu;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
@@ -60,14 +81,22 @@ __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_grou
 template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 __device__ __forceinline__ float fast_exp2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 
-// Where the pieces of one tile live.
-struct TileRef {
-  const uint8_t *ksm, *kcd, *kfl, *kesc;      // compressed K (kesc = global address of its first escape byte)
-  const uint8_t *vsm, *vcd, *vfl, *vesc;
-  const uint16_t *kraw, *vraw;                // raw bf16 [16][128] when the side is raw
-  bool rawk, rawv;
-  int esc_lim_k, esc_lim_v;                   // bytes that may be staged from kesc / vesc (allocation bound)
+// What a warp remembers of a tile between issuing its copies and consuming it.  Slot layout: offsets of the tile's escape
+// bytes inside the head's escape bytes.  Paged layout: the mode-table entries (>= 0: compressed slot, < 0: bit-complement
+// of a raw tile of the pool).
+struct TileMeta { int mk, mv; };
+
+// Loop-invariant addressing of one lane.  The slot layout keeps byte offsets that are valid for both sides (K and V buffers
+// have the same geometry); the paged layout needs none (a tile is one contiguous slot).
+struct LaneAddr {
+  long sm_off, cd_off, fl_off;   // head offset inside sm / codes / flags (bytes) + the lane's share: 16*lane, 16*lane, 16*(lane&3)
+  int ohk, ohv;                  // first escape byte of the head inside ovf
+  int availk, availv;            // bytes from there to the end of the allocation (clamped to int)
+  u32 kdst, vdst;                // lane part of the permuted shared-memory destinations of the sign/mantissa chunks
 };
+
+// Escape bytes of one side of one tile: global address of the first one, bytes that may be read from there.
+struct EscRef { const uint8_t* p; int lim; };
 
 // Escape bytes, counted from the tile's first escape byte `esc`, that the staged window holds: the window starts at the
 // 4-byte boundary below `esc`, is ESC_WIN bytes long at most, is copied in whole words and stays inside the allocation
@@ -77,38 +106,46 @@ __device__ __forceinline__ int esc_window_bytes(const uint8_t* esc, int alloc_le
   return max(0, min(ESC_WIN, (alloc_left + wsh) & ~3) - wsh);
 }
 
-// Issue the cp.async copies of one tile into a stage.  smem destinations of the sign/mantissa chunks are permuted:
-//   K: global chunk c (16 B) = (octet o = c>>6, lane l = (c>>1)&31, half = c&1)  ->  slot o*64 + half*32 + l
-//   V: global chunk c = (lane l = c>>2, token slot t = c&3)                      ->  slot t*32 + l
-__device__ __forceinline__ void issue_tile(u32 st, const TileRef& tr, int lane) {
-  if (!tr.rawk) {
-#pragma unroll
-    for (int k = 0; k < 4; k++) {
-      int c = lane + 32 * k;
-      cp16(st + ST_KSM + 16 * ((c >> 6) * 64 + (c & 1) * 32 + ((c >> 1) & 31)), tr.ksm + 16 * c);
-    }
-    cp16(st + ST_KCD + 16 * lane, tr.kcd + 16 * lane);
-    if (lane < 16) cp16(st + ST_KCD + 16 * (32 + lane), tr.kcd + 16 * (32 + lane));
-    if (lane < 4) cp16(st + ST_KFL + 16 * lane, tr.kfl + 16 * lane);
-    const uint8_t* a = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(tr.kesc) & ~(uintptr_t)3);
-    const int lim = esc_window_bytes(tr.kesc, tr.esc_lim_k) + (int)(tr.kesc - a);
-#pragma unroll
-    for (int k = 0; k < ESC_WIN / 128; k++) { int off = 4 * lane + 128 * k; if (off < lim) cp4(st + ST_KESC + off, a + off); }
-  }
-  if (!tr.rawv) {
-#pragma unroll
-    for (int k = 0; k < 4; k++) {
-      int c = lane + 32 * k;
-      cp16(st + ST_VSM + 16 * ((c & 3) * 32 + (c >> 2)), tr.vsm + 16 * c);
-    }
-    cp16(st + ST_VCD + 16 * lane, tr.vcd + 16 * lane);
-    if (lane >= 16) cp16(st + ST_VCD + 16 * (16 + lane), tr.vcd + 16 * (16 + lane));
-    if (lane >= 28) cp16(st + ST_VFL + 16 * (lane - 28), tr.vfl + 16 * (lane - 28));
-    const uint8_t* a = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(tr.vesc) & ~(uintptr_t)3);
-    const int lim = esc_window_bytes(tr.vesc, tr.esc_lim_v) + (int)(tr.vesc - a);
-#pragma unroll
-    for (int k = 0; k < ESC_WIN / 128; k++) { int off = 4 * lane + 128 * k; if (off < lim) cp4(st + ST_VESC + off, a + off); }
-  }
+template <int DOFF, int SOFF> __device__ __forceinline__ void cp16i(u32 dst, const void* src) {
+#if GAAC_CP16_CA
+  asm volatile("cp.async.ca.shared.global [%0+%2], [%1+%3], 16;\n" ::"r"(dst), "l"(src), "n"(DOFF), "n"(SOFF));
+#else
+  asm volatile("cp.async.cg.shared.global [%0+%2], [%1+%3], 16;\n" ::"r"(dst), "l"(src), "n"(DOFF), "n"(SOFF));
+#endif
+}
+template <int DOFF, int SOFF> __device__ __forceinline__ void cp4i(u32 dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0+%2], [%1+%3], 4;\n" ::"r"(dst), "l"(src), "n"(DOFF), "n"(SOFF));
+}
+
+// cp.async copies of one tile into stage `st`.  sm / cd point at the lane's 16-byte chunk (tile base + 16*lane), fl at
+// chunk (lane & 3) of the tag words.  Shared-memory destinations of the sign/mantissa chunks are permuted so that the
+// later 16-byte reads of a warp are consecutive:
+//   K: global chunk c = (octet o = c>>6, lane l = (c>>1)&31, half = c&1)  ->  slot o*64 + half*32 + l
+//   V: global chunk c = (lane l = c>>2, token slot t = c&3)               ->  slot t*32 + l
+// With c = lane + 32k the lane part of the slot is constant (LaneAddr::kdst, vdst) and the k part is an immediate.
+__device__ __forceinline__ void issue_k(u32 st, const uint8_t* sm, const uint8_t* cd, const uint8_t* fl, const LaneAddr& L, int lane) {
+  const u32 d = st + L.kdst, dl = st + 16 * lane;
+  cp16i<ST_KSM, 0>(d, sm); cp16i<ST_KSM + 256, 512>(d, sm); cp16i<ST_KSM + 1024, 1024>(d, sm); cp16i<ST_KSM + 1280, 1536>(d, sm);
+  cp16i<ST_KCD, 0>(dl, cd);
+  if (lane < 16) cp16i<ST_KCD + 512, 512>(dl, cd);
+  if (lane < 4) cp16i<ST_KFL, 0>(dl, fl);
+}
+__device__ __forceinline__ void issue_v(u32 st, const uint8_t* sm, const uint8_t* cd, const uint8_t* fl, const LaneAddr& L, int lane) {
+  const u32 d = st + L.vdst, dl = st + 16 * lane;
+  cp16i<ST_VSM, 0>(d, sm); cp16i<ST_VSM + 128, 512>(d, sm); cp16i<ST_VSM + 256, 1024>(d, sm); cp16i<ST_VSM + 384, 1536>(d, sm);
+  cp16i<ST_VCD, 0>(dl, cd);
+  if (lane >= 16) cp16i<ST_VCD + 256, 256>(dl, cd);
+  if (lane >= 28) cp16i<ST_VFL - 16 * 28, 0>(dl, fl);
+}
+// Escape window: whole words from the 4-byte boundary below the first escape byte; win = shared-memory address of the window.
+__device__ __forceinline__ void issue_esc(u32 win, const EscRef& e, int lane) {
+  const int wsh = (int)(reinterpret_cast<uintptr_t>(e.p) & 3);
+  const int lim = min(ESC_WIN, (e.lim + wsh) & ~3);           // bytes to copy, counted from the boundary
+  const uint8_t* a = e.p - wsh + 4 * lane;
+  const u32 d = win + 4 * lane;
+  static_assert(ESC_WIN == 256, "two words per lane");
+  if (4 * lane < lim) cp4i<0, 0>(d, a);
+  if (4 * lane + 128 < lim) cp4i<128, 128>(d, a);
 }
 
 // Running state of one warp.
@@ -118,21 +155,29 @@ struct WarpAcc {
 };
 
 // Online softmax on the score fragment + P^T B-fragments for the PV product.
+// The running maximum is only raised (and the accumulators rescaled) when some score of the tile exceeds it by more than
+// RESCALE_TAU in the exp2 domain; otherwise the tile is weighted against the stale maximum, so P stays below 2^RESCALE_TAU.
+// Sums and accumulators are fp32 and P keeps its relative BF16 rounding, so the result is as exact as with the true
+// maximum, and the common tile needs no cross-lane reduction, no rescale factor and no accumulator multiply.
+constexpr float RESCALE_TAU = 16.f;
 __device__ __forceinline__ void softmax_step(WarpAcc& A, const float* sc, float scale_log2, int nvalid, int lane, u32& pb0, u32& pb1) {
   const int j = lane & 3, r = lane >> 2;
   const bool v0 = r < nvalid, v8 = r + 8 < nvalid;
   const float s00 = v0 ? sc[0] * scale_log2 : -CUDART_INF_F, s01 = v0 ? sc[1] * scale_log2 : -CUDART_INF_F;
   const float s80 = v8 ? sc[2] * scale_log2 : -CUDART_INF_F, s81 = v8 ? sc[3] * scale_log2 : -CUDART_INF_F;
   float mt0 = fmaxf(s00, s80), mt1 = fmaxf(s01, s81);
+  if (__any_sync(FULLM, mt0 > A.m0 + RESCALE_TAU || mt1 > A.m1 + RESCALE_TAU)) {
 #pragma unroll
-  for (int o = 4; o < 32; o <<= 1) { mt0 = fmaxf(mt0, __shfl_xor_sync(FULLM, mt0, o)); mt1 = fmaxf(mt1, __shfl_xor_sync(FULLM, mt1, o)); }
-  const float mn0 = fmaxf(A.m0, mt0), mn1 = fmaxf(A.m1, mt1);
-  const float mu0 = (mn0 == -CUDART_INF_F) ? 0.f : mn0, mu1 = (mn1 == -CUDART_INF_F) ? 0.f : mn1;
-  const float al0 = fast_exp2(A.m0 - mu0), al1 = fast_exp2(A.m1 - mu1);
+    for (int o = 4; o < 32; o <<= 1) { mt0 = fmaxf(mt0, __shfl_xor_sync(FULLM, mt0, o)); mt1 = fmaxf(mt1, __shfl_xor_sync(FULLM, mt1, o)); }
+    const float mn0 = fmaxf(A.m0, mt0), mn1 = fmaxf(A.m1, mt1);
+    const float al0 = (mn0 == -CUDART_INF_F) ? 0.f : fast_exp2(A.m0 - mn0), al1 = (mn1 == -CUDART_INF_F) ? 0.f : fast_exp2(A.m1 - mn1);
+    A.l0 *= al0; A.l1 *= al1; A.m0 = mn0; A.m1 = mn1;
+#pragma unroll
+    for (int n = 0; n < 8; n++) { A.acc[n][0] *= al0; A.acc[n][2] *= al0; A.acc[n][1] *= al1; A.acc[n][3] *= al1; }
+  }
+  const float mu0 = fmaxf(A.m0, -1e30f), mu1 = fmaxf(A.m1, -1e30f);       // a maximum of -inf (nothing seen yet) must not produce inf - inf
   const float p00 = fast_exp2(s00 - mu0), p80 = fast_exp2(s80 - mu0), p01 = fast_exp2(s01 - mu1), p81 = fast_exp2(s81 - mu1);
-  A.l0 = A.l0 * al0 + (p00 + p80); A.l1 = A.l1 * al1 + (p01 + p81); A.m0 = mn0; A.m1 = mn1;
-#pragma unroll
-  for (int n = 0; n < 8; n++) { A.acc[n][0] *= al0; A.acc[n][2] *= al0; A.acc[n][1] *= al1; A.acc[n][3] *= al1; }
+  A.l0 += p00 + p80; A.l1 += p01 + p81;
   // this lane publishes W0 = (P[tok r][2j], P[tok r][2j+1]), W8 = (P[tok r+8][2j], P[tok r+8][2j+1]);
   // it needs b0 = (P[tok 2j][head r], P[tok 2j+1][head r]), b1 = the same for tokens 2j+8, 2j+9
   __nv_bfloat162 x = __floats2bfloat162_rn(p00, p01), y = __floats2bfloat162_rn(p80, p81);
@@ -191,8 +236,21 @@ __device__ __forceinline__ void decode_group_dev(u32 sm_lo, u32 sm_hi, u32 c24, 
   else xe = m1 ? es.glob[pos16 - 16] : 0u;
   const u32x2 x = lutx[xe];
   u32 x0 = x.x, x1 = x.y;
+#if GAAC_LUTC == 1
   const u32 c_lo = *reinterpret_cast<const u32*>(lutc + ((c24 << 2) & 0x3FFCu));
   const u32 c_hi = *reinterpret_cast<const u32*>(lutc + ((c24 >> 10) & 0x3FFCu));
+#elif GAAC_LUTC == 2
+  // one half through the table (load/store pipe), the other half by arithmetic (ALU + FMA pipes): balances the pipes
+  const u32 c_lo = *reinterpret_cast<const u32*>(lutc + ((c24 << 2) & 0x3FFCu));
+  const u32 th = (c24 >> 12) & 0xFFFu;
+  const u32 xh = mad_k<1023u>((c24 >> 12) & 0xFC0u, th);
+  const u32 c_hi = mad_k<31u>(xh & 0x00380038u, xh);
+#else
+  // four 3-bit codes -> four bytes in two steps; each step moves the upper fields with a multiply-add: (t & M) * (2^k - 1) + t
+  const u32 tl = c24 & 0xFFFu, th = (c24 >> 12) & 0xFFFu;
+  const u32 xl = mad_k<1023u>(c24 & 0xFC0u, tl), xh = mad_k<1023u>((c24 >> 12) & 0xFC0u, th);
+  const u32 c_lo = mad_k<31u>(xl & 0x00380038u, xl), c_hi = mad_k<31u>(xh & 0x00380038u, xh);
+#endif
   const u32 blo = bw.x + m1 * bw.z, bhi = bw.y + m1 * bw.w;
   if (tg & 2u) {                                      // raw exponents: e = code | hi5 << 3 (the base must not contribute)
     u32 w0, w1; int sh;
@@ -225,13 +283,18 @@ __device__ __forceinline__ void k_scores(float* sc, const uint8_t* stage, const 
   const int j = lane & 3, r = lane >> 2;
   const u32x2* lutx = reinterpret_cast<const u32x2*>(tables + TB_LUTX);
   u32 t8[2]; int pos[2]; uint4 s0[2], s1[2]; u32 cd[2][3];
+  float s2[4] = {0.f, 0.f, 0.f, 0.f};                  // second accumulator: two dependent MMA chains of four instead of one of eight
 #pragma unroll
   for (int o = 0; o < 2; o++) {
     const u32 fl = __shfl_sync(FULLM, flrow, 8 * o + r);
     pos[o] = __shfl_sync(FULLM, rowoff, 8 * o + r) + esc_prefix(fl, 8 * j) + 16;
     t8[o] = fl >> (8 * j);
     s0[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + lane));
+#if GAAC_SWZ
+    s1[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + 32 + (lane ^ 4)));
+#else
     s1[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + 32 + lane));
+#endif
     const u32* c = reinterpret_cast<const u32*>(stage + ST_KCD + o * 384 + 12 * lane);
     cd[o][0] = c[0]; cd[o][1] = c[1]; cd[o][2] = c[2];
   }
@@ -246,8 +309,9 @@ __device__ __forceinline__ void k_scores(float* sc, const uint8_t* stage, const 
       decode_group_dev<WIN>(smlo, smhi, k_group_codes(cd[o], g), t8[o] >> (2 * g), pos[o], es, lutx, tables + TB_LUTC, bw, f[o]);
     }
     { const u32 a[4] = {f[0][0], f[1][0], f[0][1], f[1][1]}; mma16816(sc, a, qa[2 * g][0], qa[2 * g][1]); }
-    { const u32 a[4] = {f[0][2], f[1][2], f[0][3], f[1][3]}; mma16816(sc, a, qa[2 * g + 1][0], qa[2 * g + 1][1]); }
+    { const u32 a[4] = {f[0][2], f[1][2], f[0][3], f[1][3]}; mma16816(s2, a, qa[2 * g + 1][0], qa[2 * g + 1][1]); }
   }
+  sc[0] += s2[0]; sc[1] += s2[1]; sc[2] += s2[2]; sc[3] += s2[3];
 }
 
 // O^T += V^T . P^T for one compressed V tile.  flrow / rowoff of V row (lane & 15) are held by lanes 16-31.
@@ -263,7 +327,11 @@ __device__ __forceinline__ void v_accum(WarpAcc& A, const uint8_t* stage, const 
     const u32 fl = __shfl_sync(FULLM, flrow, 16 + tok);
     pos[t] = __shfl_sync(FULLM, rowoff, 16 + tok) + esc_prefix(fl, 4 * r) + 16;
     t4[t] = fl >> (4 * r);
+#if GAAC_SWZ
+    sm[t] = *reinterpret_cast<const uint4*>(stage + ST_VSM + 16 * (t * 32 + (lane ^ (2 * t))));
+#else
     sm[t] = *reinterpret_cast<const uint4*>(stage + ST_VSM + 16 * (t * 32 + lane));
+#endif
   }
   {
     const uint2* c2 = reinterpret_cast<const uint2*>(stage + ST_VCD + 24 * lane);
@@ -288,67 +356,49 @@ __device__ __forceinline__ void v_accum(WarpAcc& A, const uint8_t* stage, const 
   }
 }
 
-// Consume one tile: stage = shared-memory stage of the compressed sides, tr = its description, nvalid = valid tokens (1..16).
-__device__ __forceinline__ void process_tile(WarpAcc& A, const uint8_t* stage, const uint8_t* tables, const TileRef& tr, int nvalid, int lane,
-                                             const u32 (&qa)[8][2], float scale_log2) {
+// Escape-byte offsets of the rows of a staged tile: lanes 0-15 scan the K rows, lanes 16-31 the V rows.  flrow = tag word of
+// row (lane & 15) of the lane's side (0 when that side is raw), rowoff = escape bytes of the rows before it, total = rowoff
+// of the row after it (lane 15 / 31 hold the tile's totals).
+__device__ __forceinline__ void scan_rows(const uint8_t* stage, bool rawk, bool rawv, int lane, u32& flrow, int& rowoff, int& total) {
+  const int row = lane & 15;
+  const bool isv = lane >= 16;
+  flrow = (isv ? rawv : rawk) ? 0u : *reinterpret_cast<const u32*>(stage + ST_KFL + 4 * lane);   // ST_VFL = ST_KFL + 64
+  static_assert(ST_VFL == ST_KFL + 64, "V tag words follow the K tag words");
+  const int sz = row_esc_bytes(flrow);
+  int inc = sz;
+#pragma unroll
+  for (int d = 1; d < 16; d <<= 1) { int v = __shfl_up_sync(FULLM, inc, d, 16); if (row >= d) inc += v; }
+  rowoff = inc - sz; total = inc;
+}
+
+// Scores of a raw BF16 tile [16][128] in global memory (rows >= nvalid are not read).
+__device__ __forceinline__ void raw_scores(float* sc, const uint16_t* kraw, int nvalid, int lane, const u32 (&qa)[8][2]) {
   const int j = lane & 3, r = lane >> 2;
-  // ---- row offsets of the escape bytes: lanes 0-15 scan the K rows, lanes 16-31 the V rows
-  int rowoff, total;
-  u32 flrow;
-  {
-    const int row = lane & 15;
-    const bool isv = lane >= 16;
-    const bool raw = isv ? tr.rawv : tr.rawk;
-    flrow = raw ? 0u : *reinterpret_cast<const u32*>(stage + (isv ? ST_VFL : ST_KFL) + 4 * row);
-    const int sz = row_esc_bytes(flrow);
-    int inc = sz;
 #pragma unroll
-    for (int d = 1; d < 16; d <<= 1) { int v = __shfl_up_sync(FULLM, inc, d, 16); if (row >= d) inc += v; }
-    rowoff = inc - sz; total = inc;
+  for (int s = 0; s < 8; s++) {
+    u32 a[4];
+    const uint16_t* k0 = kraw + r * D + 16 * s + 2 * j;
+    const uint16_t* k8 = k0 + 8 * D;
+    a[0] = r < nvalid ? *reinterpret_cast<const u32*>(k0) : 0u; a[2] = r < nvalid ? *reinterpret_cast<const u32*>(k0 + 8) : 0u;
+    a[1] = r + 8 < nvalid ? *reinterpret_cast<const u32*>(k8) : 0u; a[3] = r + 8 < nvalid ? *reinterpret_cast<const u32*>(k8 + 8) : 0u;
+    mma16816(sc, a, qa[s][0], qa[s][1]);
   }
-  // ---- scores
-  float sc[4] = {0.f, 0.f, 0.f, 0.f};
-  if (!tr.rawk) {
-    const int wsh = (int)(reinterpret_cast<uintptr_t>(tr.kesc) & 3);
-    if (__shfl_sync(FULLM, total, 15) + 8 <= esc_window_bytes(tr.kesc, tr.esc_lim_k))        // +8: a raw payload is read as two aligned words
-      k_scores<true>(sc, stage, tables, EscSrc<true>{stage + ST_KESC + wsh - ZPAD, nullptr}, flrow, rowoff, lane, qa);
-    else
-      k_scores<false>(sc, stage, tables, EscSrc<false>{nullptr, tr.kesc}, flrow, rowoff, lane, qa);
-  } else {
+}
+// O^T += V^T . P^T for a raw BF16 tile.
+__device__ __forceinline__ void raw_accum(WarpAcc& A, const uint16_t* vraw, int nvalid, int lane, u32 pb0, u32 pb1) {
+  const int j = lane & 3, r = lane >> 2;
 #pragma unroll
-    for (int s = 0; s < 8; s++) {
-      u32 a[4];
-      const uint16_t* k0 = tr.kraw + r * D + 16 * s + 2 * j;
-      const uint16_t* k8 = k0 + 8 * D;
-      a[0] = r < nvalid ? *reinterpret_cast<const u32*>(k0) : 0u; a[2] = r < nvalid ? *reinterpret_cast<const u32*>(k0 + 8) : 0u;
-      a[1] = r + 8 < nvalid ? *reinterpret_cast<const u32*>(k8) : 0u; a[3] = r + 8 < nvalid ? *reinterpret_cast<const u32*>(k8 + 8) : 0u;
-      mma16816(sc, a, qa[s][0], qa[s][1]);
+  for (int w = 0; w < 4; w++) {
+    u32 u01[4], u23[4];
+#pragma unroll
+    for (int t = 0; t < 4; t++) {
+      const int tok = 2 * j + (t & 1) + 8 * (t >> 1);
+      const uint16_t* vr = vraw + tok * D + 8 * (4 * w) + r;
+      const bool ok = tok < nvalid;
+      const u32 e0 = ok ? vr[0] : 0u, e1 = ok ? vr[8] : 0u, e2 = ok ? vr[16] : 0u, e3 = ok ? vr[24] : 0u;
+      u01[t] = e0 | (e1 << 16); u23[t] = e2 | (e3 << 16);
     }
-  }
-  // ---- softmax, P^T
-  u32 pb0, pb1;
-  softmax_step(A, sc, scale_log2, nvalid, lane, pb0, pb1);
-  // ---- PV
-  if (!tr.rawv) {
-    const int wsh = (int)(reinterpret_cast<uintptr_t>(tr.vesc) & 3);
-    if (__shfl_sync(FULLM, total, 31) + 8 <= esc_window_bytes(tr.vesc, tr.esc_lim_v))
-      v_accum<true>(A, stage, tables, EscSrc<true>{stage + ST_VESC + wsh - ZPAD, nullptr}, flrow, rowoff, lane, pb0, pb1);
-    else
-      v_accum<false>(A, stage, tables, EscSrc<false>{nullptr, tr.vesc}, flrow, rowoff, lane, pb0, pb1);
-  } else {
-#pragma unroll
-    for (int w = 0; w < 4; w++) {
-      u32 u01[4], u23[4];
-#pragma unroll
-      for (int t = 0; t < 4; t++) {
-        const int tok = 2 * j + (t & 1) + 8 * (t >> 1);
-        const uint16_t* vr = tr.vraw + tok * D + 8 * (4 * w) + r;
-        const bool ok = tok < nvalid;
-        const u32 e0 = ok ? vr[0] : 0u, e1 = ok ? vr[8] : 0u, e2 = ok ? vr[16] : 0u, e3 = ok ? vr[24] : 0u;
-        u01[t] = e0 | (e1 << 16); u23[t] = e2 | (e3 << 16);
-      }
-      pv_words(A, w, u01, u23, pb0, pb1);
-    }
+    pv_words(A, w, u01, u23, pb0, pb1);
   }
 }
 
@@ -374,37 +424,65 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
   int ohk = 0, ohv = 0;
   if (!PAGED && S > 0) { ohk = p.K.head_start[ch]; ohv = p.V.head_start[ch]; }
 
-  // ---- per-tile metadata of the range, staged once: escape offsets (slot layout) or mode-table entries (paged layout),
-  // so the main loop never waits on a dependent global load
-  int* metak = reinterpret_cast<int*>(smem + TB_META);
-  int* metav = metak + META_TILES;
+  // ---- addressing of this lane, and the copies of the warp's first tile: they are put in flight before the CTA builds its
+  // tables so that the first tile arrives while the tables are written
+  uint8_t* ring = smem + TABLE_BYTES + warp * (NSTAGE * STAGE_BYTES);
+  const u32 ring_s = (u32)__cvta_generic_to_shared(ring);
+  LaneAddr L;
+  L.sm_off = smh + 16 * lane; L.cd_off = cdh + 16 * lane; L.fl_off = rowb * 4 + 16 * (lane & 3);
+  L.ohk = ohk; L.ohv = ohv;
+  L.availk = PAGED ? 0 : (int)min((long)(1 << 30), p.K.ovf_bytes - ohk); L.availv = PAGED ? 0 : (int)min((long)(1 << 30), p.V.ovf_bytes - ohv);
+#if GAAC_SWZ
+  L.kdst = 16 * (32 * (lane & 1) + ((lane >> 1) ^ (4 * (lane & 1)))); L.vdst = 16 * (32 * (lane & 3) + ((lane >> 2) ^ (2 * (lane & 3))));
+#else
+  L.kdst = 16 * (32 * (lane & 1) + (lane >> 1)); L.vdst = 16 * (32 * (lane & 3) + (lane >> 2));
+#endif
+  const int* metak = reinterpret_cast<const int*>(smem + TB_META);
+  const int* metav = metak + META_TILES;
+  auto global_meta = [&](int tile) -> TileMeta {
+    if (PAGED) { const int pc = p.bt[(long)b * p.bt_stride + tile] * (2 * p.n_kv) + 2 * kvh; return TileMeta{p.mt[pc], p.mt[pc + 1]}; }
+    return TileMeta{p.K.tile_off[tileb + tile], p.V.tile_off[tileb + tile]};
+  };
+  auto meta_of = [&](int tile) -> TileMeta {          // valid after the CTA has staged its metadata
+    if (tile - tlo < META_TILES) return TileMeta{metak[tile - tlo], metav[tile - tlo]};
+    return global_meta(tile);
+  };
+  auto esc_k = [&](int mk) -> EscRef {
+    if (PAGED) return EscRef{p.buf + (long)mk * p.TS + SLOT_OVF_OFF, p.ovf_slot};
+    return EscRef{p.K.ovf + ((long)L.ohk + mk), min(ESC_WIN, L.availk - mk)};
+  };
+  auto esc_v = [&](int mv) -> EscRef {
+    if (PAGED) return EscRef{p.buf + (long)mv * p.TS + SLOT_OVF_OFF, p.ovf_slot};
+    return EscRef{p.V.ovf + ((long)L.ohv + mv), min(ESC_WIN, L.availv - mv)};
+  };
+  auto issue_payload = [&](u32 st, int tile, const TileMeta& m) {      // slot layout: needs no metadata
+    if (PAGED) {
+      if (m.mk >= 0) { const uint8_t* sk = p.buf + (long)m.mk * p.TS + 16 * lane; issue_k(st, sk, sk + SLOT_CD_OFF, sk + SLOT_FL_OFF, L, lane); }
+      if (m.mv >= 0) { const uint8_t* sv = p.buf + (long)m.mv * p.TS + 16 * lane; issue_v(st, sv, sv + SLOT_CD_OFF, sv + (SLOT_FL_OFF - 16 * 28), L, lane); }
+    } else {
+      const long so = L.sm_off + (long)tile * TILE_SM, co = L.cd_off + (long)tile * TILE_CD, fo = L.fl_off + (long)tile * (4 * T);
+      issue_k(st, p.K.sm + so, p.K.codes + co, reinterpret_cast<const uint8_t*>(p.K.flags) + fo, L, lane);
+      issue_v(st, p.V.sm + so, p.V.codes + co, reinterpret_cast<const uint8_t*>(p.V.flags) + fo, L, lane);
+    }
+  };
+  auto issue_escapes = [&](u32 st, const TileMeta& m) {
+    if (!PAGED || m.mk >= 0) issue_esc(st + ST_KESC, esc_k(m.mk), lane);
+    if (!PAGED || m.mv >= 0) issue_esc(st + ST_VESC, esc_v(m.mv), lane);
+  };
+  // ---- prologue.  Everything that reads global memory is put in flight first and consumed afterwards: the payload of the
+  // warp's first tile (needs no metadata in the slot layout), the tile's metadata, the metadata of the CTA's range, the
+  // query rows; then the tables are built while those loads travel.
+  int tile = tlo + warp;
+  TileMeta cur{0, 0};
+  if (tile < thi) {
+    if (PAGED) { cur = global_meta(tile); issue_payload(ring_s, tile, cur); }
+    else { issue_payload(ring_s, tile, cur); cur = global_meta(tile); }
+  }
+  int* mk_s = reinterpret_cast<int*>(smem + TB_META);
+  int* mv_s = mk_s + META_TILES;
   const int nstaged = min(thi - tlo, META_TILES);
-  for (int i = tid; i < nstaged; i += ATT_THREADS) {
-    if (PAGED) { const int pc = p.bt[(long)b * p.bt_stride + tlo + i] * (2 * p.n_kv) + 2 * kvh; metak[i] = p.mt[pc]; metav[i] = p.mt[pc + 1]; }
-    else { metak[i] = p.K.tile_off[tileb + tlo + i]; metav[i] = p.V.tile_off[tileb + tlo + i]; }
-  }
-  // ---- CTA tables: escape-byte table, per-lane-class base words {b3lo, b3hi, b4lo-b3lo, b4hi-b3hi} per group, zero pads
-  {
-    const int brow = PAGED ? kvh : ch % p.n_base_rows;
-    const uint8_t* b3k = (PAGED ? p.b3k : p.K.base3) + brow * D; const uint8_t* b4k = (PAGED ? p.b4k : p.K.base4) + brow * D;
-    const uint8_t* b3v = (PAGED ? p.b3v : p.V.base3) + brow * D; const uint8_t* b4v = (PAGED ? p.b4v : p.V.base4) + brow * D;
-    if (tid < 256) fill_lutx(reinterpret_cast<u32x2*>(smem + TB_LUTX), tid);
-    for (int i = tid; i < 4096; i += ATT_THREADS) reinterpret_cast<u32*>(smem + TB_LUTC)[i] = spread_codes4((u32)i);
-    if (tid >= 256 && tid < 272) {                    // K: lane class jj, group gg -> words 2gg, 2gg+1
-      const int t = tid - 256, jj = t >> 2, gg = t & 3; u32 w3[8], w4[8];
-      k_base_words(b3k, jj, w3); k_base_words(b4k, jj, w4);
-      *reinterpret_cast<u32x4*>(smem + TB_KB + 16 * t) = u32x4{w3[2 * gg], w3[2 * gg + 1], w4[2 * gg] - w3[2 * gg], w4[2 * gg + 1] - w3[2 * gg + 1]};
-    } else if (tid >= 288 && tid < 304) {             // V: lane class rr, group gg
-      const int t = tid - 288, rr = t >> 1, gg = t & 1; u32 w3[4], w4[4];
-      v_base_words(b3v, rr, w3); v_base_words(b4v, rr, w4);
-      *reinterpret_cast<u32x4*>(smem + TB_VB + 16 * t) = u32x4{w3[2 * gg], w3[2 * gg + 1], w4[2 * gg] - w3[2 * gg], w4[2 * gg + 1] - w3[2 * gg + 1]};
-    }
-    if (tid >= 320 && tid < 320 + ATT_WARPS * NSTAGE * 2) {      // the 16 zero bytes in front of every escape window
-      const int t = tid - 320, st = t >> 1;
-      *reinterpret_cast<uint4*>(smem + TABLE_BYTES + st * STAGE_BYTES + ((t & 1) ? ST_VZ : ST_KZ)) = make_uint4(0, 0, 0, 0);
-    }
-    if (tid == 0) s_next = tlo + ATT_WARPS;           // tiles tlo .. tlo+W-1 go to warps 0..W-1, the rest is handed out on demand
-  }
+  TileMeta m_first{0, 0};
+  if (tid < nstaged) m_first = global_meta(tlo + tid);
   u32 qa[8][2];
   {
     const bool ok = r < G;
@@ -415,86 +493,121 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       qa[s][1] = ok ? *reinterpret_cast<const u32*>(qp + 16 * s + 2 * j + 8) : 0u;
     }
   }
+  // ---- CTA tables: escape-byte table, code table, per-lane-class base words {b3lo, b3hi, b4lo-b3lo, b4hi-b3hi} per group,
+  // zero pads, per-tile metadata of the range (escape offsets or mode-table entries, so that the main loop never waits on a
+  // dependent global load)
+  {
+    const int brow = PAGED ? kvh : ch % p.n_base_rows;
+    const uint8_t* b3k = (PAGED ? p.b3k : p.K.base3) + brow * D; const uint8_t* b4k = (PAGED ? p.b4k : p.K.base4) + brow * D;
+    const uint8_t* b3v = (PAGED ? p.b3v : p.V.base3) + brow * D; const uint8_t* b4v = (PAGED ? p.b4v : p.V.base4) + brow * D;
+    if (tid >= 256 && tid < 272) {                    // K: lane class jj, group gg -> words 2gg, 2gg+1
+      const int t = tid - 256, jj = t >> 2, gg = t & 3; u32 w3[8], w4[8];
+      k_base_words(b3k, jj, w3); k_base_words(b4k, jj, w4);
+      *reinterpret_cast<u32x4*>(smem + TB_KB + 16 * t) = u32x4{w3[2 * gg], w3[2 * gg + 1], w4[2 * gg] - w3[2 * gg], w4[2 * gg + 1] - w3[2 * gg + 1]};
+    } else if (tid >= 288 && tid < 304) {             // V: lane class rr, group gg
+      const int t = tid - 288, rr = t >> 1, gg = t & 1; u32 w3[4], w4[4];
+      v_base_words(b3v, rr, w3); v_base_words(b4v, rr, w4);
+      *reinterpret_cast<u32x4*>(smem + TB_VB + 16 * t) = u32x4{w3[2 * gg], w3[2 * gg + 1], w4[2 * gg] - w3[2 * gg], w4[2 * gg + 1] - w3[2 * gg + 1]};
+    }
+    if (tid < 256) fill_lutx(reinterpret_cast<u32x2*>(smem + TB_LUTX), tid);
+#if GAAC_LUTC
+    for (int i = tid; i < 4096; i += ATT_THREADS) reinterpret_cast<u32*>(smem + TB_LUTC)[i] = spread_codes4((u32)i);
+#endif
+    if (tid >= 320 && tid < 320 + ATT_WARPS * NSTAGE * 2) {      // the 16 zero bytes in front of every escape window
+      const int t = tid - 320, st = t >> 1;
+      *reinterpret_cast<uint4*>(smem + TABLE_BYTES + st * STAGE_BYTES + ((t & 1) ? ST_VZ : ST_KZ)) = make_uint4(0, 0, 0, 0);
+    }
+    if (tid == 0) s_next = tlo + ATT_WARPS;           // tiles tlo .. tlo+W-1 go to warps 0..W-1, the rest is handed out on demand
+    if (tid < nstaged) { mk_s[tid] = m_first.mk; mv_s[tid] = m_first.mv; }
+    for (int i = tid + ATT_THREADS; i < nstaged; i += ATT_THREADS) { const TileMeta m = global_meta(tlo + i); mk_s[i] = m.mk; mv_s[i] = m.mv; }
+  }
+  if (tile < thi) issue_escapes(ring_s, cur);
+  cp_commit();
   WarpAcc A;
 #pragma unroll
   for (int n = 0; n < 8; n++) A.acc[n][0] = A.acc[n][1] = A.acc[n][2] = A.acc[n][3] = 0.f;
   A.m0 = A.m1 = -CUDART_INF_F; A.l0 = A.l1 = 0.f;
   __syncthreads();
 
-  // ---- tile addressing
-  uint8_t* ring = smem + TABLE_BYTES + warp * (NSTAGE * STAGE_BYTES);
-  const u32 ring_s = (u32)__cvta_generic_to_shared(ring);
-  auto make_ref = [&](int tile, TileRef& tr) {
-    int mk, mv;
-    if (tile - tlo < META_TILES) { mk = metak[tile - tlo]; mv = metav[tile - tlo]; }
-    else if (PAGED) { const int pc = p.bt[(long)b * p.bt_stride + tile] * (2 * p.n_kv) + 2 * kvh; mk = p.mt[pc]; mv = p.mt[pc + 1]; }
-    else { mk = p.K.tile_off[tileb + tile]; mv = p.V.tile_off[tileb + tile]; }
-    if (PAGED) {
-      tr.rawk = mk < 0; tr.rawv = mv < 0;
-      const long pk = tr.rawk ? ~mk : mk, pv = tr.rawv ? ~mv : mv;
-      const uint8_t* sk = p.buf + pk * p.TS; const uint8_t* sv = p.buf + pv * p.TS;
-      tr.ksm = sk; tr.kcd = sk + SLOT_CD_OFF; tr.kfl = sk + SLOT_FL_OFF; tr.kesc = sk + SLOT_OVF_OFF; tr.esc_lim_k = p.ovf_slot;
-      tr.vsm = sv; tr.vcd = sv + SLOT_CD_OFF; tr.vfl = sv + SLOT_FL_OFF; tr.vesc = sv + SLOT_OVF_OFF; tr.esc_lim_v = p.ovf_slot;
-      tr.kraw = p.raw + pk * (T * D); tr.vraw = p.raw + pv * (T * D);
-    } else {
-      tr.rawk = tr.rawv = false;
-      tr.ksm = p.K.sm + smh + (long)tile * TILE_SM; tr.kcd = p.K.codes + cdh + (long)tile * TILE_CD;
-      tr.kfl = reinterpret_cast<const uint8_t*>(p.K.flags + rowb + (long)tile * T);
-      tr.vsm = p.V.sm + smh + (long)tile * TILE_SM; tr.vcd = p.V.codes + cdh + (long)tile * TILE_CD;
-      tr.vfl = reinterpret_cast<const uint8_t*>(p.V.flags + rowb + (long)tile * T);
-      const long ek = (long)ohk + mk, ev = (long)ohv + mv;
-      tr.kesc = p.K.ovf + ek; tr.vesc = p.V.ovf + ev;
-      tr.esc_lim_k = (int)min((long)ESC_WIN, p.K.ovf_bytes - ek); tr.esc_lim_v = (int)min((long)ESC_WIN, p.V.ovf_bytes - ev);
-      tr.kraw = tr.vraw = nullptr;
-    }
-  };
-  auto grab = [&]() -> int {                          // next unassigned tile of the CTA's range (>= thi when none is left)
-    int t = 0;
-    if (lane == 0) t = atomicAdd(&s_next, 1);
-    return __shfl_sync(FULLM, t, 0);
-  };
-
-  // ---- main loop: the warp's first tile is tlo + warp; every further tile is taken from the CTA's counter when its
-  // copies are issued, one tile ahead of its use, so fast and slow warps finish within about one tile of each other
-  int tile = tlo + warp;
-  TileRef cur, nxt;
-  if (tile < thi) { make_ref(tile, cur); issue_tile(ring_s, cur, lane); }
-  cp_commit();
+  // ---- main loop.  The warp's first tile is tlo + warp; every further tile is taken from the CTA's counter while the
+  // current one is being consumed, one tile ahead of its use, so fast and slow warps finish within about one tile of each
+  // other.  The counter is read at the top of the iteration and its value used after the K half, which hides the latency
+  // of the shared-memory atomic; the copies of the next tile are issued between the K half and the V half.
   int stg = 0;
   while (tile < thi) {
-    const int t1 = grab();
-    if (t1 < thi) { make_ref(t1, nxt); issue_tile(ring_s + (stg ^ 1) * STAGE_BYTES, nxt, lane); }
+    int t1 = 0;
+    if (lane == 0) t1 = atomicAdd(&s_next, 1);
+    cp_wait<0>();
+    __syncwarp();
+    const uint8_t* stage = ring + stg * STAGE_BYTES;
+    const int nvalid = min(T, S - tile * T);
+    const bool rawk = PAGED && cur.mk < 0, rawv = PAGED && cur.mv < 0;
+    u32 flrow; int rowoff, total;
+    scan_rows(stage, rawk, rawv, lane, flrow, rowoff, total);
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (!rawk) {
+      const EscRef e = esc_k(cur.mk);
+      const int wsh = (int)(reinterpret_cast<uintptr_t>(e.p) & 3);
+      if (__shfl_sync(FULLM, total, 15) + 8 <= esc_window_bytes(e.p, e.lim))                  // +8: a raw payload is read as two aligned words
+        k_scores<true>(sc, stage, smem, EscSrc<true>{stage + ST_KESC + wsh - ZPAD, nullptr}, flrow, rowoff, lane, qa);
+      else
+        k_scores<false>(sc, stage, smem, EscSrc<false>{nullptr, e.p}, flrow, rowoff, lane, qa);
+    } else {
+      raw_scores(sc, p.raw + (long)(~cur.mk) * (T * D), nvalid, lane, qa);
+    }
+    t1 = __shfl_sync(FULLM, t1, 0);
+    TileMeta nxt{0, 0};
+    if (t1 < thi) {
+      nxt = meta_of(t1);
+      const u32 st = ring_s + (stg ^ 1) * STAGE_BYTES;
+      issue_payload(st, t1, nxt); issue_escapes(st, nxt);
+    }
     cp_commit();
-    cp_wait<1>();
-    __syncwarp();
-    process_tile(A, ring + stg * STAGE_BYTES, smem, cur, min(T, S - tile * T), lane, qa, p.scale_log2);
-    __syncwarp();
+    u32 pb0, pb1;
+    softmax_step(A, sc, p.scale_log2, nvalid, lane, pb0, pb1);
+    if (!rawv) {
+      const EscRef e = esc_v(cur.mv);
+      const int wsh = (int)(reinterpret_cast<uintptr_t>(e.p) & 3);
+      if (__shfl_sync(FULLM, total, 31) + 8 <= esc_window_bytes(e.p, e.lim))
+        v_accum<true>(A, stage, smem, EscSrc<true>{stage + ST_VESC + wsh - ZPAD, nullptr}, flrow, rowoff, lane, pb0, pb1);
+      else
+        v_accum<false>(A, stage, smem, EscSrc<false>{nullptr, e.p}, flrow, rowoff, lane, pb0, pb1);
+    } else {
+      raw_accum(A, p.raw + (long)(~cur.mv) * (T * D), nvalid, lane, pb0, pb1);
+    }
     cur = nxt; stg ^= 1; tile = t1;
   }
   cp_wait<0>();
   // ---- slot layout: the raw BF16 tail belongs to the last split's warp 0
   if (!PAGED && TL > 0 && split == p.nsplit - 1 && warp == 0) {
-    TileRef tr; tr.rawk = tr.rawv = true;
-    tr.kraw = reinterpret_cast<const uint16_t*>(p.K.tail) + (long)ch * p.tail_cap * D;
-    tr.vraw = reinterpret_cast<const uint16_t*>(p.V.tail) + (long)ch * p.tail_cap * D;
+    const uint16_t* kraw = reinterpret_cast<const uint16_t*>(p.K.tail) + (long)ch * p.tail_cap * D;
+    const uint16_t* vraw = reinterpret_cast<const uint16_t*>(p.V.tail) + (long)ch * p.tail_cap * D;
     for (int t0 = 0; t0 < TL; t0 += T) {
-      process_tile(A, ring, smem, tr, min(T, TL - t0), lane, qa, p.scale_log2);
-      tr.kraw += T * D; tr.vraw += T * D;
+      const int nvalid = min(T, TL - t0);
+      float sc[4] = {0.f, 0.f, 0.f, 0.f};
+      raw_scores(sc, kraw, nvalid, lane, qa);
+      u32 pb0, pb1;
+      softmax_step(A, sc, p.scale_log2, nvalid, lane, pb0, pb1);
+      raw_accum(A, vraw, nvalid, lane, pb0, pb1);
+      kraw += T * D; vraw += T * D;
     }
   }
 
   // ---- merge the warps of the CTA (the rings are free now)
   __syncthreads();
+  constexpr int ACC_LD = D + 4;                                  // row stride of the staged accumulators: 4j + r banks, conflict-free stores
   float* sh_m = reinterpret_cast<float*>(smem + TABLE_BYTES);    // [W][8]
   float* sh_l = sh_m + ATT_WARPS * 8;                            // [W][8]
-  float* sh_acc = sh_l + ATT_WARPS * 8;                          // [W][8][128]
+  float* sh_acc = sh_l + ATT_WARPS * 8;                          // [W][8][ACC_LD]
 #pragma unroll
   for (int o = 4; o < 32; o <<= 1) { A.l0 += __shfl_xor_sync(FULLM, A.l0, o); A.l1 += __shfl_xor_sync(FULLM, A.l1, o); }
   if (r == 0) { sh_m[warp * 8 + 2 * j] = A.m0; sh_l[warp * 8 + 2 * j] = A.l0; sh_m[warp * 8 + 2 * j + 1] = A.m1; sh_l[warp * 8 + 2 * j + 1] = A.l1; }
+  if (2 * j < G) {                                               // heads 2j, 2j+1 (the second may be a padding head: stored, never read)
 #pragma unroll
-  for (int n = 0; n < 8; n++) {
-    float* a0 = sh_acc + ((warp * 8 + 2 * j) * D) + 16 * n + r;
-    a0[0] = A.acc[n][0]; a0[D] = A.acc[n][1]; a0[8] = A.acc[n][2]; a0[D + 8] = A.acc[n][3];
+    for (int n = 0; n < 8; n++) {
+      float* a0 = sh_acc + ((warp * 8 + 2 * j) * ACC_LD) + 16 * n + r;
+      a0[0] = A.acc[n][0]; a0[ACC_LD] = A.acc[n][1]; a0[8] = A.acc[n][2]; a0[ACC_LD + 8] = A.acc[n][3];
+    }
   }
   __syncthreads();
   const int NS = p.nsplit;
@@ -509,7 +622,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       for (int w = 0; w < ATT_WARPS; w++) {
         const float mw = sh_m[w * 8 + g];
         const float f = (mw == -CUDART_INF_F) ? 0.f : fast_exp2(mw - M);
-        Lc += sh_l[w * 8 + g] * f; Ac += sh_acc[(w * 8 + g) * D + d] * f;
+        Lc += sh_l[w * 8 + g] * f; Ac += sh_acc[(w * 8 + g) * ACC_LD + d] * f;
       }
       const long qh = (long)b * p.n_q + kvh * G + g, pidx = qh * NS + split;
       if (d == 0) { p.pm[pidx] = M; p.pl[pidx] = Lc; }
@@ -536,6 +649,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     float* c_red = c_ML + 16;                                             // [W][G][128] (NS <= 1024 keeps this inside the ring area)
     const long qh0 = (long)b * p.n_q + kvh * G;
     for (int i = tid; i < G * NS; i += ATT_THREADS) { c_f[i] = __ldcg(p.pm + qh0 * NS + i); c_l[i] = __ldcg(p.pl + qh0 * NS + i); }
+    float4 pre[8];                                                        // split `warp` of every head, in flight while M and L are computed
+#pragma unroll
+    for (int g = 0; g < 8; g++)
+      pre[g] = (g < G && warp < NS) ? __ldcg(reinterpret_cast<const float4*>(p.pa + ((qh0 + g) * NS + warp) * D) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
     __syncthreads();
     if (warp < G) {
       float M = -CUDART_INF_F;
@@ -555,8 +672,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     __syncthreads();
     float4 acc4[8];
 #pragma unroll
-    for (int g = 0; g < 8; g++) acc4[g] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s2 = warp; s2 < NS; s2 += ATT_WARPS) {
+    for (int g = 0; g < 8; g++) {
+      const float f = (g < G && warp < NS) ? c_f[g * NS + warp] : 0.f;
+      acc4[g] = make_float4(pre[g].x * f, pre[g].y * f, pre[g].z * f, pre[g].w * f);
+    }
+    for (int s2 = warp + ATT_WARPS; s2 < NS; s2 += ATT_WARPS) {
 #pragma unroll
       for (int g = 0; g < 8; g++) {
         if (g < G) {
