@@ -44,6 +44,7 @@ _SIGNATURES = {
     "gaac_decode_attn": (i32, [C.POINTER(Side), C.POINTER(Side), vp, vp, i32, i32, i32, vp, i64, f32, i32, vp, i32, i32, vp, sz, vp, vp, vp]),
     "gaac_decode_attn_partial": (i32, [C.POINTER(Side), C.POINTER(Side), vp, vp, i32, i32, i32, vp, i64, f32, i32, vp, i32, i32, vp, sz, vp, vp]),
     "gaac_combine": (i32, [vp, vp, vp, i64, i32, vp, vp, vp]),
+    "gaac_combine_parts": (i32, [vp, i64, i32, vp, vp, vp]),
     "gaac_append_kv": (i32, [C.POINTER(Store), C.POINTER(Store), vp, vp, vp, i32, i32, vp, vp, i64, i64, i32, vp]),
     "gaac_paged_store": (i32, [C.POINTER(Paged), vp, vp, i64, i64, vp, i32, vp, vp]),
     "gaac_paged_release": (i32, [C.POINTER(Paged), vp, i32, vp]),

@@ -727,6 +727,25 @@ __global__ void __launch_bounds__(128) combine_kernel(const float* __restrict__ 
   if (out_f32) out_f32[qh * D + d] = v;
 }
 
+// The same merge over packed partials: parts [n_parts][n_heads][130] = (m in natural-log units, l, acc[128]) per head, the
+// layout an all-gather of the ranks' gaac_decode_attn_partial outputs produces.
+__global__ void __launch_bounds__(128) combine_parts_kernel(const float* __restrict__ parts, long n_heads, int n_parts,
+                                                             uint16_t* __restrict__ out, float* __restrict__ out_f32) {
+  const long qh = blockIdx.x; const int d = threadIdx.x;
+  float M = -CUDART_INF_F;
+  for (int s = 0; s < n_parts; s++) M = fmaxf(M, parts[(s * n_heads + qh) * 130]);
+  float L = 0.f, Ac = 0.f;
+  for (int s = 0; s < n_parts; s++) {
+    const float* pp = parts + (s * n_heads + qh) * 130;
+    const float ms = pp[0];
+    const float f = (ms == -CUDART_INF_F) ? 0.f : __expf(ms - M);
+    L += pp[1] * f; Ac += pp[2 + d] * f;
+  }
+  const float v = L > 0.f ? Ac / L : 0.f;
+  if (out) out[qh * D + d] = __bfloat16_as_ushort(__float2bfloat16(v));
+  if (out_f32) out_f32[qh * D + d] = v;
+}
+
 static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 static int carve_workspace(void* ws, size_t ws_bytes, int B, int n_q, int nsplit, AttnParams& p) {
   const size_t n = (size_t)B * n_q * nsplit;
@@ -798,6 +817,12 @@ extern "C" int gaac_decode_attn_partial(const gaac_side* K, const gaac_side* V, 
 extern "C" int gaac_combine(const float* pm, const float* pl, const float* pa, int64_t n_heads, int n_parts, void* out_bf16, float* out_f32, void* stream) {
   if (!pm || !pl || !pa || n_heads <= 0 || n_parts <= 0 || (!out_bf16 && !out_f32)) return GAAC_E_ARG;
   combine_kernel<<<(unsigned)n_heads, 128, 0, (cudaStream_t)stream>>>(pm, pl, pa, n_parts, (uint16_t*)out_bf16, out_f32);
+  return launch_status();
+}
+
+extern "C" int gaac_combine_parts(const float* parts, int64_t n_heads, int n_parts, void* out_bf16, float* out_f32, void* stream) {
+  if (!parts || n_heads <= 0 || n_parts <= 0 || (!out_bf16 && !out_f32)) return GAAC_E_ARG;
+  combine_parts_kernel<<<(unsigned)n_heads, 128, 0, (cudaStream_t)stream>>>(parts, (long)n_heads, n_parts, (uint16_t*)out_bf16, out_f32);
   return launch_status();
 }
 

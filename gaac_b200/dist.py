@@ -50,12 +50,11 @@ def merge_partials(part: torch.Tensor, group=None, combine_fn=None, out_f32: tor
         gathered = torch.empty(world * part.shape[0], *part.shape[1:], dtype=part.dtype, device=part.device)   # concatenated along dim 0
         dist.all_gather_into_tensor(gathered, part.contiguous(), group=group)
         gathered = gathered.view(world, *part.shape)
-    g = gathered.permute(1, 0, 2)                                   # [n_heads, world, 130]
-    pm, pl, pa = g[:, :, 0].contiguous(), g[:, :, 1].contiguous(), g[:, :, 2:].contiguous()
     if combine_fn is None:
-        from .kernel import combine
-        return combine(pm, pl, pa, out_f32=out_f32)
-    return combine_fn(pm, pl, pa)
+        from .kernel import combine_parts
+        return combine_parts(gathered.contiguous(), out_f32=out_f32)          # one launch on the gathered buffer as it is
+    g = gathered.permute(1, 0, 2)                                   # [n_heads, world, 130]
+    return combine_fn(g[:, :, 0].contiguous(), g[:, :, 1].contiguous(), g[:, :, 2:].contiguous())
 
 
 class ContextSplitAttention:

@@ -120,3 +120,14 @@ def combine(pm: torch.Tensor, pl: torch.Tensor, pa: torch.Tensor, out_f32: torch
     _lib.check(_lib.lib().gaac_combine(pm.contiguous().data_ptr(), pl.contiguous().data_ptr(), pa.contiguous().data_ptr(), n_heads, n_parts,
                                        out.data_ptr(), _lib.ptr(out_f32), _lib.stream_ptr(pm.device)), "gaac_combine")
     return out
+
+
+def combine_parts(parts: torch.Tensor, out_f32: torch.Tensor | None = None) -> torch.Tensor:
+    """Merge packed partials [n_parts, n_heads, 130] fp32 (rows of (m, l, acc[128]), m in natural-log units) -> [n_heads, 128] bf16:
+    the buffer an all-gather of the ranks' partial outputs produces, merged in one launch."""
+    n_parts, n_heads, w = parts.shape
+    assert w == 130 and parts.is_contiguous()
+    out = torch.empty(n_heads, 128, dtype=torch.bfloat16, device=parts.device)
+    _lib.check(_lib.lib().gaac_combine_parts(parts.data_ptr(), n_heads, n_parts, out.data_ptr(), _lib.ptr(out_f32), _lib.stream_ptr(parts.device)),
+               "gaac_combine_parts")
+    return out

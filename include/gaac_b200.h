@@ -93,7 +93,7 @@ size_t gaac_attn_workspace_bytes(int B, int n_q, int nsplit);
  * (slot[b] < 0: padded row, output exactly 0); seq_len[cache head] compressed tokens; tail_len[cache head] raw tail tokens
  * (NULL when there is no tail).  nsplit >= 1 context splits per (row, kv head).  out [B, n_q, 128] bf16; when out_f32 is
  * non-NULL the un-rounded fp32 result is written there as well.  workspace: gaac_attn_workspace_bytes bytes, its first
- * 4*B*n_kv bytes must be zero on the first use and are left zero by every call.  n_base_rows: rows of the base tables
+ * 4*B*n_q bytes (rounded up to 256) must be zero on the first use and are left zero by every call.  n_base_rows: rows of the base tables
  * (cache head h uses row h % n_base_rows).  Replaces gaac_attn_launch = gaac_attn<G> + gaac_tail<G> + gaac_combine<128>
  * (gaac/kernel.py:48-326). */
 int gaac_decode_attn(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
@@ -118,6 +118,11 @@ int gaac_decode_attn_static(const gaac_side* K, const gaac_side* V, const void* 
  * L <= 0; parts with m = -inf are skipped.  Replaces gaac_combine<128> (gaac/kernel.py:281-294); also the merge step of
  * the cross-GPU context split. */
 int gaac_combine(const float* pm, const float* pl, const float* pa, int64_t n_heads, int n_parts, void* out_bf16, float* out_f32, void* stream);
+
+/* gaac_combine over packed partials: parts [n_parts, n_heads, 130] fp32, each row (m, l, acc[128]) as written by
+ * gaac_decode_attn_partial; this is the buffer an all-gather of the ranks' partials produces, so the cross-GPU merge is one
+ * launch with no re-packing.  Same arithmetic as gaac_combine<128> (gaac/kernel.py:281-294). */
+int gaac_combine_parts(const float* parts, int64_t n_heads, int n_parts, void* out_bf16, float* out_f32, void* stream);
 
 /* As gaac_decode_attn, but stops after the per-(row, query head) merge of this GPU's splits and writes the un-normalised
  * partial (m, l, acc[128]) of every query head to part [B*n_q, 130] fp32 instead of the output (context split across

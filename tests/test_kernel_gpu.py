@@ -122,3 +122,8 @@ def test_partial_mode_equals_full_attention():
     combine(allp[:, :, 0].contiguous(), allp[:, :, 1].contiguous(), allp[:, :, 2:].contiguous(), out_f32=o32)
     ref = O.attention_ref(q16[0], k16.transpose(1, 0, 2), v16.transpose(1, 0, 2), SCALE)
     assert np.abs(o32.cpu().numpy() - ref).max() <= attn_tol(ref, v16)
+    # the packed form (what an all-gather of the ranks' partials holds) merges to the same values in one launch
+    from gaac_b200.kernel import combine_parts
+    o32b = torch.empty_like(o32)
+    outb = combine_parts(torch.stack(parts, 0).contiguous(), out_f32=o32b)
+    assert torch.equal(o32b, o32) and outb.shape == (n_kv * G, 128)
