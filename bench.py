@@ -177,6 +177,24 @@ def run_ours(args):
     part = torch.empty(N_Q, 130, dtype=torch.float32, device=dev)
     gathered = torch.empty(world * N_Q, 130, dtype=torch.float32, device=dev)
     ext = _ext()
+    # N > 1: the partials travel by plain stores from the attention kernel's epilogue into every rank's receive buffer
+    # (peer memory); NCCL all-gather + merge kernel is the fallback when the peer mapping cannot be set up on every rank.
+    peer, exchange_mode = None, "none"
+    if world > 1:
+        exchange_mode = "nccl all-gather + merge kernel"
+        ok = 0
+        if not args.nccl_exchange:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")          # plain peer loads/stores only
+            try:
+                from gaac_b200.dist import PeerExchange
+                peer = PeerExchange(N_Q, dev); ok = 1
+            except Exception as e:
+                print(f"[rank {rank}] peer exchange unavailable: {type(e).__name__}: {e}", file=sys.stderr, flush=True)
+        okt = torch.tensor([ok], dtype=torch.int32, device=dev); dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+        if int(okt) == 1:
+            exchange_mode = "partials pushed into peer memory by the attention kernel (NVLink stores) + wait-and-merge kernel"
+        else:
+            peer = None
 
     def layer(i, qq):
         kp, vp = sets[i % N_SETS]
@@ -185,6 +203,9 @@ def run_ours(args):
                   qq.view(N_Q, HEAD_DIM), slots, N_Q, N_KV, SL, S_loc, SCALE, nsplit, ebf, ebf, e32, 0)
         if world == 1:
             return ext.gaac_attn_launch(*common)
+        if peer is not None:
+            ext.gaac_attn_launch(*common, exchange=peer.x)
+            return peer.merge(N_KV)
         ext.gaac_attn_launch(*common, partial=part)
         dist.all_gather_into_tensor(gathered, part)
         return combine_parts(gathered.view(world, N_Q, 130))
@@ -279,13 +300,14 @@ def run_ours(args):
         line = {"metric": "decode_attn_us_per_layer_64k_ctx", "value": us_per_layer, "unit": "us/layer", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
                 "ms_per_step": us_per_layer / 1e3, "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": WORKLOAD, "l2": f"steps rotate over {N_SETS} KV sets ({comp_bytes * N_SETS / 1e6:.0f} MB compressed per rank) larger than L2",
-                           "nsplit": nsplit, "tokens_per_rank": S_loc, "launch": launch_mode, "parallelism": "single GPU" if world == 1 else f"context split x{world}, NCCL all-gather of [32,130] fp32 partials + one merge kernel"},
+                           "nsplit": nsplit, "tokens_per_rank": S_loc, "launch": launch_mode, "parallelism": "single GPU" if world == 1 else f"context split x{world}; {exchange_mode}"},
                 "hbm_gbs_compressed": achieved * (kern_us / us_per_layer) if world == 1 else world * algo_bytes / (us_per_layer * 1e-6) / 1e9,
                 "bf16_equiv_gbs": world * bf16_bytes / (us_per_layer * 1e-6) / 1e9,
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES,
                              "peak_source": which, "algorithmic_bytes_per_launch": algo_bytes, "kernel_us": kern_us, "frac_of_8TBs_nominal": achieved / 8000.0},
                 "e2e": {"value": e2e_us, "unit": "us/layer", "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2},
                 "gpu_launches": launches_per_step * args.steps, "clocks": clk.summary()}
+        if peer is not None: line["config"]["exchange_wait_ran_out"] = peer.error()
         line.update(extras)
         print(json.dumps(line), flush=True)
     finish()
@@ -367,6 +389,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--nccl-exchange", action="store_true", help="N > 1: exchange the partials with an NCCL all-gather instead of peer-memory stores")
     ap.add_argument("--no-graph", action="store_true", help="launch every layer eagerly instead of replaying CUDA graphs")
     ap.add_argument("--profile", action="store_true", help="only the warm-up and the timed steps (no e2e, no side measurements): the command to run under ncu")
     ap.add_argument("--profile-encode", action="store_true", help="only the block encoder on [8, 65536, 128] K and V, --steps times each: the command to run under ncu")

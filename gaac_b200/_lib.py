@@ -31,6 +31,11 @@ class Paged(C.Structure):
                 ("b3k", vp), ("b4k", vp), ("b3v", vp), ("b4v", vp), ("n_kv", i32), ("TS", i32), ("ovf_slot", i32)]
 
 
+class Exchange(C.Structure):
+    """gaac_exchange"""
+    _fields_ = [("recv", vp), ("flags", vp), ("epoch", vp), ("ticket", vp), ("err", vp), ("rank", i32), ("world", i32)]
+
+
 _SIGNATURES = {
     "gaac_status_string": (C.c_char_p, [i32]),
     "gaac_abi_version": (i32, []),
@@ -45,6 +50,8 @@ _SIGNATURES = {
     "gaac_decode_attn_partial": (i32, [C.POINTER(Side), C.POINTER(Side), vp, vp, i32, i32, i32, vp, i64, f32, i32, vp, i32, i32, vp, sz, vp, vp]),
     "gaac_combine": (i32, [vp, vp, vp, i64, i32, vp, vp, vp]),
     "gaac_combine_parts": (i32, [vp, i64, i32, vp, vp, vp]),
+    "gaac_decode_attn_push": (i32, [C.POINTER(Side), C.POINTER(Side), vp, vp, i32, i32, i32, vp, i64, f32, i32, vp, i32, i32, vp, sz, C.POINTER(Exchange), vp]),
+    "gaac_exchange_merge": (i32, [C.POINTER(Exchange), i64, i32, vp, vp, vp]),
     "gaac_append_kv": (i32, [C.POINTER(Store), C.POINTER(Store), vp, vp, vp, i32, i32, vp, vp, i64, i64, i32, vp]),
     "gaac_paged_store": (i32, [C.POINTER(Paged), vp, vp, i64, i64, vp, i32, vp, vp]),
     "gaac_paged_release": (i32, [C.POINTER(Paged), vp, i32, vp]),

@@ -69,6 +69,9 @@ struct AttnParams {
   const uint16_t* q; int B, n_q, n_kv, G; float scale_log2; int nsplit;
   int* counters; float* pm; float* pl; float* pa;
   uint16_t* out; float* out_f32; float* part;
+  // cross-GPU exchange (x_recv == NULL: unused): the partial of every query head is stored into every rank's receive
+  // buffer, then the rank's arrival counter on every rank is raised once per (row, kv head)
+  float* const* x_recv; int* const* x_flags; const int* x_epoch; int x_rank, x_world;
 };
 
 __device__ __forceinline__ void mma16816(float* c, const u32* a, u32 b0, u32 b1) {
@@ -697,7 +700,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       for (int w = 0; w < ATT_WARPS; w++) Ac += c_red[(w * 8 + g) * D + d];
       const float M = c_ML[2 * g], L = c_ML[2 * g + 1];
       const long qh = qh0 + g;
-      if (p.part) {                                  // un-normalised partial for a cross-GPU merge: m in natural-log units
+      if (p.x_recv) {                                // the same partial, pushed to every rank's receive buffer over NVLink
+        const int par = __ldcg(p.x_epoch) & 1;
+        const long row = ((long)(par * p.x_world + p.x_rank) * p.B * p.n_q + qh) * 130;
+        for (int rk = 0; rk < p.x_world; rk++) {
+          float* o = p.x_recv[rk] + row;
+          if (d == 0) { o[0] = M * LN2; o[1] = L; }
+          o[2 + d] = Ac;
+        }
+      } else if (p.part) {                           // un-normalised partial for a cross-GPU merge: m in natural-log units
         float* o = p.part + qh * 130;
         if (d == 0) { o[0] = M * LN2; o[1] = L; }
         o[2 + d] = Ac;
@@ -707,6 +718,57 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
         if (p.out_f32) p.out_f32[qh * D + d] = v;
       }
     }
+    if (p.x_recv) {                                  // the stores above must be visible on the peers before the counter moves
+      __threadfence_system();
+      __syncthreads();
+      if (tid < p.x_world) atomicAdd_system(p.x_flags[tid] + p.x_rank, 1);
+    }
+  }
+}
+
+// Second half of the cross-GPU exchange: wait until every rank's partials of this exchange have arrived in this GPU's
+// receive buffer, merge them, and advance the exchange counter.  One CTA per query head.  Every wait is bounded: after
+// X_WAIT_LIMIT polls (about a second) the kernel sets *err, writes zeros and returns, so a missing peer never hangs the GPU.
+constexpr int X_WAIT_LIMIT = 4000000;
+__global__ void __launch_bounds__(128) exchange_merge_kernel(float* const* x_recv, int* const* x_flags, int* epoch, int* ticket, int* err, int rank, int world,
+                                                              int groups, long n_heads, uint16_t* __restrict__ out, float* __restrict__ out_f32) {
+  __shared__ int ok_s;
+  const long qh = blockIdx.x; const int d = threadIdx.x;
+  const int ep = *reinterpret_cast<volatile int*>(epoch);               // advanced only after every CTA has taken its ticket
+  const int expected = (ep + 1) * groups;
+  if (d == 0) ok_s = 1;
+  __syncthreads();
+  if (d < world) {
+    const int* f = x_flags[rank] + d;
+    for (int it = 0;; it++) {
+      int v;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if (v - expected >= 0) break;
+      if (it >= X_WAIT_LIMIT) { ok_s = 0; atomicExch(err, 1); break; }
+      __nanosleep(200);
+    }
+  }
+  __syncthreads();
+  float v = 0.f;
+  if (ok_s) {
+    const float* base = x_recv[rank] + (long)(ep & 1) * world * n_heads * 130;
+    float M = -CUDART_INF_F;
+    for (int s = 0; s < world; s++) M = fmaxf(M, __ldcg(base + (s * n_heads + qh) * 130));
+    float L = 0.f, Ac = 0.f;
+    for (int s = 0; s < world; s++) {
+      const float* pp = base + (s * n_heads + qh) * 130;
+      const float ms = __ldcg(pp);
+      const float f = (ms == -CUDART_INF_F) ? 0.f : __expf(ms - M);
+      L += __ldcg(pp + 1) * f; Ac += __ldcg(pp + 2 + d) * f;
+    }
+    v = L > 0.f ? Ac / L : 0.f;
+  }
+  if (out) out[qh * D + d] = __bfloat16_as_ushort(__float2bfloat16(v));
+  if (out_f32) out_f32[qh * D + d] = v;
+  __syncthreads();
+  if (d == 0) {
+    __threadfence();
+    if (atomicAdd(ticket, 1) == (int)gridDim.x - 1) { *ticket = 0; __threadfence(); atomicAdd(epoch, 1); }
   }
 }
 
@@ -769,8 +831,9 @@ static int launch_attn(const AttnParams& p, cudaStream_t st) {
 
 static int slot_attn(const gaac_side* K, const gaac_side* V, const void* q, const int32_t* slot, int B, int n_q, int n_kv, const int32_t* seq_len,
                      int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap, int n_base_rows, void* ws, size_t ws_bytes,
-                     void* out, float* out_f32, float* part, void* stream) {
-  if (!K || !V || !q || !slot || !seq_len || (!out && !part)) return GAAC_E_ARG;
+                     void* out, float* out_f32, float* part, void* stream, const gaac_exchange* x = nullptr) {
+  if (!K || !V || !q || !slot || !seq_len || (!out && !part && !x)) return GAAC_E_ARG;
+  if (x && (!x->recv || !x->flags || !x->epoch || !x->ticket || !x->err || x->world < 1 || x->world > 64 || x->rank < 0 || x->rank >= x->world)) return GAAC_E_ARG;
   if (B <= 0 || n_q <= 0 || n_kv <= 0 || nsplit <= 0 || nsplit > 1024 || S_pad <= 0 || S_pad % T || n_base_rows <= 0) return GAAC_E_ARG;
   if (n_q % n_kv || n_q / n_kv < 1 || n_q / n_kv > 8) return GAAC_E_UNSUPPORTED;
   for (const gaac_side* s : {K, V}) {
@@ -784,6 +847,7 @@ static int slot_attn(const gaac_side* K, const gaac_side* V, const void* q, cons
   p.K = *K; p.V = *V; p.slot = slot; p.seq_len = seq_len; p.tail_len = tail_len; p.tail_cap = tail_cap; p.S_pad = S_pad; p.n_base_rows = n_base_rows;
   p.q = (const uint16_t*)q; p.B = B; p.n_q = n_q; p.n_kv = n_kv; p.G = n_q / n_kv; p.scale_log2 = scale * LOG2E; p.nsplit = nsplit;
   p.out = (uint16_t*)out; p.out_f32 = out_f32; p.part = part;
+  if (x) { p.x_recv = x->recv; p.x_flags = x->flags; p.x_epoch = x->epoch; p.x_rank = x->rank; p.x_world = x->world; }
   if (int e = carve_workspace(ws, ws_bytes, B, n_q, nsplit, p)) return e;
   return launch_attn<false>(p, (cudaStream_t)stream);
 }
@@ -817,6 +881,22 @@ extern "C" int gaac_decode_attn_partial(const gaac_side* K, const gaac_side* V, 
 extern "C" int gaac_combine(const float* pm, const float* pl, const float* pa, int64_t n_heads, int n_parts, void* out_bf16, float* out_f32, void* stream) {
   if (!pm || !pl || !pa || n_heads <= 0 || n_parts <= 0 || (!out_bf16 && !out_f32)) return GAAC_E_ARG;
   combine_kernel<<<(unsigned)n_heads, 128, 0, (cudaStream_t)stream>>>(pm, pl, pa, n_parts, (uint16_t*)out_bf16, out_f32);
+  return launch_status();
+}
+
+extern "C" int gaac_decode_attn_push(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
+                                     const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
+                                     int n_base_rows, void* workspace, size_t workspace_bytes, const gaac_exchange* x, void* stream) {
+  if (!x) return GAAC_E_ARG;
+  return slot_attn(K, V, q_bf16, slot, B, n_q, n_kv, seq_len, S_pad, scale, nsplit, tail_len, tail_cap, n_base_rows, workspace, workspace_bytes,
+                   nullptr, nullptr, nullptr, stream, x);
+}
+
+extern "C" int gaac_exchange_merge(const gaac_exchange* x, int64_t n_heads, int groups, void* out_bf16, float* out_f32, void* stream) {
+  if (!x || !x->recv || !x->flags || !x->epoch || !x->ticket || !x->err || x->world < 1 || x->world > 64 || x->rank < 0 || x->rank >= x->world) return GAAC_E_ARG;
+  if (n_heads <= 0 || groups <= 0 || (!out_bf16 && !out_f32)) return GAAC_E_ARG;
+  exchange_merge_kernel<<<(unsigned)n_heads, 128, 0, (cudaStream_t)stream>>>(x->recv, x->flags, x->epoch, x->ticket, x->err, x->rank, x->world, groups,
+                                                                             (long)n_heads, (uint16_t*)out_bf16, out_f32);
   return launch_status();
 }
 

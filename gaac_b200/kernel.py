@@ -50,11 +50,12 @@ class _Ext:
 
     @staticmethod
     def gaac_attn_launch(smk, ck, fk, tok, ovk, ohsk, b3k, b4k, smv, cv, fv, tov, ovv, ohsv, b3v, b4v,
-                         q, slot, n_q, n_kv, SL, S_pad, scale, nsplit, kt, vt, TL, TCAP, out_f32=None, partial=None):
+                         q, slot, n_q, n_kv, SL, S_pad, scale, nsplit, kt, vt, TL, TCAP, out_f32=None, partial=None, exchange=None):
         """Same positional arguments as the reference launcher (gaac/kernel.py:296-300): 16 K/V buffers, q [B*n_q, 128] bf16,
         slot int32 [B], n_q, n_kv, SL int32 [heads], S_pad, scale, nsplit, K/V tails [heads, TCAP, 128] bf16 (empty = none),
         TL int32 [heads], TCAP.  Returns out [B*n_q, 128] bf16.  Extras: out_f32 (fp32 tensor to receive the un-rounded
-        result), partial ([B*n_q, 130] fp32 tensor: write (m, l, acc) there instead of the output)."""
+        result), partial ([B*n_q, 130] fp32 tensor: write (m, l, acc) there instead of the output), exchange (a
+        gaac_b200._lib.Exchange: push the partial rows into every rank's receive buffer instead; returns None)."""
         D = 128
         if q.size(-1) != D:
             raise RuntimeError("head_dim must be 128")
@@ -72,6 +73,9 @@ class _Ext:
         L = _lib.lib()
         common = (K, V, q.data_ptr(), slot.data_ptr(), B, n_q, n_kv, SL.data_ptr(), S_pad, float(scale), int(nsplit),
                   TL.data_ptr() if has_tail else None, int(TCAP) if has_tail else 0, b3k.size(0), ws.data_ptr(), ws.numel())
+        if exchange is not None:
+            _lib.check(L.gaac_decode_attn_push(*common, exchange, _lib.stream_ptr(dev)), "gaac_decode_attn_push")
+            return None
         if partial is not None:
             _lib.check(L.gaac_decode_attn_partial(*common, partial.data_ptr(), _lib.stream_ptr(dev)), "gaac_decode_attn_partial")
             return partial

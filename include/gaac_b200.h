@@ -132,6 +132,37 @@ int gaac_decode_attn_partial(const gaac_side* K, const gaac_side* V, const void*
                              const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
                              int n_base_rows, void* workspace, size_t workspace_bytes, float* part, void* stream);
 
+/* Cross-GPU context split without a collective library on the data path: one process per GPU, every rank's receive buffer
+ * and arrival counters mapped into every rank's address space (peer memory over NVLink).  No counterpart in the reference,
+ * which is single-GPU.
+ *   recv[r]  : rank r's receive buffer, 2 * world * n_heads * 130 floats (two exchanges deep, indexed by the parity of the
+ *              exchange counter, then by sending rank, then by query head)
+ *   flags[r] : rank r's arrival counters, int[world], zero before the first exchange, never reset (they count (row, kv head)
+ *              groups received from each rank since the start)
+ *   epoch, ticket, err : this rank's own device ints, zero before the first exchange; epoch counts finished exchanges and must
+ *              advance in step on all ranks (every rank makes the same sequence of calls); err becomes 1 when a wait ran out
+ * recv and flags are DEVICE arrays of `world` pointers. */
+typedef struct {
+  float* const* recv;
+  int32_t* const* flags;
+  int32_t* epoch;
+  int32_t* ticket;
+  int32_t* err;
+  int rank, world;
+} gaac_exchange;
+
+/* gaac_decode_attn_partial whose last CTA of every (row, kv head) stores its partial rows straight into every rank's
+ * receive buffer (plain stores over NVLink, a system-scope fence, then one system-scope add per rank on the arrival counter):
+ * the exchange rides on the attention kernel's epilogue, there is no separate send. */
+int gaac_decode_attn_push(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
+                          const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
+                          int n_base_rows, void* workspace, size_t workspace_bytes, const gaac_exchange* x, void* stream);
+
+/* Wait (bounded: about one second, then *err = 1 and a zero output) until the partials of all ranks for the current
+ * exchange have arrived, merge them as gaac_combine does and advance the exchange counter.  n_heads = B * n_q,
+ * groups = B * n_kv of the matching gaac_decode_attn_push.  Launch it on the stream of the push, after it. */
+int gaac_exchange_merge(const gaac_exchange* x, int64_t n_heads, int groups, void* out_bf16, float* out_f32, void* stream);
+
 /* ---------------------------------------------------------------------------------------------- slot cache (layout A) append */
 
 /* Mutable side of the slot cache (gaac/kv_cache.py:99-119). */

@@ -127,3 +127,59 @@ def test_partial_mode_equals_full_attention():
     o32b = torch.empty_like(o32)
     outb = combine_parts(torch.stack(parts, 0).contiguous(), out_f32=o32b)
     assert torch.equal(o32b, o32) and outb.shape == (n_kv * G, 128)
+
+
+def _half_pages(n_kv, S, seed):
+    import torch
+    from gaac_b200 import Codec, TileEncoder
+    k16, v16 = O.synth_kv("k", n_kv, S, seed), O.synth_kv("v", n_kv, S, seed)
+    k, v = to_bf16_cuda(k16), to_bf16_cuda(v16)
+    ck, cv = Codec(n_kv).calibrate(k), Codec(n_kv).calibrate(v)
+    halves = []
+    for lo, hi in ((0, S // 2), (S // 2, S)):
+        halves.append((TileEncoder("k").encode(ck, k[:, lo:hi].contiguous()), TileEncoder("v").encode(cv, v[:, lo:hi].contiguous()), hi - lo))
+    return k16, v16, halves
+
+
+def test_peer_exchange_two_ranks_on_one_gpu():
+    """Fused exchange (gaac_decode_attn_push + gaac_exchange_merge) with both ranks' buffers on one GPU: every push is launched
+    before any merge, so no kernel ever waits for another launch.  Three exchanges in a row use both buffer parities."""
+    import torch
+    from gaac_b200.kernel import _ext
+    from gaac_b200.dist import PeerExchange
+    n_kv, G, S = 2, 4, 2048
+    n_q = n_kv * G
+    k16, v16, halves = _half_pages(n_kv, S, 3)
+    bufs = [PeerExchange.local_buffer(2, n_q, "cuda") for _ in range(2)]
+    xs = [PeerExchange.local(bufs, r, n_q) for r in range(2)]
+    slots = torch.zeros(1, dtype=torch.int32, device="cuda")
+    e = torch.empty(0, dtype=torch.int32, device="cuda"); eq = torch.empty(0, dtype=torch.bfloat16, device="cuda")
+    rng = np.random.default_rng(5)
+    for step in range(3):
+        q16 = O.f32_to_bf16(rng.standard_normal((1, n_q, 128)).astype(np.float32))
+        q = to_bf16_cuda(q16)
+        for r, (kp, vp, n) in enumerate(halves):
+            SL = torch.full((n_kv,), n, dtype=torch.int32, device="cuda")
+            _ext().gaac_attn_launch(kp.sm, kp.codes, kp.flags, kp.tile_off, kp.ovf, kp.ovf_head_start, kp.base3, kp.base4,
+                                    vp.sm, vp.codes, vp.flags, vp.tile_off, vp.ovf, vp.ovf_head_start, vp.base3, vp.base4,
+                                    q.reshape(-1, 128), slots, n_q, n_kv, SL, n, SCALE, 4, eq, eq, e, 0, exchange=xs[r].x)
+        o32 = [torch.empty(n_q, 128, dtype=torch.float32, device="cuda") for _ in range(2)]
+        outs = [xs[r].merge(n_kv, out_f32=o32[r]) for r in range(2)]
+        ref = O.attention_ref(q16[0], k16.transpose(1, 0, 2), v16.transpose(1, 0, 2), SCALE)
+        for r in range(2):
+            assert np.abs(o32[r].cpu().numpy() - ref).max() <= attn_tol(ref, v16)
+            assert not xs[r].error()
+        assert torch.equal(o32[0], o32[1]) and torch.equal(outs[0], outs[1])
+
+
+def test_peer_exchange_wait_runs_out():
+    """A merge whose peers never push gives up after its bounded wait: error flag set, output zero, GPU still usable."""
+    import torch
+    from gaac_b200.dist import PeerExchange
+    n_q = 8
+    bufs = [PeerExchange.local_buffer(2, n_q, "cuda") for _ in range(2)]
+    x = PeerExchange.local(bufs, 0, n_q)
+    out = x.merge(2)
+    assert x.error()
+    assert (out == 0).all()
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0
