@@ -37,29 +37,45 @@ __global__ void __launch_bounds__(ENC_WARPS * 32) encode_tiles_kernel(
   }
 }
 
-// Exclusive prefix of tile_bytes per head.  One CTA per head.
-__global__ void __launch_bounds__(256) tile_scan_kernel(const int* __restrict__ tile_bytes, int ntiles, int* __restrict__ tile_off,
-                                                         long tile_off_stride, int* __restrict__ head_bytes) {
-  __shared__ int wsum[8];
-  __shared__ int carry_s;
+// Exclusive prefix of tile_bytes per head.  One CTA of 1024 threads per head, four tiles per thread and pass: a 64K-token
+// head (4096 tiles) is one pass of two warp scans.
+constexpr int SCAN_THREADS = 1024;
+__global__ void __launch_bounds__(SCAN_THREADS) tile_scan_kernel(const int* __restrict__ tile_bytes, int ntiles, int* __restrict__ tile_off,
+                                                                  long tile_off_stride, int* __restrict__ head_bytes) {
+  __shared__ int wsum[32];
+  __shared__ int carry_s, pass_total;
   const long h = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) carry_s = 0;
   __syncthreads();
-  for (int base = 0; base < ntiles; base += 256) {
-    const int i = base + tid;
-    const int v = i < ntiles ? tile_bytes[h * ntiles + i] : 0;
-    int inc = v;
+  for (int base = 0; base < ntiles; base += 4 * SCAN_THREADS) {
+    const int i0 = base + 4 * tid;
+    int v[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) v[k] = i0 + k < ntiles ? tile_bytes[h * ntiles + i0 + k] : 0;
+    const int s = v[0] + v[1] + v[2] + v[3];
+    int inc = s;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) { int u = __shfl_up_sync(FULL, inc, d); if (lane >= d) inc += u; }
     if (lane == 31) wsum[warp] = inc;
     __syncthreads();
-    int woff = 0;
-    for (int w = 0; w < warp; w++) woff += wsum[w];
-    const int carry = carry_s;
-    if (i < ntiles) tile_off[h * tile_off_stride + i] = carry + woff + inc - v;
+    if (warp == 0) {
+      const int w = wsum[lane];
+      int winc = w;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) { int u = __shfl_up_sync(FULL, winc, d); if (lane >= d) winc += u; }
+      wsum[lane] = winc - w;                         // exclusive prefix over the warps
+      if (lane == 31) pass_total = winc;
+    }
     __syncthreads();
-    if (tid == 255) carry_s = carry + woff + inc;
+    int off = carry_s + wsum[warp] + inc - s;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      if (i0 + k < ntiles) tile_off[h * tile_off_stride + i0 + k] = off;
+      off += v[k];
+    }
+    __syncthreads();
+    if (tid == 0) carry_s += pass_total;
     __syncthreads();
   }
   if (tid == 0 && head_bytes) head_bytes[h] = carry_s;
@@ -217,7 +233,7 @@ extern "C" int gaac_compact(const uint8_t* slots, const int32_t* tile_bytes, int
   if (head_start && (!ovf || !slots)) return GAAC_E_ARG;
   if (ovf_off && (!head_start || !flags || S <= 0 || S_pad < S)) return GAAC_E_ARG;
   cudaStream_t st = (cudaStream_t)stream;
-  tile_scan_kernel<<<(unsigned)H, 256, 0, st>>>(tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_bytes);
+  tile_scan_kernel<<<(unsigned)H, SCAN_THREADS, 0, st>>>(tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_bytes);
   if (head_start) {
     const long n_items = H * ntiles;
     compact_copy_kernel<<<(unsigned)((n_items + 3) / 4), 128, 0, st>>>(slots, tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_start, ovf, n_items,
