@@ -1,0 +1,79 @@
+"""Time the UNMODIFIED reference package on this GPU, beside gaac_b200, on bench.py's workload (config 1).
+
+The reference is installed, as it is, under baseline/_ref (`pip install --no-deps --target baseline/_ref <reference checkout>`)
+and its JIT extension `gaac_attn_v1` is prebuilt for sm_100a under baseline/_ref/_torch_ext (TORCH_CUDA_ARCH_LIST=10.0a), so
+that nothing is compiled with nvcc on the GPU box; its Triton encoder compiles there in seconds.  Both directories are
+git-ignored.  This script runs the reference through its own public API (Codec.calibrate, TileEncoder.encode, attention) and
+prints one JSON line: microseconds per layer of its CUDA kernel (its own nsplit heuristic, and the best of a small sweep),
+milliseconds per encode of its Triton encoder, and two live parity checks against gaac_b200 on the same tensors.
+bench.py runs it in a child process as a side measurement; it is not part of any timed region of gaac_b200.
+"""
+import json, os, sys, time
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.path.join(HERE, "_ref")
+os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
+os.environ.setdefault("TORCH_EXTENSIONS_DIR", os.path.join(REF, "_torch_ext"))
+sys.path.insert(0, REF)
+sys.path.insert(1, os.path.dirname(HERE))
+
+N_Q, N_KV, CTX, HEAD_DIM, N_SETS = 32, 8, 65536, 128, 4
+
+
+def main():
+    import torch
+    import gaac as ref                                           # the reference package
+    import gaac_b200 as ours
+    from gaac_b200.synth import synth_kv
+    dev = torch.device("cuda", 0)
+    scale = HEAD_DIM ** -0.5
+    out = {"reference_version": getattr(ref, "__version__", "0.1.0")}
+    sets, enc_ms = [], []
+    for i in range(N_SETS):
+        k = synth_kv("k", N_KV, CTX, seed=100 + i, device=dev); v = synth_kv("v", N_KV, CTX, seed=100 + i, device=dev)
+        ck, cv = ref.Codec(N_KV, device=dev).calibrate(k[:, :2048]), ref.Codec(N_KV, device=dev).calibrate(v[:, :2048])
+        tk, tv = ref.TileEncoder("k", device=dev), ref.TileEncoder("v", device=dev)
+        kp, vp = tk.encode(ck, k), tv.encode(cv, v)              # first call compiles the Triton kernels
+        if i == 0:
+            for _ in range(3): tk.encode(ck, k)
+            torch.cuda.synchronize()
+            for _ in range(9):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(); tk.encode(ck, k); b.record(); torch.cuda.synchronize(); enc_ms.append(a.elapsed_time(b))
+            # encoder parity, full size: gaac_b200's encoder on the same tensor and bases
+            oc = ours.Codec(N_KV, dev); oc.set_bases(ck.base3, ck.base4)
+            op = ours.TileEncoder("k", dev).encode(oc, k)
+            out["encoder_bit_identical"] = bool(all(torch.equal(getattr(op, f), getattr(kp, f)) for f in ("sm", "codes", "flags", "tile_off", "ovf_head_start"))
+                                                and torch.equal(op.ovf[:int(op.ovf_head_start[-1])], kp.ovf[:int(kp.ovf_head_start[-1])]))
+        sets.append((kp, vp)); del k, v
+    out["triton_encode_ms"] = sorted(enc_ms)[len(enc_ms) // 2]
+    out["triton_encode_blocks_per_s"] = N_KV * (CTX // 16) / (out["triton_encode_ms"] * 1e-3)
+    q = torch.randn(1, N_Q, HEAD_DIM, generator=torch.Generator(device=dev).manual_seed(7), device=dev).to(torch.bfloat16)
+
+    def timed(fn, n=200, warm=20):
+        for i in range(warm): fn(i)
+        torch.cuda.synchronize(); ts = []
+        for i in range(n):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(); fn(i); b.record(); torch.cuda.synchronize(); ts.append(a.elapsed_time(b) * 1e3)
+        return sorted(ts)[len(ts) // 2]
+
+    t0 = time.time()
+    o_ref = ref.attention(q, *sets[0], scale=scale)              # loads (or builds) the reference's CUDA extension
+    torch.cuda.synchronize()
+    out["extension_load_s"] = time.time() - t0
+    o_ours = ours.attention(q, *sets[0], scale=scale)            # gaac_b200 reading the reference's Pages: the drop-in claim
+    out["attn_max_abs_diff_vs_gaac_b200"] = float((o_ref.float() - o_ours.float()).abs().max())
+    ns0 = ref.choose_nsplit(1, N_KV, CTX)
+    res = {}
+    for ns in sorted({ns0, 18, 36, 48}):
+        res[ns] = timed(lambda i: ref.attention(q, *sets[i % N_SETS], scale=scale, nsplit=ns))
+    out["attn_us_by_nsplit"] = res
+    out["attn_us_own_nsplit"] = res[ns0]; out["own_nsplit"] = ns0
+    out["attn_us_best"] = min(res.values())
+    out["gaac_b200_us_same_protocol"] = timed(lambda i: ours.attention(q, *sets[i % N_SETS], scale=scale))
+    print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

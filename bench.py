@@ -380,7 +380,25 @@ def side_measurements(torch, dev, sets, q, args) -> dict:
         out["bf16_kv_decode_library"] = {"name": name, "us": sorted(ts)[len(ts) // 2] * 1e3}
     except Exception as e:
         out["bf16_kv_decode_library"] = {"error": repr(e)}
+    # the reference's own CUDA kernel and Triton encoder on this GPU (unmodified package under baseline/_ref, child process)
+    out["reference_cuda_kernel"] = reference_kernel_side_number()
     return out
+
+
+def reference_kernel_side_number() -> dict:
+    script = os.path.join(ROOT, "baseline", "run_reference_kernel.py")
+    if not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "gaac")):
+        return {"unavailable": "the reference package is not installed under baseline/_ref on this box"}
+    try:
+        r = subprocess.run([sys.executable, script], capture_output=True, text=True, timeout=300)
+        lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
+        if r.returncode != 0 or not lines:
+            return {"unavailable": f"reference run failed (rc {r.returncode}): " + (r.stderr.strip().splitlines() or ["no output"])[-1][:300]}
+        return json.loads(lines[-1])
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "reference run did not finish in 300 s"}
+    except Exception as e:
+        return {"unavailable": repr(e)}
 
 
 def main():
