@@ -219,9 +219,10 @@ def run_ours(args):
     for i in range(max(3, args.warmup)):
         layer(i, q)
     barrier()
-    # One CUDA graph per KV set (attention, and for N > 1 the all-gather and the merge): the launch path of a decode loop,
-    # which the reference's serving engine also captures.  Host launch cost then stays below the kernel time at every N.
-    graphs, launch_mode = None, "eager"
+    # CUDA graphs: the launch path of a decode loop, which the reference's serving engine also captures.  One graph holds
+    # N_SETS consecutive layers (the kernels carry programmatic-dependent-launch edges, so a layer's CTAs become resident while
+    # the previous layer's split merge is finishing); single-layer graphs cover steps % N_SETS.
+    graphs, g_all, launch_mode = None, None, "eager"
     if not (args.profile or args.no_graph):
         try:
             graphs = []
@@ -230,33 +231,39 @@ def run_ours(args):
                 with torch.cuda.graph(g_):
                     o_ = layer(i, q)
                 graphs.append((g_, o_))
-            launch_mode = "cuda graph replay, one layer per graph"
+            g_all = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_all):
+                o_all = [layer(i, q) for i in range(N_SETS)]
+            launch_mode = f"cuda graph replay, {N_SETS} layers per graph"
         except Exception as e:                                                          # capture unsupported: same on every rank
-            graphs = None; launch_mode = f"eager (graph capture failed: {type(e).__name__})"
+            graphs = g_all = None; launch_mode = f"eager (graph capture failed: {type(e).__name__})"
         barrier()
 
-    def step(i):
+    def run_steps(n, events=None):
+        """Exactly n layer steps."""
         if graphs is None:
-            return layer(i, q)
-        graphs[i % N_SETS][0].replay()
-        return graphs[i % N_SETS][1]
-    for i in range(3): step(i)
+            for i in range(n):
+                if events: events[i][0].record()
+                layer(i, q)
+                if events: events[i][1].record()
+            return
+        for _ in range(n // N_SETS): g_all.replay()
+        for i in range(n % N_SETS): graphs[i][0].replay()
+    run_steps(2 * N_SETS + 1)
     barrier()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)] if graphs is None else None
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clk:
         t0.record()
-        for i in range(args.steps):
-            ev[i][0].record(); step(i); ev[i][1].record()
+        run_steps(args.steps, ev)
         t1.record()
         barrier()
         # keep the GPU busy a little longer so the 100 ms sampler sees the loaded clocks (the same number of calls on every
-        # rank: the calls contain a collective when N > 1)
-        for i in range(0 if args.profile else 4000):
-            step(i)
+        # rank: the calls contain an exchange when N > 1)
+        if not args.profile: run_steps(4000)
         torch.cuda.synchronize()
     total_ms = t0.elapsed_time(t1)
-    kern_ms = sorted(a.elapsed_time(b) for a, b in ev)
+    kern_ms = sorted(a.elapsed_time(b) for a, b in ev) if ev else [total_ms / args.steps]   # graph mode: device time per layer of the replayed region
     if world > 1:
         tt = torch.tensor([total_ms], dtype=torch.float64, device=dev); dist.all_reduce(tt, op=dist.ReduceOp.MAX); total_ms = float(tt)
     us_per_layer = total_ms / args.steps * 1e3
@@ -303,7 +310,7 @@ def run_ours(args):
                            "nsplit": nsplit, "tokens_per_rank": S_loc, "launch": launch_mode, "parallelism": "single GPU" if world == 1 else f"context split x{world}; {exchange_mode}"},
                 "hbm_gbs_compressed": achieved * (kern_us / us_per_layer) if world == 1 else world * algo_bytes / (us_per_layer * 1e-6) / 1e9,
                 "bf16_equiv_gbs": world * bf16_bytes / (us_per_layer * 1e-6) / 1e9,
-                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES,
+                "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES * S_loc / CTX,
                              "peak_source": which, "algorithmic_bytes_per_launch": algo_bytes, "kernel_us": kern_us, "frac_of_8TBs_nominal": achieved / 8000.0},
                 "e2e": {"value": e2e_us, "unit": "us/layer", "h2d_bytes_per_step": q_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2},
                 "gpu_launches": launches_per_step * args.steps, "clocks": clk.summary()}

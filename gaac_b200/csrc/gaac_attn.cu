@@ -412,6 +412,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
   const int bh = blockIdx.x, split = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, j = lane & 3, r = lane >> 2;
   const int b = bh / p.n_kv, kvh = bh % p.n_kv, G = p.G;
 
+  // ---- programmatic dependent launch: the grid is launched with stream serialisation relaxed, so its CTAs can be made
+  // resident while the previous kernel of the stream is still finishing (its split merge runs on a few SMs only).  Nothing
+  // is read before that kernel has completed; the next kernel of the stream may be staged behind this one right away (it
+  // cannot become resident before this grid's CTAs leave their SMs).  Both instructions are no-ops in a plain launch.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::);
+
   // ---- which cache head, how many tokens, this CTA's tile range [tlo, thi)
   int S, ch = 0, TL = 0;
   if (PAGED) { S = p.seq_len[b]; }
@@ -734,6 +741,8 @@ __global__ void __launch_bounds__(128) exchange_merge_kernel(float* const* x_rec
                                                               int groups, long n_heads, uint16_t* __restrict__ out, float* __restrict__ out_f32) {
   __shared__ int ok_s;
   const long qh = blockIdx.x; const int d = threadIdx.x;
+  asm volatile("griddepcontrol.wait;" ::: "memory");                   // resident early, runs after the attention kernel has completed
+  asm volatile("griddepcontrol.launch_dependents;" ::);
   const int ep = *reinterpret_cast<volatile int*>(epoch);               // advanced only after every CTA has taken its ticket
   const int expected = (ep + 1) * groups;
   if (d == 0) ok_s = 1;
@@ -824,8 +833,13 @@ static int carve_workspace(void* ws, size_t ws_bytes, int B, int n_q, int nsplit
 template <bool PAGED>
 static int launch_attn(const AttnParams& p, cudaStream_t st) {
   cudaFuncSetAttribute(decode_attn_kernel<PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
-  dim3 grid((unsigned)(p.B * p.n_kv), (unsigned)p.nsplit);
-  decode_attn_kernel<PAGED><<<grid, ATT_THREADS, ATT_SMEM, st>>>(p);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(p.B * p.n_kv), (unsigned)p.nsplit); cfg.blockDim = dim3(ATT_THREADS);
+  cfg.dynamicSmemBytes = ATT_SMEM; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, decode_attn_kernel<PAGED>, p) != cudaSuccess) { cudaGetLastError(); return GAAC_E_LAUNCH; }
   return launch_status();
 }
 
@@ -895,8 +909,13 @@ extern "C" int gaac_decode_attn_push(const gaac_side* K, const gaac_side* V, con
 extern "C" int gaac_exchange_merge(const gaac_exchange* x, int64_t n_heads, int groups, void* out_bf16, float* out_f32, void* stream) {
   if (!x || !x->recv || !x->flags || !x->epoch || !x->ticket || !x->err || x->world < 1 || x->world > 64 || x->rank < 0 || x->rank >= x->world) return GAAC_E_ARG;
   if (n_heads <= 0 || groups <= 0 || (!out_bf16 && !out_f32)) return GAAC_E_ARG;
-  exchange_merge_kernel<<<(unsigned)n_heads, 128, 0, (cudaStream_t)stream>>>(x->recv, x->flags, x->epoch, x->ticket, x->err, x->rank, x->world, groups,
-                                                                             (long)n_heads, (uint16_t*)out_bf16, out_f32);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)n_heads); cfg.blockDim = dim3(128); cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, exchange_merge_kernel, x->recv, x->flags, x->epoch, x->ticket, x->err, x->rank, x->world, groups,
+                         (long)n_heads, (uint16_t*)out_bf16, out_f32) != cudaSuccess) { cudaGetLastError(); return GAAC_E_LAUNCH; }
   return launch_status();
 }
 
