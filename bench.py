@@ -338,6 +338,70 @@ def run_encode_only(args):
     print(json.dumps({"profile_encode": out}), flush=True)
 
 
+def run_other_workload(args):
+    """Secondary workloads on one GPU (not the headline line): `batch64` = one GPU's share of BASELINE config 4 (64 sequences x
+    1 kv head, GQA 8, 32768-token contexts, slot layout); `paged16` = BASELINE config 2's attention (16 sequences, contexts
+    uniform in [4096, 65536] + a 0-15 token filling block, 32 q / 8 kv heads, paged layout, seeded random block table)."""
+    import numpy as np, torch
+    from gaac_b200 import Codec, TileEncoder, attention
+    from gaac_b200.kernel import choose_nsplit_sm100
+    from gaac_b200.synth import synth_kv
+    dev = torch.device("cuda", 0)
+
+    def timed(fn):
+        for i in range(max(3, args.warmup)): fn(i)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(args.steps): fn(i)
+        b.record(); torch.cuda.synchronize()
+        return a.elapsed_time(b) / args.steps * 1e3
+
+    if args.workload == "batch64":
+        B, S, G = 64, 32768, 8
+        sets = []
+        for i in range(2):                                                  # two KV sets of 0.8 GB: every step streams from HBM
+            k = synth_kv("k", 8, S, 300 + i, dev).repeat(8, 1, 1); v = synth_kv("v", 8, S, 300 + i, dev).repeat(8, 1, 1)
+            ck, cv = Codec(1, dev).calibrate(k[:1, :2048]), Codec(1, dev).calibrate(v[:1, :2048])
+            sets.append((TileEncoder("k", dev).encode(ck, k), TileEncoder("v", dev).encode(cv, v))); del k, v
+        q = torch.randn(B, G, 128, device=dev).to(torch.bfloat16)
+        nbytes = sets[0][0].nbytes + sets[0][1].nbytes; ns = choose_nsplit_sm100(B, 1, S)
+        us = timed(lambda i: attention(q, *sets[i % 2], nsplit=ns))
+        desc = "64 sequences x 1 kv head x 8 q heads, 32768-token contexts, slot layout (one GPU's share of config 4)"
+    else:
+        from gaac_b200.vllm.store import LayerState, OVF_OFF
+        from gaac_b200.vllm.paged_kernel import paged_attention
+        n_kv, G, B = 8, 4, 16
+        rng = np.random.default_rng(0)
+        lens = [int(l) // 16 * 16 + int(t) for l, t in zip(rng.integers(4096, 65537, B), rng.integers(0, 16, B))]
+        num_blocks = sum((l + 15) // 16 for l in lens) + 1024
+        cal_k, cal_v = synth_kv("k", n_kv, 2048, 7, dev), synth_kv("v", n_kv, 2048, 7, dev)
+        ck, cv = Codec(n_kv, dev).calibrate(cal_k), Codec(n_kv, dev).calibrate(cal_v)
+        st = LayerState(num_blocks, n_kv, raw_tiles=B * 2 * n_kv + 4096, ovf_slot=128, device=dev,
+                        bases={"k3": ck.base3.cpu(), "k4": ck.base4.cpu(), "v3": cv.base3.cpu(), "v4": cv.base4.cpu()})
+        buf = torch.zeros(num_blocks * 2 * n_kv * (OVF_OFF + 128), dtype=torch.uint8, device=dev)
+        perm = rng.permutation(num_blocks); used = 0
+        bt = np.zeros((B, (max(lens) + 15) // 16), np.int32)
+        for i, L in enumerate(lens):
+            k = synth_kv("k", n_kv, L, 7, dev).transpose(0, 1).contiguous(); v = synth_kv("v", n_kv, L, 7, dev).transpose(0, 1).contiguous()
+            nb = (L + 15) // 16
+            blocks = perm[used:used + nb]; used += nb; bt[i, :nb] = blocks
+            ent = np.array([[blocks[t], t * 16, 0, min(16, L - t * 16)] for t in range(nb)], np.int32)
+            st.store(k, v, buf, torch.from_numpy(ent).to(dev), torch.empty(nb * 2 * n_kv, dtype=torch.int32, device=dev))
+        btd = torch.from_numpy(bt).to(dev); sl = torch.tensor(lens, dtype=torch.int32, device=dev)
+        q = torch.randn(B, n_kv * G, 128, device=dev).to(torch.bfloat16)
+        out = torch.empty(B, n_kv * G * 128, dtype=torch.bfloat16, device=dev)
+        full, part = sum(l // 16 for l in lens), sum(l % 16 for l in lens)
+        nbytes = full * 2 * n_kv * (2880 + 53) + part * 2 * n_kv * 256      # slot payload + mean escape bytes; filling blocks are raw BF16
+        ns = choose_nsplit_sm100(B, n_kv, bt.shape[1] * 16, ragged=True)
+        us = timed(lambda i: paged_attention(q, out, buf, st.raw, st.mt, btd, sl, st.bases, st.TS, n_kv * G, n_kv, ns))
+        desc = f"16 sequences, contexts 4096..65536 (+0..15 filling tokens, {sum(lens)} tokens in all), 32 q / 8 kv heads, paged layout, random block table"
+    peak, which = measured_peak_gbs()
+    print(json.dumps({"metric": "decode_attn_us_per_layer", "workload": args.workload, "value": us, "unit": "us/layer", "n_gpus": 1, "steps": args.steps,
+                      "config": {"workload": desc, "nsplit": ns}, "compressed_mb": nbytes / 1e6,
+                      "roofline": {"bound": "hbm", "achieved": nbytes / us / 1e3, "peak": peak, "unit": "GB/s", "frac": nbytes / us / 1e3 / peak, "peak_source": which}}), flush=True)
+
+
 def side_measurements(torch, dev, sets, q, args) -> dict:
     """Numbers reported beside the headline (outside its timed region): the CPU baseline on a bounded sample, the encoder's
     throughput, and a library BF16-KV decode (flash-attn / SDPA) at the same shape for context."""
@@ -414,11 +478,15 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="config1", choices=["config1", "batch64", "paged16"], help="config1 = the headline line; the others print a one-GPU line for a secondary workload")
     ap.add_argument("--nccl-exchange", action="store_true", help="N > 1: exchange the partials with an NCCL all-gather instead of peer-memory stores")
     ap.add_argument("--no-graph", action="store_true", help="launch every layer eagerly instead of replaying CUDA graphs")
     ap.add_argument("--profile", action="store_true", help="only the warm-up and the timed steps (no e2e, no side measurements): the command to run under ncu")
     ap.add_argument("--profile-encode", action="store_true", help="only the block encoder on [8, 65536, 128] K and V, --steps times each: the command to run under ncu")
     args = ap.parse_args()
+    if args.workload != "config1":
+        run_other_workload(args)
+        return
     if args.profile_encode:
         run_encode_only(args)
     elif args.impl == "reference":

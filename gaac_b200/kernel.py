@@ -29,15 +29,28 @@ def choose_nsplit(B: int, n_kv: int, S: int, target_ctas: int = 96, min_tok: int
     return min(max(1, target_ctas // (B * n_kv)), max(1, S // min_tok), cap)
 
 
-def choose_nsplit_sm100(B: int, n_kv: int, S: int, sm_count: int = SM_COUNT_B200, min_tiles_per_warp: int = 2) -> int:
-    """Splits per (row, kv head) for a B200.  The kernel runs one 16-warp CTA per SM, so the grid B*n_kv*nsplit should fill
-    the SMs in one wave without spilling into a second one, while every warp of a CTA keeps at least min_tiles_per_warp
-    16-token tiles so the per-CTA prologue and merge stay amortised."""
+def choose_nsplit_sm100(B: int, n_kv: int, S: int, sm_count: int = SM_COUNT_B200, min_tiles_per_warp: int = 2, ragged: bool = False) -> int:
+    """Splits per (row, kv head) for a B200.  The kernel runs one 16-warp CTA per SM.
+
+    Few rows (B*n_kv up to half the SMs): fill the SMs in one wave, while every warp of a CTA keeps at least
+    min_tiles_per_warp 16-token tiles so the per-CTA prologue and merge stay amortised.
+    Many rows: the grid runs in several waves.  With equal lengths (S is every row's length) the split count minimises
+    waves x (tiles per CTA / 16 warps x tile time + per-CTA fixed cost); with ragged lengths (S is the longest row,
+    ragged=True) CTAs of about 512 tiles at the longest row let the block scheduler even out the rows."""
     rows = max(1, B * n_kv)
     ntiles = max(1, (S + 15) // 16)
-    want = max(1, sm_count // rows)
     most = max(1, ntiles // (ATT_WARPS * min_tiles_per_warp))
-    return max(1, min(want, most))
+    if 2 * rows <= sm_count:
+        return max(1, min(sm_count // rows, most))
+    if ragged:
+        return max(1, min(-(-ntiles // 512), most))
+    tile_us, fixed_us, best, best_t = 4.4, 10.0, 1, None              # measured: time of one tile pair in a full CTA, prologue + merges
+    for ns in range(1, min(most, 32) + 1):
+        waves = -(-rows * ns // sm_count)
+        t = waves * (-(-ntiles // ns) / ATT_WARPS * tile_us + fixed_us)
+        if best_t is None or t < best_t * 0.97:                        # prefer fewer splits unless clearly better
+            best, best_t = ns, t
+    return best
 
 
 def _side(sm, codes, flags, tile_off, ovf, head_start, base3, base4, tail) -> _lib.Side:

@@ -70,3 +70,16 @@ def test_cpu_tensors_are_refused():
     with pytest.raises(RuntimeError, match="no CPU path"):
         from gaac_b200.codec import exponent_hist
         exponent_hist(x, 2)
+
+
+def test_split_count_heuristics():
+    """choose_nsplit keeps the reference's values; choose_nsplit_sm100 fills 148 SMs in one wave for few rows, bounds the
+    tiles per warp from below, and switches to the wave model / ragged rule when the rows alone exceed half the SMs."""
+    from gaac_b200.kernel import choose_nsplit, choose_nsplit_sm100
+    assert choose_nsplit(1, 8, 65536) == 12 and choose_nsplit(16, 8, 65536) == 1 and choose_nsplit(1, 8, 1024) == 2   # gaac/kernel.py:340-342
+    assert choose_nsplit_sm100(1, 8, 65536) == 18           # 144 CTAs
+    assert choose_nsplit_sm100(1, 8, 8192) == 16            # at least two tiles per warp
+    assert choose_nsplit_sm100(1, 1, 100) == 1
+    assert choose_nsplit_sm100(64, 1, 32768) == 2           # one wave of 128 CTAs
+    assert choose_nsplit_sm100(16, 8, 65536, ragged=True) == 8
+    assert choose_nsplit_sm100(256, 8, 4096) == 1
