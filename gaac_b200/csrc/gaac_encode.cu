@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(256) head_prefix_kernel(const int* __restrict_
 __global__ void __launch_bounds__(128) compact_copy_kernel(const uint8_t* __restrict__ slots, const int* __restrict__ tile_bytes, int ntiles,
                                                             const int* __restrict__ tile_off, long tile_off_stride,
                                                             const int* __restrict__ head_start, uint8_t* __restrict__ ovf, long n_items,
-                                                            const int* __restrict__ flags, long S, long S_pad, int* __restrict__ ovf_off) {
+                                                            const int* __restrict__ flags, long S, long S_pad, int* __restrict__ ovf_off, int zero_pad) {
   const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (item >= n_items) return;
   const int lane = threadIdx.x & 31;
@@ -121,6 +121,7 @@ __global__ void __launch_bounds__(128) compact_copy_kernel(const uint8_t* __rest
   const uint8_t* src = slots + item * (long)TILE_MAX_ESC;
   uint8_t* dst = ovf + (long)head_start[h] + toff;
   for (int i = lane; i < n; i += 32) dst[i] = src[i];
+  if (zero_pad && item == 0 && lane < zero_pad) ovf[(long)head_start[n_items / ntiles] + lane] = 0;     // over-read padding behind the last head
   if (ovf_off) {
     const long row = t * T + (lane & 15);
     const int sz = (lane < T && row < S) ? row_esc_bytes((u32)flags[h * S_pad + row]) : 0;
@@ -237,8 +238,30 @@ extern "C" int gaac_compact(const uint8_t* slots, const int32_t* tile_bytes, int
   if (head_start) {
     const long n_items = H * ntiles;
     compact_copy_kernel<<<(unsigned)((n_items + 3) / 4), 128, 0, st>>>(slots, tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_start, ovf, n_items,
-                                                                    flags, S, S_pad, ovf_off);
+                                                                    flags, S, S_pad, ovf_off, 0);
   }
+  return launch_status();
+}
+
+extern "C" int gaac_encode_begin(const void* x_bf16, int64_t H, int64_t S, int64_t S_in, int64_t S_pad,
+                                 const uint8_t* base3, const uint8_t* base4, const int32_t* bidx, int n_kv, int kind,
+                                 uint8_t* sm, uint8_t* codes, int32_t* flags, uint8_t* slots, int32_t* tile_bytes,
+                                 int32_t* tile_off, int32_t* head_bytes, int32_t* head_start, void* stream) {
+  if (!tile_off || !head_bytes || !head_start) return GAAC_E_ARG;
+  if (int e = gaac_encode_tiles(x_bf16, H, S, S_in, S_pad, base3, base4, bidx, n_kv, kind, sm, codes, flags, slots, tile_bytes, stream)) return e;
+  const int64_t ntiles = (S + T - 1) / T;
+  if (int e = gaac_compact(nullptr, tile_bytes, H, ntiles, nullptr, nullptr, tile_off, ntiles, head_bytes, nullptr, 0, 0, nullptr, stream)) return e;
+  return gaac_head_prefix(head_bytes, H, head_start, stream);
+}
+
+extern "C" int gaac_compact_copy(const uint8_t* slots, const int32_t* tile_bytes, int64_t H, int64_t ntiles, const int32_t* head_start, uint8_t* ovf,
+                                 const int32_t* tile_off, int64_t tile_off_stride, const int32_t* flags, int64_t S, int64_t S_pad, int32_t* ovf_off,
+                                 int zero_pad, void* stream) {
+  if (!slots || !tile_bytes || !head_start || !ovf || !tile_off || H <= 0 || ntiles <= 0 || tile_off_stride < ntiles || zero_pad < 0 || zero_pad > 32) return GAAC_E_ARG;
+  if (ovf_off && (!flags || S <= 0 || S_pad < S)) return GAAC_E_ARG;
+  const long n_items = H * ntiles;
+  compact_copy_kernel<<<(unsigned)((n_items + 3) / 4), 128, 0, (cudaStream_t)stream>>>(slots, tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_start, ovf,
+                                                                                       n_items, flags, S, S_pad, ovf_off, zero_pad);
   return launch_status();
 }
 

@@ -76,16 +76,29 @@ class TileEncoder:
 
     def encode(self, codec: Codec, x: torch.Tensor) -> Page:
         """x: [H, S, D] bf16 -> Page, bit-identical to the reference Codec.encode(x, kind).  (gaac/encoder.py:111-123)"""
+        if not x.is_cuda:
+            raise RuntimeError("TileEncoder needs CUDA tensors: gaac_b200 has no CPU path")
         H, S, _ = x.shape; dev = x.device
         S_pad = (S + T - 1) // T * T
+        ntiles = S_pad // T
+        x = x.contiguous()
+        L = _lib.lib(); st = _lib.stream_ptr(dev)
+        # every buffer whose size is known is allocated before the one host synchronisation, so the GPU never waits for the host
         sm = torch.empty(H, S_pad * D, dtype=torch.uint8, device=dev)
         cd = torch.empty(H, S_pad * CB, dtype=torch.uint8, device=dev)
         flags = torch.empty(H, S_pad, dtype=torch.int32, device=dev)          # every row of every tile is written, padded rows as 0
-        tile_bytes = self.encode_tiles(x, codec.base3, codec.base4, sm, cd, flags, S, S_pad, codec.n_kv)
-        _, head_bytes = self.tile_offsets(tile_bytes)
-        head_start = torch.empty(H + 1, dtype=torch.int32, device=dev)
-        _lib.check(_lib.lib().gaac_head_prefix(head_bytes.data_ptr(), H, head_start.data_ptr(), _lib.stream_ptr(dev)), "gaac_head_prefix")
-        ovf = torch.zeros(int(head_start[-1]) + 8, dtype=torch.uint8, device=dev)     # host sync: sizes the escape stream
+        meta = torch.empty(2 * H * ntiles + 2 * H + 1, dtype=torch.int32, device=dev)
+        tile_bytes, tile_off = meta[:H * ntiles].view(H, ntiles), meta[H * ntiles:2 * H * ntiles].view(H, ntiles)
+        head_bytes, head_start = meta[2 * H * ntiles:2 * H * ntiles + H], meta[2 * H * ntiles + H:]
         ovf_off = torch.empty(H, S, dtype=torch.int32, device=dev)
-        tile_off = self.compact(tile_bytes, head_start, ovf, flags, S, S_pad, ovf_off)
+        if H == 0 or ntiles == 0:
+            head_start.zero_()
+            return Page(sm, cd, flags, ovf_off, torch.zeros(8, dtype=torch.uint8, device=dev), head_start, tile_off, codec.base3, codec.base4, H, S, codec.n_kv, self.kind)
+        slots = self._scratch(H * ntiles * SLOT, dev)
+        _lib.check(L.gaac_encode_begin(x.data_ptr(), H, S, x.shape[1], S_pad, codec.base3.data_ptr(), codec.base4.data_ptr(), None, codec.n_kv,
+                                       0 if self.kind == "k" else 1, sm.data_ptr(), cd.data_ptr(), flags.data_ptr(), slots.data_ptr(),
+                                       tile_bytes.data_ptr(), tile_off.data_ptr(), head_bytes.data_ptr(), head_start.data_ptr(), st), "gaac_encode_begin")
+        ovf = torch.empty(int(head_start[-1]) + 8, dtype=torch.uint8, device=dev)     # host sync: sizes the escape stream exactly, as the reference does
+        _lib.check(L.gaac_compact_copy(slots.data_ptr(), tile_bytes.data_ptr(), H, ntiles, head_start.data_ptr(), ovf.data_ptr(), tile_off.data_ptr(), ntiles,
+                                       flags.data_ptr(), S, S_pad, ovf_off.data_ptr(), 8, st), "gaac_compact_copy")
         return Page(sm, cd, flags, ovf_off, ovf, head_start, tile_off, codec.base3, codec.base4, H, S, codec.n_kv, self.kind)

@@ -52,6 +52,22 @@ int gaac_compact(const uint8_t* slots, const int32_t* tile_bytes, int64_t H, int
                  const int32_t* head_start, uint8_t* ovf, int32_t* tile_off, int64_t tile_off_stride, int32_t* head_bytes,
                  const int32_t* flags, int64_t S, int64_t S_pad, int32_t* ovf_off, void* stream);
 
+/* TileEncoder.encode up to the point where the host must size the escape stream, in one call: gaac_encode_tiles, the prefix
+ * sums of gaac_compact (tile_off [H, ntiles] contiguous, head_bytes [H]) and gaac_head_prefix (head_start [H+1]).  The caller
+ * reads head_start[H], allocates ovf of that many bytes (+ padding) and finishes with gaac_compact_copy.  Same reference lines
+ * as the three entry points it chains (gaac/encoder.py:94-121). */
+int gaac_encode_begin(const void* x_bf16, int64_t H, int64_t S, int64_t S_in, int64_t S_pad,
+                      const uint8_t* base3, const uint8_t* base4, const int32_t* bidx, int n_kv, int kind,
+                      uint8_t* sm, uint8_t* codes, int32_t* flags, uint8_t* slots, int32_t* tile_bytes,
+                      int32_t* tile_off, int32_t* head_bytes, int32_t* head_start, void* stream);
+
+/* The copy half of gaac_compact with tile offsets that are already known: scratch slots -> ovf + head_start[h] + tile_off[h, t],
+ * optionally the per-row offsets ovf_off [H, S], and zero_pad (0..32) zero bytes written behind the last head (the reference
+ * allocates its stream with 8 bytes of over-read padding, gaac/encoder.py:121).  Replaces _compact (gaac/encoder.py:69-76). */
+int gaac_compact_copy(const uint8_t* slots, const int32_t* tile_bytes, int64_t H, int64_t ntiles, const int32_t* head_start, uint8_t* ovf,
+                      const int32_t* tile_off, int64_t tile_off_stride, const int32_t* flags, int64_t S, int64_t S_pad, int32_t* ovf_off,
+                      int zero_pad, void* stream);
+
 /* head_start[0..H] = exclusive prefix of head_bytes[0..H-1] (int32).  Replaces the head-level cumsum of
  * TileEncoder.encode (gaac/encoder.py:119-120). */
 int gaac_head_prefix(const int32_t* head_bytes, int64_t H, int32_t* head_start, void* stream);
