@@ -116,14 +116,17 @@ GAAC_HD u32 pack_hi5(u32 e4) {
 // Encode one group of 8 stored positions given its exponent bytes (elements 0-3 in e_lo, 4-7 in e_hi) and the bases.
 // Returns the tier tag (0, 1, 3); codes24 = 8 x 3-bit codes; esc = escape payload (1 byte for tier 1, 40 bits for tier 2).
 GAAC_HD u32 encode_group(u32 e_lo, u32 e_hi, u32 b3_lo, u32 b3_hi, u32 b4_lo, u32 b4_hi, u32& codes24, u64& esc) {
-  u32 d3l = sub_bytes(e_lo, b3_lo), d3h = sub_bytes(e_hi, b3_hi);
-  if (((d3l | d3h) & 0xF8F8F8F8u) == 0) {
-    codes24 = pack_codes4(d3l) | (pack_codes4(d3h) << 12); esc = 0; return 0u;
-  }
-  u32 d4l = sub_bytes(e_lo, b4_lo), d4h = sub_bytes(e_hi, b4_hi);
-  if (((d4l | d4h) & 0xF0F0F0F0u) == 0) {
-    codes24 = pack_codes4(d4l & 0x07070707u) | (pack_codes4(d4h & 0x07070707u) << 12);
-    esc = pack_bit4(d4l) | (pack_bit4(d4h) << 4); return 1u;
+  // Both windows are tried up front and the tier is picked with selects: in a warp some lane nearly always needs the 4-bit
+  // window, so a branch per tier would run both paths one after the other.  Only the raw tier (under 1 %) branches.
+  const u32 d3l = sub_bytes(e_lo, b3_lo), d3h = sub_bytes(e_hi, b3_hi);
+  const u32 d4l = sub_bytes(e_lo, b4_lo), d4h = sub_bytes(e_hi, b4_hi);
+  const bool t0 = ((d3l | d3h) & 0xF8F8F8F8u) == 0;
+  const bool t1 = ((d4l | d4h) & 0xF0F0F0F0u) == 0;
+  if (t0 | t1) {
+    const u32 cl = t0 ? d3l : (d4l & 0x07070707u), ch = t0 ? d3h : (d4h & 0x07070707u);
+    codes24 = pack_codes4(cl) | (pack_codes4(ch) << 12);
+    esc = t0 ? 0u : (pack_bit4(d4l) | (pack_bit4(d4h) << 4));
+    return t0 ? 0u : 1u;
   }
   codes24 = pack_codes4(e_lo & 0x07070707u) | (pack_codes4(e_hi & 0x07070707u) << 12);
   esc = (u64)pack_hi5(e_lo) | ((u64)pack_hi5(e_hi) << 20); return 3u;
