@@ -1,7 +1,7 @@
 """Time the UNMODIFIED reference package on this GPU, beside gaac_b200, on bench.py's workload (config 1).
 
 The reference is installed, as it is, under baseline/_ref (`pip install --no-deps --target baseline/_ref <reference checkout>`)
-and its JIT extension `gaac_attn_v1` is prebuilt for sm_100a under baseline/_ref/_torch_ext (TORCH_CUDA_ARCH_LIST=10.0a), so
+and its JIT extension `gaac_attn_v1` is prebuilt for sm_100a under baseline/_ref/_torch_ext by build_reference.py, so
 that nothing is compiled with nvcc on the GPU box; its Triton encoder compiles there in seconds.  Both directories are
 git-ignored.  This script runs the reference through its own public API (Codec.calibrate, TileEncoder.encode, attention) and
 prints one JSON line: microseconds per layer of its CUDA kernel (its own nsplit heuristic, and the best of a small sweep),
@@ -12,8 +12,40 @@ import json, os, sys, time
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REF = os.path.join(HERE, "_ref")
+
+
+def _extension_dir() -> str:
+    """The prebuilt extension's directory, spelled as it was when it was built (see build_reference.py)."""
+    ext = os.path.join(REF, "_torch_ext")
+    try:
+        built_as = open(os.path.join(ext, "BUILD_DIR")).read().strip()
+        if built_as and os.path.realpath(built_as) == os.path.realpath(ext):
+            ext = built_as
+    except OSError:
+        pass
+    return ext
+
+
+def _preload_extension(ref_kernel) -> bool:
+    """Hand the prebuilt gaac_attn_v1.so to the reference's loader cache (gaac/kernel.py:329-337 keeps the loaded module in `_mod`).
+    torch's JIT loader would rebuild it (over a minute of nvcc) because a copied tree does not keep the file times ninja logged;
+    the library is the reference's own kernel, compiled from its own source by its own build step, only that step is not
+    repeated.  Returns False (and the reference then builds it itself) when the library is not there or does not load."""
+    so = os.path.join(os.environ["TORCH_EXTENSIONS_DIR"], "gaac_attn_v1", "gaac_attn_v1.so")
+    try:
+        import importlib.machinery, importlib.util
+        import torch  # noqa: F401  (the extension links against libtorch)
+        loader = importlib.machinery.ExtensionFileLoader("gaac_attn_v1", so)
+        mod = importlib.util.module_from_spec(importlib.util.spec_from_loader("gaac_attn_v1", loader))
+        loader.exec_module(mod)
+        ref_kernel._mod = mod
+        return True
+    except Exception:
+        return False
+
+
 os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
-os.environ.setdefault("TORCH_EXTENSIONS_DIR", os.path.join(REF, "_torch_ext"))
+os.environ.setdefault("TORCH_EXTENSIONS_DIR", _extension_dir())
 sys.path.insert(0, REF)
 sys.path.insert(1, os.path.dirname(HERE))
 
@@ -59,6 +91,8 @@ def main():
         return sorted(ts)[len(ts) // 2]
 
     t0 = time.time()
+    import gaac.kernel as ref_kernel
+    out["extension_preloaded"] = _preload_extension(ref_kernel)
     o_ref = ref.attention(q, *sets[0], scale=scale)              # loads (or builds) the reference's CUDA extension
     torch.cuda.synchronize()
     out["extension_load_s"] = time.time() - t0
