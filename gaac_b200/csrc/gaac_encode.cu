@@ -159,15 +159,22 @@ __global__ void __launch_bounds__(ENC_WARPS * 32) decode_page_kernel(
 
 // Exponent histogram: x [N, n_ch] bf16, hist [n_ch, 256] int64.  grid = (ceil(n_ch/128), row chunks); a thread owns one
 // channel and keeps a private 256-bin histogram of 16-bit counters in shared memory, flushed with atomics.
-constexpr int HIST_ROWS = 2048;       // rows per CTA (16-bit counters cannot overflow)
+constexpr int HIST_ROWS = 64;         // rows per CTA: short chunks put hundreds of CTAs on a 2048-token calibration sample (16-bit counters cannot overflow)
 __global__ void __launch_bounds__(128) exponent_hist_kernel(const uint16_t* __restrict__ x, long N, long n_ch, unsigned long long* __restrict__ hist) {
   extern __shared__ unsigned short bins[];           // [256][128]: bin-major so a warp's increments spread over banks
   const int tid = threadIdx.x;
   const long c = (long)blockIdx.x * 128 + tid;
   for (int b = 0; b < 256; b++) bins[b * 128 + tid] = 0;
   const long r0 = (long)blockIdx.y * HIST_ROWS, r1 = min(N, r0 + HIST_ROWS);
-  if (c < n_ch)
-    for (long r = r0; r < r1; r++) bins[((x[r * n_ch + c] >> 7) & 0xFF) * 128 + tid]++;
+  if (c < n_ch) {
+    long r = r0;
+    for (; r + 4 <= r1; r += 4) {                       // four independent loads in flight per thread
+      const unsigned a0 = x[r * n_ch + c], a1 = x[(r + 1) * n_ch + c], a2 = x[(r + 2) * n_ch + c], a3 = x[(r + 3) * n_ch + c];
+      bins[((a0 >> 7) & 0xFF) * 128 + tid]++; bins[((a1 >> 7) & 0xFF) * 128 + tid]++;
+      bins[((a2 >> 7) & 0xFF) * 128 + tid]++; bins[((a3 >> 7) & 0xFF) * 128 + tid]++;
+    }
+    for (; r < r1; r++) bins[((x[r * n_ch + c] >> 7) & 0xFF) * 128 + tid]++;
+  }
   if (c < n_ch)
     for (int b = 0; b < 256; b++) {
       unsigned v = bins[b * 128 + tid];
