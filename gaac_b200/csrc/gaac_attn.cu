@@ -35,19 +35,39 @@ namespace gaac {
 #ifndef GAAC_LUTC
 #define GAAC_LUTC 1
 #endif
+#ifndef GAAC_BULK
+#define GAAC_BULK 1
+#endif
 #ifndef GAAC_SWZ
 #define GAAC_SWZ 1
 #endif
 constexpr int ATT_WARPS = 16;
 constexpr int ATT_THREADS = ATT_WARPS * 32;
 constexpr int NSTAGE = 2;
-constexpr int ESC_WIN = 256;                         // escape bytes staged per tile and kind; longer tiles read the rest from global
+constexpr int ESC_WIN = 256;                         // escape bytes staged per tile and kind; longer tiles read theirs from global memory
 // stage layout (bytes)
 // stage layout (bytes); each escape window is preceded by 16 bytes that stay zero: a group without an escape byte reads one of them
 constexpr int ZPAD = 16;
+#if GAAC_BULK
+// Stage = 16 bytes (mbarrier, then 8 bytes that stay zero) + a block per side:
+//   sign/mantissa (2048, storage order) | codes (768) | tag words (64) | escape window (ESC_WIN + 16: it starts at the
+//   16-byte boundary below the tile's first escape byte).  Every piece is ONE bulk copy: copies of 128 bytes (one per
+//   row, skewed to avoid the bank conflicts of the storage order) were measured 15 % slower, the copy engine wants few large
+//   copies, so the fragment reads accept a 2-way (K) / 4-way (V) conflict.
+// codes | tags | escapes are adjacent as in the paged tile slot, so the paged layout fetches them with one copy.
+constexpr int ESC_COPY = ESC_WIN + 16;
+constexpr int SM_ROW = 128;
+constexpr int SB_SM = 0, SB_CD = SB_SM + 16 * SM_ROW, SB_FL = SB_CD + 768, SB_ESC = SB_FL + 64, SIDE_BYTES = SB_ESC + ESC_COPY;
+constexpr int ST_MBAR = 0, ST_ZERO = 8, ST_K = 16, ST_V = ST_K + SIDE_BYTES;
+constexpr int ST_KSM = ST_K + SB_SM, ST_KCD = ST_K + SB_CD, ST_KFL = ST_K + SB_FL, ST_KESC = ST_K + SB_ESC;
+constexpr int ST_VSM = ST_V + SB_SM, ST_VCD = ST_V + SB_CD, ST_VFL = ST_V + SB_FL, ST_VESC = ST_V + SB_ESC;
+constexpr int STAGE_BYTES = ST_V + SIDE_BYTES;
+static_assert(SB_CD - SB_SM == SLOT_CD_OFF && SB_FL - SB_SM == SLOT_FL_OFF && SB_ESC - SB_SM == SLOT_OVF_OFF, "side block laid out as the paged tile slot");
+#else
 constexpr int ST_KSM = 0, ST_KCD = 2048, ST_VSM = 2816, ST_VCD = 4864, ST_KFL = 5632, ST_VFL = 5696;
 constexpr int ST_KZ = 5760, ST_KESC = ST_KZ + ZPAD, ST_VZ = ST_KESC + ESC_WIN, ST_VESC = ST_VZ + ZPAD;
 constexpr int STAGE_BYTES = ST_VESC + ESC_WIN;       // 6304
+#endif
 // CTA-wide tables in front of the rings: escape-byte table, K base words [j][g], V base words [r][g], a zero word
 constexpr int META_TILES = 512;                      // tiles of a CTA's range whose metadata is staged (longer ranges read the rest from global)
 // CTA tables: escape-byte table (2 KiB), K / V base words, per-tile metadata, and the code table: four 3-bit codes -> four bytes
@@ -55,6 +75,12 @@ constexpr int META_TILES = 512;                      // tiles of a CTA's range w
 constexpr int TB_LUTX = 0, TB_KB = 2048, TB_VB = TB_KB + 256, TB_META = TB_VB + 256, TB_LUTC = TB_META + 2 * META_TILES * 4;
 constexpr int TABLE_BYTES = TB_LUTC + (GAAC_LUTC ? 4096 * 4 : 0);
 constexpr int ATT_SMEM = TABLE_BYTES + ATT_WARPS * NSTAGE * STAGE_BYTES;
+#if GAAC_BULK
+static_assert(TABLE_BYTES % 16 == 0 && STAGE_BYTES % 16 == 0 && ST_KSM % 16 == 0 && ST_KCD % 16 == 0 && ST_KFL % 16 == 0 && ST_KESC % 16 == 0 &&
+              ST_VSM % 16 == 0 && ST_VCD % 16 == 0 && ST_VFL % 16 == 0 && ST_VESC % 16 == 0 && ESC_COPY % 16 == 0 && ST_MBAR % 8 == 0 && SM_ROW % 16 == 0,
+              "bulk copies need 16-byte aligned shared-memory destinations and sizes");
+static_assert(ATT_SMEM + 64 <= 232448, "one CTA per SM: at most 227 KB of shared memory, static part included");
+#endif
 constexpr unsigned FULLM = 0xffffffffu;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 
@@ -67,7 +93,7 @@ struct AttnParams {
   const uint8_t *b3k, *b4k, *b3v, *b4v;
   // common
   const uint16_t* q; int B, n_q, n_kv, G; float scale_log2; int nsplit;
-  int* counters; float* pm; float* pl; float* pa;
+  int* counters; int* err; float* pm; float* pl; float* pa;     // err: set to 1 when a bounded wait inside the kernel ran out
   uint16_t* out; float* out_f32; float* part;
   // cross-GPU exchange (x_recv == NULL: unused): the partial of every query head is stored into every rank's receive
   // buffer, then the rank's arrival counter on every rank is raised once per (row, kv head)
@@ -82,6 +108,28 @@ __device__ __forceinline__ void cp16(u32 dst, const void* src) { asm volatile("c
 __device__ __forceinline__ void cp4(u32 dst, const void* src) { asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src)); }
 __device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+// ---- bulk asynchronous copies (TMA engine, no tensor map): global -> shared, completion counted in bytes on an mbarrier.
+// Both addresses are 16-byte aligned and the size is a multiple of 16 at every call site.
+__device__ __forceinline__ void mbar_init(u32 mbar, u32 count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbar), "r"(count)); }
+__device__ __forceinline__ void mbar_expect_tx(u32 mbar, u32 bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(mbar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_add_tx(u32 mbar, u32 bytes) { asm volatile("mbarrier.expect_tx.shared::cta.b64 [%0], %1;\n" ::"r"(mbar), "r"(bytes) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(u32 mbar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(mbar) : "memory"); }
+__device__ __forceinline__ void bulk_g2s(u32 dst, const void* src, u32 bytes, u32 mbar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst), "l"(src), "r"(bytes), "r"(mbar) : "memory");
+}
+// Bounded wait for a phase of the barrier: false when it gave up (the copies of a stage normally land within microseconds;
+// the bound is there so that a lost copy can never hang the GPU).
+constexpr int MBAR_WAIT_LIMIT = 1 << 22;
+__device__ __forceinline__ bool mbar_wait(u32 mbar, u32 parity) {
+  for (int it = 0; it < MBAR_WAIT_LIMIT; it++) {
+    u32 ok;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(ok) : "r"(mbar), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
 __device__ __forceinline__ float fast_exp2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 
 // What a warp remembers of a tile between issuing its copies and consuming it.  Slot layout: offsets of the tile's escape
@@ -108,6 +156,17 @@ __device__ __forceinline__ int esc_window_bytes(const uint8_t* esc, int alloc_le
   const int wsh = (int)(reinterpret_cast<uintptr_t>(esc) & 3);
   return max(0, min(ESC_WIN, (alloc_left + wsh) & ~3) - wsh);
 }
+
+#if GAAC_BULK
+// Bytes of the bulk copy that stages the escape window of a tile whose first escape byte is `esc`: the copy starts at the
+// 16-byte boundary below `esc`, is ESC_COPY bytes long at most, a multiple of 16, and stays inside [base, end); 0 when the
+// boundary lies before `base` (the tile then reads its escapes from global memory).
+__device__ __forceinline__ int esc_copy_bytes(const uint8_t* esc, const uint8_t* base, const uint8_t* end) {
+  const uint8_t* a = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(esc) & ~(uintptr_t)15);
+  if (a < base) return 0;
+  return (int)min((long)ESC_COPY, (long)((end - a) & ~(long)15));
+}
+#endif
 
 template <int DOFF, int SOFF> __device__ __forceinline__ void cp16i(u32 dst, const void* src) {
 #if GAAC_CP16_CA
@@ -146,7 +205,7 @@ __device__ __forceinline__ void issue_esc(u32 win, const EscRef& e, int lane) {
   const int lim = min(ESC_WIN, (e.lim + wsh) & ~3);           // bytes to copy, counted from the boundary
   const uint8_t* a = e.p - wsh + 4 * lane;
   const u32 d = win + 4 * lane;
-  static_assert(ESC_WIN == 256, "two words per lane");
+  static_assert(ESC_WIN <= 256, "two words per lane");
   if (4 * lane < lim) cp4i<0, 0>(d, a);
   if (4 * lane + 128 < lim) cp4i<128, 128>(d, a);
 }
@@ -203,11 +262,11 @@ __device__ __forceinline__ void pv_words(WarpAcc& A, int w, const u32 (&u01)[4],
 }
 
 // Escape bytes of one tile as read by the group decoder.
-//   staged window (WIN): zp = shared-memory address 16 bytes below the tile's first escape byte; the bytes from zp up to the
-//     window are zero, so a group without an escape byte reads zp[0] and a 4-bit-window group reads zp[16 + pos]: one
-//     multiply-add, no branch.
+//   staged window (WIN): zp = shared-memory address of a zero byte below the tile's first escape byte; a group without an
+//     escape byte reads zp[0] and a 4-bit-window group reads zp[off + pos]: one multiply-add, no branch.
 //   global memory (!WIN, tiles whose escapes exceed the window): plain loads at glob[pos].
-template <bool WIN> struct EscSrc { const uint8_t* zp; const uint8_t* glob; };
+//   off = distance from zp to the tile's first escape byte (the zero byte a group without escapes reads sits at zp[0]).
+template <bool WIN> struct EscSrc { const uint8_t* zp; const uint8_t* glob; int off; };
 
 // ---- byte-SWAR pieces written for the pipes of the SM: logic ops (LOP3 / PRMT / SHF) run on the ALU pipe, whose rate is half
 // the issue rate, so shifts that can be merged with an add are written as multiply-adds (FMA pipe) and the 3-bit -> byte
@@ -229,14 +288,14 @@ __device__ __forceinline__ u32 spread_hi5_dev(u32 u) {
 }
 
 // Rebuild one group (two sign/mantissa words) into four bf16x2 words.  Same results as decode_group_lut (gaac_tile.h);
-// pos16 = 16 + escape position of the group, advanced past it on return; lutc = the 4096-entry code table.
+// pos16 = es.off + escape position of the group, advanced past it on return; lutc = the 4096-entry code table.
 template <bool WIN>
 __device__ __forceinline__ void decode_group_dev(u32 sm_lo, u32 sm_hi, u32 c24, u32 tg, int& pos16, const EscSrc<WIN>& es,
                                                  const u32x2* lutx, const uint8_t* lutc, const u32x4& bw, u32 out[4]) {
   const u32 m1 = tg & 1u;                             // promoted (tags are 0, 1 or 3)
   u32 xe;
   if (WIN) xe = es.zp[m1 * (u32)pos16];               // raw groups read a payload byte here; their addends are replaced below
-  else xe = m1 ? es.glob[pos16 - 16] : 0u;
+  else xe = m1 ? es.glob[pos16 - es.off] : 0u;
   const u32x2 x = lutx[xe];
   u32 x0 = x.x, x1 = x.y;
 #if GAAC_LUTC == 1
@@ -263,7 +322,7 @@ __device__ __forceinline__ void decode_group_dev(u32 sm_lo, u32 sm_hi, u32 c24, 
       asm volatile("ld.shared.u32 %0, [%1];" : "=r"(w0) : "r"(a & ~3u) : "memory");
       asm volatile("ld.shared.u32 %0, [%1+4];" : "=r"(w1) : "r"(a & ~3u) : "memory");
     } else {
-      const uint8_t* p = es.glob + (pos16 - 16);
+      const uint8_t* p = es.glob + (pos16 - es.off);
       sh = 8 * (int)(reinterpret_cast<uintptr_t>(p) & 3);
       const u32* a = reinterpret_cast<const u32*>(reinterpret_cast<uintptr_t>(p) & ~(uintptr_t)3);
       w0 = a[0]; w1 = a[1];
@@ -290,12 +349,16 @@ __device__ __forceinline__ void k_scores(float* sc, const uint8_t* stage, const 
 #pragma unroll
   for (int o = 0; o < 2; o++) {
     const u32 fl = __shfl_sync(FULLM, flrow, 8 * o + r);
-    pos[o] = __shfl_sync(FULLM, rowoff, 8 * o + r) + esc_prefix(fl, 8 * j) + 16;
+    pos[o] = __shfl_sync(FULLM, rowoff, 8 * o + r) + esc_prefix(fl, 8 * j) + es.off;
     t8[o] = fl >> (8 * j);
+#if GAAC_BULK
+    s0[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + (8 * o + (lane >> 2)) * SM_ROW + 32 * (lane & 3));   // storage order, skewed rows
+    s1[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + (8 * o + (lane >> 2)) * SM_ROW + 32 * (lane & 3) + 16);
+#elif GAAC_SWZ
     s0[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + lane));
-#if GAAC_SWZ
     s1[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + 32 + (lane ^ 4)));
 #else
+    s0[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + lane));
     s1[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + 32 + lane));
 #endif
     const u32* c = reinterpret_cast<const u32*>(stage + ST_KCD + o * 384 + 12 * lane);
@@ -328,9 +391,11 @@ __device__ __forceinline__ void v_accum(WarpAcc& A, const uint8_t* stage, const 
   for (int t = 0; t < 4; t++) {
     const int tok = 2 * j + (t & 1) + 8 * (t >> 1);
     const u32 fl = __shfl_sync(FULLM, flrow, 16 + tok);
-    pos[t] = __shfl_sync(FULLM, rowoff, 16 + tok) + esc_prefix(fl, 4 * r) + 16;
+    pos[t] = __shfl_sync(FULLM, rowoff, 16 + tok) + esc_prefix(fl, 4 * r) + es.off;
     t4[t] = fl >> (4 * r);
-#if GAAC_SWZ
+#if GAAC_BULK
+    sm[t] = *reinterpret_cast<const uint4*>(stage + ST_VSM + (lane >> 1) * SM_ROW + 64 * (lane & 1) + 16 * t);
+#elif GAAC_SWZ
     sm[t] = *reinterpret_cast<const uint4*>(stage + ST_VSM + 16 * (t * 32 + (lane ^ (2 * t))));
 #else
     sm[t] = *reinterpret_cast<const uint4*>(stage + ST_VSM + 16 * (t * 32 + lane));
@@ -365,8 +430,7 @@ __device__ __forceinline__ void v_accum(WarpAcc& A, const uint8_t* stage, const 
 __device__ __forceinline__ void scan_rows(const uint8_t* stage, bool rawk, bool rawv, int lane, u32& flrow, int& rowoff, int& total) {
   const int row = lane & 15;
   const bool isv = lane >= 16;
-  flrow = (isv ? rawv : rawk) ? 0u : *reinterpret_cast<const u32*>(stage + ST_KFL + 4 * lane);   // ST_VFL = ST_KFL + 64
-  static_assert(ST_VFL == ST_KFL + 64, "V tag words follow the K tag words");
+  flrow = (isv ? rawv : rawk) ? 0u : *reinterpret_cast<const u32*>(stage + (isv ? ST_VFL : ST_KFL) + 4 * row);
   const int sz = row_esc_bytes(flrow);
   int inc = sz;
 #pragma unroll
@@ -479,15 +543,72 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     if (!PAGED || m.mk >= 0) issue_esc(st + ST_KESC, esc_k(m.mk), lane);
     if (!PAGED || m.mv >= 0) issue_esc(st + ST_VESC, esc_v(m.mv), lane);
   };
+#if GAAC_BULK
+  // Bulk copies of one tile into stage `st`, issued by lane 0: it arms the stage's mbarrier with the total byte count (one
+  // arrival per phase), then issues up to eight copies (K, V) x (sign/mantissa, codes, tag words, escape window); in the paged
+  // layout a whole slot is one copy.  (Spreading the copies over eight lanes was measured slower than this.)
+  // Slot layout, escape window of a tile whose escapes start `m` bytes into the head's escape bytes, in 32-bit arithmetic:
+  // w16 = its first byte's offset inside a 16-byte unit, n = bytes of the copy from the unit's start (a multiple of 16, at most
+  // ESC_COPY, inside the allocation; 0 when the unit starts before the allocation).
+  const int a16k = PAGED ? 0 : (int)((reinterpret_cast<uintptr_t>(p.K.ovf) + (unsigned)ohk) & 15), a16v = PAGED ? 0 : (int)((reinterpret_cast<uintptr_t>(p.V.ovf) + (unsigned)ohv) & 15);
+  auto esc_win = [&](bool vside, int m, int& w16, int& n) {
+    w16 = ((vside ? a16v : a16k) + m) & 15;
+    const int to_end = (vside ? L.availv : L.availk) - m + w16;                 // bytes from the unit's start to the end of the allocation
+    n = ((vside ? L.ohv : L.ohk) + m < w16) ? 0 : max(0, min(ESC_COPY, to_end & ~15));
+  };
+  auto bulk_issue = [&](u32 st, int tile, const TileMeta& m) {                  // executed by lane 0
+    const u32 mb = st + ST_MBAR;
+    if (PAGED) {
+      const u32 n = (u32)min(p.TS, SLOT_OVF_OFF + ESC_COPY);                    // a slot is one contiguous piece, escapes included
+      mbar_expect_tx(mb, (m.mk >= 0 ? n : 0u) + (m.mv >= 0 ? n : 0u));
+      if (m.mk >= 0) bulk_g2s(st + ST_KSM, p.buf + (long)m.mk * p.TS, n, mb);
+      if (m.mv >= 0) bulk_g2s(st + ST_VSM, p.buf + (long)m.mv * p.TS, n, mb);
+    } else {
+      int wk, nk, wv, nv;
+      esc_win(false, m.mk, wk, nk); esc_win(true, m.mv, wv, nv);
+      mbar_expect_tx(mb, (u32)(2 * (TILE_SM + TILE_CD + 4 * T) + nk + nv));
+      const long so = smh + (long)tile * TILE_SM, co = cdh + (long)tile * TILE_CD, fo = (rowb + (long)tile * T) * 4;
+      bulk_g2s(st + ST_KSM, p.K.sm + so, TILE_SM, mb); bulk_g2s(st + ST_VSM, p.V.sm + so, TILE_SM, mb);
+      bulk_g2s(st + ST_KCD, p.K.codes + co, TILE_CD, mb); bulk_g2s(st + ST_VCD, p.V.codes + co, TILE_CD, mb);
+      bulk_g2s(st + ST_KFL, reinterpret_cast<const uint8_t*>(p.K.flags) + fo, 4 * T, mb);
+      bulk_g2s(st + ST_VFL, reinterpret_cast<const uint8_t*>(p.V.flags) + fo, 4 * T, mb);
+      if (nk > 0) bulk_g2s(st + ST_KESC, p.K.ovf + ((long)L.ohk + m.mk - wk), (u32)nk, mb);
+      if (nv > 0) bulk_g2s(st + ST_VESC, p.V.ovf + ((long)L.ohv + m.mv - wv), (u32)nv, mb);
+    }
+  };
+  // Escape bytes of a staged side as the group decoder reads them: first escape byte in global memory, offset from the stage's
+  // zero byte to the first escape byte, staged bytes counted from the first escape byte
+  auto staged_escapes = [&](bool vside, int m, const uint8_t*& esc, int& off, int& avail) {
+    const int base = (vside ? ST_VESC : ST_KESC) - ST_ZERO;
+    if (PAGED) {
+      esc = p.buf + (long)m * p.TS + SLOT_OVF_OFF; off = base; avail = min(p.ovf_slot, min(p.TS, SLOT_OVF_OFF + ESC_COPY) - SLOT_OVF_OFF);
+    } else {
+      int w16, n;
+      esc_win(vside, m, w16, n);
+      esc = (vside ? p.V.ovf : p.K.ovf) + ((long)(vside ? L.ohv : L.ohk) + m);
+      off = base + w16; avail = n - w16;
+    }
+  };
+#endif
   // ---- prologue.  Everything that reads global memory is put in flight first and consumed afterwards: the payload of the
   // warp's first tile (needs no metadata in the slot layout), the tile's metadata, the metadata of the CTA's range, the
   // query rows; then the tables are built while those loads travel.
   int tile = tlo + warp;
   TileMeta cur{0, 0};
+#if GAAC_BULK
+  if (lane == 0) {                                    // one barrier per stage, one arrival (this lane's) per phase; 8 zero bytes beside it
+    mbar_init(ring_s + ST_MBAR, 1); mbar_init(ring_s + STAGE_BYTES + ST_MBAR, 1);
+    *reinterpret_cast<unsigned long long*>(ring + ST_ZERO) = 0ull; *reinterpret_cast<unsigned long long*>(ring + STAGE_BYTES + ST_ZERO) = 0ull;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncwarp();
+  if (tile < thi) { cur = global_meta(tile); if (lane == 0) bulk_issue(ring_s, tile, cur); }
+#else
   if (tile < thi) {
     if (PAGED) { cur = global_meta(tile); issue_payload(ring_s, tile, cur); }
     else { issue_payload(ring_s, tile, cur); cur = global_meta(tile); }
   }
+#endif
   int* mk_s = reinterpret_cast<int*>(smem + TB_META);
   int* mv_s = mk_s + META_TILES;
   const int nstaged = min(thi - tlo, META_TILES);
@@ -523,16 +644,20 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
 #if GAAC_LUTC
     for (int i = tid; i < 4096; i += ATT_THREADS) reinterpret_cast<u32*>(smem + TB_LUTC)[i] = spread_codes4((u32)i);
 #endif
+#if !GAAC_BULK
     if (tid >= 320 && tid < 320 + ATT_WARPS * NSTAGE * 2) {      // the 16 zero bytes in front of every escape window
       const int t = tid - 320, st = t >> 1;
       *reinterpret_cast<uint4*>(smem + TABLE_BYTES + st * STAGE_BYTES + ((t & 1) ? ST_VZ : ST_KZ)) = make_uint4(0, 0, 0, 0);
     }
+#endif
     if (tid == 0) s_next = tlo + ATT_WARPS;           // tiles tlo .. tlo+W-1 go to warps 0..W-1, the rest is handed out on demand
     if (tid < nstaged) { mk_s[tid] = m_first.mk; mv_s[tid] = m_first.mv; }
     for (int i = tid + ATT_THREADS; i < nstaged; i += ATT_THREADS) { const TileMeta m = global_meta(tlo + i); mk_s[i] = m.mk; mv_s[i] = m.mv; }
   }
+#if !GAAC_BULK
   if (tile < thi) issue_escapes(ring_s, cur);
   cp_commit();
+#endif
   WarpAcc A;
 #pragma unroll
   for (int n = 0; n < 8; n++) A.acc[n][0] = A.acc[n][1] = A.acc[n][2] = A.acc[n][3] = 0.f;
@@ -544,11 +669,22 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
   // other.  The counter is read at the top of the iteration and its value used after the K half, which hides the latency
   // of the shared-memory atomic; the copies of the next tile are issued between the K half and the V half.
   int stg = 0;
+#if GAAC_BULK
+  u32 phase = 0;                                       // bit s: parity of the phase of stage s that is waited for next
+#endif
   while (tile < thi) {
     int t1 = 0;
     if (lane == 0) t1 = atomicAdd(&s_next, 1);
+#if GAAC_BULK
+    if (!__all_sync(FULLM, mbar_wait(ring_s + stg * STAGE_BYTES + ST_MBAR, (phase >> stg) & 1u))) {     // the whole warp gives up together
+      if (lane == 0) atomicExch(p.err, 1);
+      break;
+    }
+    phase ^= 1u << stg;
+#else
     cp_wait<0>();
     __syncwarp();
+#endif
     const uint8_t* stage = ring + stg * STAGE_BYTES;
     const int nvalid = min(T, S - tile * T);
     const bool rawk = PAGED && cur.mk < 0, rawv = PAGED && cur.mv < 0;
@@ -556,12 +692,21 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     scan_rows(stage, rawk, rawv, lane, flrow, rowoff, total);
     float sc[4] = {0.f, 0.f, 0.f, 0.f};
     if (!rawk) {
+#if GAAC_BULK
+      const uint8_t* esc; int off, avail;
+      staged_escapes(false, cur.mk, esc, off, avail);
+      if (__shfl_sync(FULLM, total, 15) + 8 <= avail)                                         // +8: a raw payload is read as two aligned words
+        k_scores<true>(sc, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off}, flrow, rowoff, lane, qa);
+      else
+        k_scores<false>(sc, stage, smem, EscSrc<false>{nullptr, esc, 0}, flrow, rowoff, lane, qa);
+#else
       const EscRef e = esc_k(cur.mk);
       const int wsh = (int)(reinterpret_cast<uintptr_t>(e.p) & 3);
       if (__shfl_sync(FULLM, total, 15) + 8 <= esc_window_bytes(e.p, e.lim))                  // +8: a raw payload is read as two aligned words
-        k_scores<true>(sc, stage, smem, EscSrc<true>{stage + ST_KESC + wsh - ZPAD, nullptr}, flrow, rowoff, lane, qa);
+        k_scores<true>(sc, stage, smem, EscSrc<true>{stage + ST_KESC + wsh - ZPAD, nullptr, ZPAD}, flrow, rowoff, lane, qa);
       else
-        k_scores<false>(sc, stage, smem, EscSrc<false>{nullptr, e.p}, flrow, rowoff, lane, qa);
+        k_scores<false>(sc, stage, smem, EscSrc<false>{nullptr, e.p, 0}, flrow, rowoff, lane, qa);
+#endif
     } else {
       raw_scores(sc, p.raw + (long)(~cur.mk) * (T * D), nvalid, lane, qa);
     }
@@ -570,24 +715,41 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     if (t1 < thi) {
       nxt = meta_of(t1);
       const u32 st = ring_s + (stg ^ 1) * STAGE_BYTES;
+#if GAAC_BULK
+      if (lane == 0) bulk_issue(st, t1, nxt);
+#else
       issue_payload(st, t1, nxt); issue_escapes(st, nxt);
+#endif
     }
+#if !GAAC_BULK
     cp_commit();
+#endif
     u32 pb0, pb1;
     softmax_step(A, sc, p.scale_log2, nvalid, lane, pb0, pb1);
     if (!rawv) {
+#if GAAC_BULK
+      const uint8_t* esc; int off, avail;
+      staged_escapes(true, cur.mv, esc, off, avail);
+      if (__shfl_sync(FULLM, total, 31) + 8 <= avail)
+        v_accum<true>(A, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off}, flrow, rowoff, lane, pb0, pb1);
+      else
+        v_accum<false>(A, stage, smem, EscSrc<false>{nullptr, esc, 0}, flrow, rowoff, lane, pb0, pb1);
+#else
       const EscRef e = esc_v(cur.mv);
       const int wsh = (int)(reinterpret_cast<uintptr_t>(e.p) & 3);
       if (__shfl_sync(FULLM, total, 31) + 8 <= esc_window_bytes(e.p, e.lim))
-        v_accum<true>(A, stage, smem, EscSrc<true>{stage + ST_VESC + wsh - ZPAD, nullptr}, flrow, rowoff, lane, pb0, pb1);
+        v_accum<true>(A, stage, smem, EscSrc<true>{stage + ST_VESC + wsh - ZPAD, nullptr, ZPAD}, flrow, rowoff, lane, pb0, pb1);
       else
-        v_accum<false>(A, stage, smem, EscSrc<false>{nullptr, e.p}, flrow, rowoff, lane, pb0, pb1);
+        v_accum<false>(A, stage, smem, EscSrc<false>{nullptr, e.p, 0}, flrow, rowoff, lane, pb0, pb1);
+#endif
     } else {
       raw_accum(A, p.raw + (long)(~cur.mv) * (T * D), nvalid, lane, pb0, pb1);
     }
     cur = nxt; stg ^= 1; tile = t1;
   }
+#if !GAAC_BULK
   cp_wait<0>();
+#endif
   // ---- slot layout: the raw BF16 tail belongs to the last split's warp 0
   if (!PAGED && TL > 0 && split == p.nsplit - 1 && warp == 0) {
     const uint16_t* kraw = reinterpret_cast<const uint16_t*>(p.K.tail) + (long)ch * p.tail_cap * D;
@@ -820,10 +982,10 @@ __global__ void __launch_bounds__(128) combine_parts_kernel(const float* __restr
 static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 static int carve_workspace(void* ws, size_t ws_bytes, int B, int n_q, int nsplit, AttnParams& p) {
   const size_t n = (size_t)B * n_q * nsplit;
-  const size_t need = align256(4 * (size_t)B * n_q) + align256(4 * n) * 2 + align256(4 * n * D);
+  const size_t need = align256(4 * ((size_t)B * n_q + 1)) + align256(4 * n) * 2 + align256(4 * n * D);
   if (!ws || ws_bytes < need) return GAAC_E_WORKSPACE;
   uint8_t* w = (uint8_t*)ws;
-  p.counters = (int*)w; w += align256(4 * (size_t)B * n_q);
+  p.counters = (int*)w; p.err = p.counters + (size_t)B * n_q; w += align256(4 * ((size_t)B * n_q + 1));
   p.pm = (float*)w; w += align256(4 * n);
   p.pl = (float*)w; w += align256(4 * n);
   p.pa = (float*)w;
@@ -873,7 +1035,7 @@ using namespace gaac;
 extern "C" size_t gaac_attn_workspace_bytes(int B, int n_q, int nsplit) {
   if (B <= 0 || n_q <= 0 || nsplit <= 0) return 0;
   const size_t n = (size_t)B * n_q * nsplit;
-  return align256(4 * (size_t)B * n_q) + align256(4 * n) * 2 + align256(4 * n * D);
+  return align256(4 * ((size_t)B * n_q + 1)) + align256(4 * n) * 2 + align256(4 * n * D);
 }
 
 extern "C" int gaac_decode_attn(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,

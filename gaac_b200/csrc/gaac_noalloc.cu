@@ -53,7 +53,7 @@ extern "C" int gaac_decode_attn_static(const gaac_side* K, const gaac_side* V, c
   void* ws = nullptr;
   if (int e = scratch_for_current_device(&ws)) return e;
   // the ticket counters at the head of the workspace must start at zero whatever an earlier call left behind
-  const size_t header = ((size_t)4 * B * n_q + 255) & ~(size_t)255;
+  const size_t header = ((size_t)4 * ((size_t)B * n_q + 1) + 255) & ~(size_t)255;     // split counters + the error word
   if (cudaMemsetAsync(ws, 0, header, (cudaStream_t)stream) != cudaSuccess) { cudaGetLastError(); return GAAC_E_LAUNCH; }
   return gaac_decode_attn(K, V, q_bf16, slot, B, n_q, n_kv, seq_len, S_pad, scale, nsplit, tail_len, tail_cap, n_base_rows,
                           ws, STATIC_SCRATCH_BYTES, out_bf16, out_f32, stream);
