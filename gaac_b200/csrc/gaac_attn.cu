@@ -602,7 +602,23 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   __syncwarp();
-  if (tile < thi) { cur = global_meta(tile); if (lane == 0) bulk_issue(ring_s, tile, cur); }
+  if (tile < thi) {
+    if (PAGED) { cur = global_meta(tile); if (lane == 0) bulk_issue(ring_s, tile, cur); }
+    else {
+      // slot layout: the six payload copies need no metadata and leave at once; the escape windows (and the barrier's arrival)
+      // follow further down, when the tile's escape offsets have come back from global memory
+      if (lane == 0) {
+        const u32 mb = ring_s + ST_MBAR;
+        const long so = smh + (long)tile * TILE_SM, co = cdh + (long)tile * TILE_CD, fo = (rowb + (long)tile * T) * 4;
+        mbar_add_tx(mb, 2 * (TILE_SM + TILE_CD + 4 * T));
+        bulk_g2s(ring_s + ST_KSM, p.K.sm + so, TILE_SM, mb); bulk_g2s(ring_s + ST_VSM, p.V.sm + so, TILE_SM, mb);
+        bulk_g2s(ring_s + ST_KCD, p.K.codes + co, TILE_CD, mb); bulk_g2s(ring_s + ST_VCD, p.V.codes + co, TILE_CD, mb);
+        bulk_g2s(ring_s + ST_KFL, reinterpret_cast<const uint8_t*>(p.K.flags) + fo, 4 * T, mb);
+        bulk_g2s(ring_s + ST_VFL, reinterpret_cast<const uint8_t*>(p.V.flags) + fo, 4 * T, mb);
+      }
+      cur = global_meta(tile);
+    }
+  }
 #else
   if (tile < thi) {
     if (PAGED) { cur = global_meta(tile); issue_payload(ring_s, tile, cur); }
@@ -654,7 +670,17 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     if (tid < nstaged) { mk_s[tid] = m_first.mk; mv_s[tid] = m_first.mv; }
     for (int i = tid + ATT_THREADS; i < nstaged; i += ATT_THREADS) { const TileMeta m = global_meta(tlo + i); mk_s[i] = m.mk; mv_s[i] = m.mv; }
   }
-#if !GAAC_BULK
+#if GAAC_BULK
+  if (!PAGED && tile < thi && lane == 0) {
+    const u32 mb = ring_s + ST_MBAR;
+    int wk, nk, wv, nv;
+    esc_win(false, cur.mk, wk, nk); esc_win(true, cur.mv, wv, nv);
+    if (nk + nv > 0) mbar_add_tx(mb, (u32)(nk + nv));
+    if (nk > 0) bulk_g2s(ring_s + ST_KESC, p.K.ovf + ((long)L.ohk + cur.mk - wk), (u32)nk, mb);
+    if (nv > 0) bulk_g2s(ring_s + ST_VESC, p.V.ovf + ((long)L.ohv + cur.mv - wv), (u32)nv, mb);
+    mbar_arrive(mb);
+  }
+#else
   if (tile < thi) issue_escapes(ring_s, cur);
   cp_commit();
 #endif
