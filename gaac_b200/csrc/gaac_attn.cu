@@ -33,7 +33,7 @@ namespace gaac {
 #define GAAC_CP16_CA 1
 #endif
 #ifndef GAAC_LUTC
-#define GAAC_LUTC 1
+#define GAAC_LUTC 2
 #endif
 #ifndef GAAC_BULK
 #define GAAC_BULK 1
