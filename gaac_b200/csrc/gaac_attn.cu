@@ -578,16 +578,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
   };
   // Escape bytes of a staged side as the group decoder reads them: first escape byte in global memory, offset from the stage's
   // zero byte to the first escape byte, staged bytes counted from the first escape byte
-  auto staged_escapes = [&](bool vside, int m, const uint8_t*& esc, int& off, int& avail) {
+  auto staged_escapes = [&](bool vside, int m, int& off, int& avail) {
     const int base = (vside ? ST_VESC : ST_KESC) - ST_ZERO;
-    if (PAGED) {
-      esc = p.buf + (long)m * p.TS + SLOT_OVF_OFF; off = base; avail = min(p.ovf_slot, min(p.TS, SLOT_OVF_OFF + ESC_COPY) - SLOT_OVF_OFF);
-    } else {
-      int w16, n;
-      esc_win(vside, m, w16, n);
-      esc = (vside ? p.V.ovf : p.K.ovf) + ((long)(vside ? L.ohv : L.ohk) + m);
-      off = base + w16; avail = n - w16;
-    }
+    if (PAGED) { off = base; avail = min(p.ovf_slot, min(p.TS, SLOT_OVF_OFF + ESC_COPY) - SLOT_OVF_OFF); }
+    else { int w16, n; esc_win(vside, m, w16, n); off = base + w16; avail = n - w16; }
+  };
+  auto global_escapes = [&](bool vside, int m) -> const uint8_t* {            // only tiles whose escapes exceed the window get here
+    if (PAGED) return p.buf + (long)m * p.TS + SLOT_OVF_OFF;
+    return (vside ? p.V.ovf : p.K.ovf) + ((long)(vside ? L.ohv : L.ohk) + m);
   };
 #endif
   // ---- prologue.  Everything that reads global memory is put in flight first and consumed afterwards: the payload of the
@@ -719,12 +717,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     float sc[4] = {0.f, 0.f, 0.f, 0.f};
     if (!rawk) {
 #if GAAC_BULK
-      const uint8_t* esc; int off, avail;
-      staged_escapes(false, cur.mk, esc, off, avail);
+      int off, avail;
+      staged_escapes(false, cur.mk, off, avail);
       if (__shfl_sync(FULLM, total, 15) + 8 <= avail)                                         // +8: a raw payload is read as two aligned words
         k_scores<true>(sc, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off}, flrow, rowoff, lane, qa);
       else
-        k_scores<false>(sc, stage, smem, EscSrc<false>{nullptr, esc, 0}, flrow, rowoff, lane, qa);
+        k_scores<false>(sc, stage, smem, EscSrc<false>{nullptr, global_escapes(false, cur.mk), 0}, flrow, rowoff, lane, qa);
 #else
       const EscRef e = esc_k(cur.mk);
       const int wsh = (int)(reinterpret_cast<uintptr_t>(e.p) & 3);
@@ -754,12 +752,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     softmax_step(A, sc, p.scale_log2, nvalid, lane, pb0, pb1);
     if (!rawv) {
 #if GAAC_BULK
-      const uint8_t* esc; int off, avail;
-      staged_escapes(true, cur.mv, esc, off, avail);
+      int off, avail;
+      staged_escapes(true, cur.mv, off, avail);
       if (__shfl_sync(FULLM, total, 31) + 8 <= avail)
         v_accum<true>(A, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off}, flrow, rowoff, lane, pb0, pb1);
       else
-        v_accum<false>(A, stage, smem, EscSrc<false>{nullptr, esc, 0}, flrow, rowoff, lane, pb0, pb1);
+        v_accum<false>(A, stage, smem, EscSrc<false>{nullptr, global_escapes(true, cur.mv), 0}, flrow, rowoff, lane, pb0, pb1);
 #else
       const EscRef e = esc_v(cur.mv);
       const int wsh = (int)(reinterpret_cast<uintptr_t>(e.p) & 3);
