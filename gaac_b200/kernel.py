@@ -24,6 +24,13 @@ def workspace(dev, B: int, n_q: int, nsplit: int) -> torch.Tensor:
     return ws
 
 
+def workspace_error(dev, B: int, n_q: int) -> bool:
+    """True when a kernel that used the cached workspace of the current stream gave up on a bounded wait for its own asynchronous
+    copies (the int32 behind the B*n_q split counters).  Reads device memory, so it synchronises; meant for tests and debugging."""
+    ws = _WS.get((torch.device(dev).index, torch.cuda.current_stream(dev).cuda_stream))
+    return bool(ws is not None and ws[4 * B * n_q:4 * B * n_q + 4].view(torch.int32).item() != 0)
+
+
 def choose_nsplit(B: int, n_kv: int, S: int, target_ctas: int = 96, min_tok: int = 512, cap: int = 48) -> int:
     """Splits per (row, kv head), the reference's heuristic verbatim (gaac/kernel.py:340-342; tuned for a 48-SM GB10)."""
     return min(max(1, target_ctas // (B * n_kv)), max(1, S // min_tok), cap)

@@ -109,7 +109,9 @@ size_t gaac_attn_workspace_bytes(int B, int n_q, int nsplit);
  * (slot[b] < 0: padded row, output exactly 0); seq_len[cache head] compressed tokens; tail_len[cache head] raw tail tokens
  * (NULL when there is no tail).  nsplit >= 1 context splits per (row, kv head).  out [B, n_q, 128] bf16; when out_f32 is
  * non-NULL the un-rounded fp32 result is written there as well.  workspace: gaac_attn_workspace_bytes bytes, its first
- * 4*B*n_q bytes (rounded up to 256) must be zero on the first use and are left zero by every call.  n_base_rows: rows of the base tables
+ * 4*(B*n_q + 1) bytes (rounded up to 256) must be zero on the first use: B*n_q int32 split counters, left zero by every call,
+ * then one int32 error word that the kernel sets to 1 if a bounded wait on its own asynchronous copies ever ran out (the
+ * output of that call is then not valid; it stays 0 in normal operation).  n_base_rows: rows of the base tables
  * (cache head h uses row h % n_base_rows).  Replaces gaac_attn_launch = gaac_attn<G> + gaac_tail<G> + gaac_combine<128>
  * (gaac/kernel.py:48-326). */
 int gaac_decode_attn(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,

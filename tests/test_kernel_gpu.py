@@ -183,3 +183,21 @@ def test_peer_exchange_wait_runs_out():
     assert x.error()
     assert (out == 0).all()
     assert float(torch.ones(4, device="cuda").sum()) == 4.0
+
+
+def test_copy_wait_error_word_stays_clear():
+    """The kernel's waits on its own bulk copies are bounded and report through an error word in the workspace: it must be
+    zero after ordinary calls (long context, many splits)."""
+    import torch
+    from gaac_b200 import attention, Codec, TileEncoder
+    from gaac_b200.kernel import workspace_error
+    n_kv, G, S = 2, 4, 8192
+    k16, v16 = O.synth_kv("k", n_kv, S, 9), O.synth_kv("v", n_kv, S, 9)
+    k, v = to_bf16_cuda(k16), to_bf16_cuda(v16)
+    ck, cv = Codec(n_kv).calibrate(k), Codec(n_kv).calibrate(v)
+    kp, vp = TileEncoder("k").encode(ck, k), TileEncoder("v").encode(cv, v)
+    q = to_bf16_cuda(O.f32_to_bf16(np.random.default_rng(3).standard_normal((1, n_kv * G, 128)).astype(np.float32)))
+    for nsplit in (1, 7, 16):
+        attention(q, kp, vp, nsplit=nsplit)
+    torch.cuda.synchronize()
+    assert not workspace_error("cuda", 1, n_kv * G)
