@@ -200,4 +200,4 @@ def test_copy_wait_error_word_stays_clear():
     for nsplit in (1, 7, 16):
         attention(q, kp, vp, nsplit=nsplit)
     torch.cuda.synchronize()
-    assert not workspace_error("cuda", 1, n_kv * G)
+    assert not workspace_error(q.device, 1, n_kv * G)
