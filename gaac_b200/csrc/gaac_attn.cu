@@ -473,7 +473,8 @@ template <bool PAGED>
 __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ int s_next, s_last;
-  const int bh = blockIdx.x, split = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, j = lane & 3, r = lane >> 2;
+  const int bh = blockIdx.x, split = blockIdx.y, tid = threadIdx.x, lane = tid & 31, j = lane & 3, r = lane >> 2;
+  const int warp = __shfl_sync(FULLM, tid >> 5, 0);   // the same value, but known to the compiler to be uniform across the warp
   const int b = bh / p.n_kv, kvh = bh % p.n_kv, G = p.G;
 
   // ---- programmatic dependent launch: the grid is launched with stream serialisation relaxed, so its CTAs can be made
