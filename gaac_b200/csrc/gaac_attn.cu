@@ -493,11 +493,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     S = sl < 0 ? 0 : p.seq_len[ch];
     TL = (sl < 0 || !p.tail_len) ? 0 : p.tail_len[ch];
   }
+  // These values are the same in every thread, but they were loaded from memory: passing them through a shuffle tells the
+  // compiler so, and the address arithmetic built on them (one lane issues the copies) stays in uniform registers.
+  S = __shfl_sync(FULLM, S, 0); ch = __shfl_sync(FULLM, ch, 0); TL = __shfl_sync(FULLM, TL, 0);
   const int ntiles = (S + 15) >> 4, chunk = (ntiles + p.nsplit - 1) / p.nsplit;
   const int tlo = min(split * chunk, ntiles), thi = min(tlo + chunk, ntiles);
   const long smh = (long)ch * p.S_pad * D, cdh = (long)ch * p.S_pad * CB, rowb = (long)ch * p.S_pad, tileb = (long)ch * (p.S_pad >> 4);
   int ohk = 0, ohv = 0;
   if (!PAGED && S > 0) { ohk = p.K.head_start[ch]; ohv = p.V.head_start[ch]; }
+  ohk = __shfl_sync(FULLM, ohk, 0); ohv = __shfl_sync(FULLM, ohv, 0);
 
   // ---- addressing of this lane, and the copies of the warp's first tile: they are put in flight before the CTA builds its
   // tables so that the first tile arrives while the tables are written
