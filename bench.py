@@ -326,9 +326,10 @@ def run_ours(args):
     # ---- end to end: q from pinned host memory, result back on the host, every step
     q_host = q.cpu().pin_memory(); out_host = torch.empty(1, N_Q, HEAD_DIM, dtype=torch.bfloat16).pin_memory()
     q_dev = torch.empty_like(q)
+    from gaac_b200 import attention as public_attention
     def e2e_step(i):
         q_dev.copy_(q_host, non_blocking=True)
-        out = layer(i, q_dev)
+        out = layer(i, q_dev) if world > 1 else public_attention(q_dev, *sets[i % N_SETS], scale=SCALE, nsplit=nsplit)     # the call a user makes
         out_host.copy_(out.view(1, N_Q, HEAD_DIM), non_blocking=True)
         torch.cuda.synchronize()
     for i in range(3): e2e_step(i)

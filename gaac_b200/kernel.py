@@ -118,21 +118,37 @@ def _ext():
 def attention(q, kp, vp, scale=None, nsplit=None, out_f32=None):
     """Decode attention over two Pages (kinds 'k' / 'v', H = B*n_kv heads of equal length).
     q: [B, n_q, D] bf16 (one query token per sequence) -> [B, n_q, D] bf16.  (gaac/kernel.py:345-359)
-    nsplit=None picks the B200 heuristic; an explicit nsplit is honoured as given."""
+    nsplit=None picks the B200 heuristic; an explicit nsplit is honoured as given.
+    What depends only on the Pages (identity slot map, per-head lengths, the two gaac_side descriptors) is built once and kept
+    on the Page objects, so a decode loop pays one library call per layer."""
     B, n_q, Dq = q.shape
+    if Dq != 128:
+        raise RuntimeError("head_dim must be 128")
+    if not q.is_cuda:
+        raise RuntimeError("gaac_b200 attention needs CUDA tensors: there is no CPU path")
     n_kv = kp.H // B
+    G = n_q // max(1, n_kv)
+    if not (1 <= G <= 8 and G * n_kv == n_q):
+        raise RuntimeError("GQA group size must be 1..8")
     dev = q.device
     if nsplit is None: nsplit = choose_nsplit_sm100(B, n_kv, kp.S)
-    cache = getattr(kp, "_attn_meta", None)          # identity slot map and per-head lengths, built once per Page
-    if cache is None or cache[0].device != dev or cache[0].numel() != B:
+    cache = getattr(kp, "_attn_meta", None)          # identity slot map, per-head lengths, K descriptor: built once per Page
+    if cache is None or cache[0].device != dev or cache[0].numel() != B or cache[2].ovf != kp.ovf.data_ptr():
         cache = (torch.arange(B, dtype=torch.int32, device=dev), torch.full((kp.H,), kp.S, dtype=torch.int32, device=dev),
-                 torch.empty(0, dtype=torch.int32, device=dev), torch.empty(0, dtype=q.dtype, device=dev))
+                 _side(kp.sm, kp.codes, kp.flags, kp.tile_off, kp.ovf, kp.ovf_head_start, kp.base3, kp.base4, None))
         kp._attn_meta = cache
-    slots, SL, e, eq = cache
-    out = _ext().gaac_attn_launch(kp.sm, kp.codes, kp.flags, kp.tile_off, kp.ovf, kp.ovf_head_start, kp.base3, kp.base4,
-                                  vp.sm, vp.codes, vp.flags, vp.tile_off, vp.ovf, vp.ovf_head_start, vp.base3, vp.base4,
-                                  q.reshape(B * n_q, Dq).contiguous(), slots, n_q, n_kv, SL, kp.sm.shape[1] // 128,
-                                  scale if scale is not None else Dq ** -0.5, nsplit, eq, eq, e, 0, out_f32=out_f32)
+    slots, SL, K = cache
+    V = getattr(vp, "_attn_side", None)
+    if V is None or V.ovf != vp.ovf.data_ptr():
+        V = _side(vp.sm, vp.codes, vp.flags, vp.tile_off, vp.ovf, vp.ovf_head_start, vp.base3, vp.base4, None)
+        vp._attn_side = V
+    q2 = q.reshape(B * n_q, Dq)
+    if not q2.is_contiguous(): q2 = q2.contiguous()
+    ws = workspace(dev, B, n_q, nsplit)
+    out = torch.empty(B * n_q, Dq, dtype=q.dtype, device=dev)
+    _lib.check(_lib.lib().gaac_decode_attn(K, V, q2.data_ptr(), slots.data_ptr(), B, n_q, n_kv, SL.data_ptr(), kp.sm.shape[1] // 128,
+                                           float(scale if scale is not None else Dq ** -0.5), int(nsplit), None, 0, kp.base3.size(0),
+                                           ws.data_ptr(), ws.numel(), out.data_ptr(), _lib.ptr(out_f32), _lib.stream_ptr(dev)), "gaac_decode_attn")
     return out.view(B, n_q, Dq)
 
 
