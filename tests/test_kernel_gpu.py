@@ -201,3 +201,29 @@ def test_copy_wait_error_word_stays_clear():
         attention(q, kp, vp, nsplit=nsplit)
     torch.cuda.synchronize()
     assert not workspace_error(q.device, 1, n_kv * G)
+
+
+@pytest.mark.parametrize("S", [65536, 131072])
+def test_attention_full_size_contexts(S):
+    """BASELINE config 1 (65536 tokens) and config 3 (131072 tokens) shapes: 32 query / 8 kv heads, synthetic KV of the benchmark
+    generator, default split count.  The codec is lossless, so the fp64 reference is computed on the GPU from the original BF16
+    tensors; the split merge is also checked against a single-split run (same result within the same tolerance)."""
+    import torch
+    from gaac_b200 import attention, Codec, TileEncoder
+    from gaac_b200.synth import synth_kv
+    n_kv, G = 8, 4
+    k, v = synth_kv("k", n_kv, S, 41, "cuda"), synth_kv("v", n_kv, S, 41, "cuda")
+    ck, cv = Codec(n_kv).calibrate(k[:, :2048]), Codec(n_kv).calibrate(v[:, :2048])
+    kp, vp = TileEncoder("k").encode(ck, k), TileEncoder("v").encode(cv, v)
+    q = torch.randn(1, n_kv * G, 128, generator=torch.Generator(device="cuda").manual_seed(5), device="cuda").to(torch.bfloat16)
+    o32 = torch.empty(1, n_kv * G, 128, dtype=torch.float32, device="cuda")
+    out = attention(q, kp, vp, SCALE, out_f32=o32)
+    qd = q[0].double().view(n_kv, G, 128)
+    s = torch.einsum("hgd,htd->hgt", qd, k.double()) * SCALE
+    ref = torch.einsum("hgt,htd->hgd", torch.softmax(s, -1), v.double()).reshape(n_kv * G, 128)
+    tol = 2e-3 * max(1.0, float(ref.abs().max()), float(v.float().abs().max()))
+    assert float((o32[0].double() - ref).abs().max()) <= tol
+    assert torch.equal(out[0], o32[0].to(torch.bfloat16))
+    o1 = torch.empty_like(o32)
+    attention(q, kp, vp, SCALE, nsplit=1, out_f32=o1)
+    assert float((o1[0].double() - ref).abs().max()) <= tol
