@@ -5,7 +5,8 @@ and its JIT extension `gaac_attn_v1` is prebuilt for sm_100a under baseline/_ref
 that nothing is compiled with nvcc on the GPU box; its Triton encoder compiles there in seconds.  Both directories are
 git-ignored.  This script runs the reference through its own public API (Codec.calibrate, TileEncoder.encode, attention) and
 prints one JSON line: microseconds per layer of its CUDA kernel (its own nsplit heuristic, and the best of a small sweep),
-milliseconds per encode of its Triton encoder, and two live parity checks against gaac_b200 on the same tensors.
+milliseconds per encode of its Triton encoder, and live parity checks against gaac_b200 on the same tensors (encoder output,
+attention over the reference's Pages, and the slot cache after prefill + appends).
 bench.py runs it in a child process as a side measurement; it is not part of any timed region of gaac_b200.
 """
 import json, os, sys, time
@@ -106,7 +107,40 @@ def main():
     out["attn_us_own_nsplit"] = res[ns0]; out["own_nsplit"] = ns0
     out["attn_us_best"] = min(res.values())
     out["gaac_b200_us_same_protocol"] = timed(lambda i: ours.attention(q, *sets[i % N_SETS], scale=scale))
+    out.update(slot_cache_parity(torch, ref, ours, dev))
     print(json.dumps(out), flush=True)
+
+
+def slot_cache_parity(torch, ref, ours, dev) -> dict:
+    """The slot cache of both packages fed with the same prompts and the same decode steps (per-sequence calibration, prefill of
+    two sequences of different length, 40 appended tokens each, so tiles are finalised on the way): every compressed buffer must
+    be byte-identical, and both attentions over their own cache must agree."""
+    from gaac_b200.synth import synth_kv
+    try:
+        n_kv, n_q, cap = 4, 16, 512
+        rc, oc = ref.CompressedKVCache(2, n_kv, cap, device=dev), ours.CompressedKVCache(2, n_kv, cap, device=dev)
+        for slot, L in ((0, 200), (1, 77)):
+            k = synth_kv("k", n_kv, L, 900 + slot, dev).transpose(0, 1).contiguous(); v = synth_kv("v", n_kv, L, 900 + slot, dev).transpose(0, 1).contiguous()
+            rc.prefill(slot, k, v); oc.prefill(slot, k, v)
+        slots = torch.tensor([0, 1], dtype=torch.int32, device=dev)
+        g = torch.Generator(device=dev).manual_seed(3)
+        for step in range(40):
+            k = (torch.randn(2, n_kv, 128, generator=g, device=dev) * 2).to(torch.bfloat16); v = torch.randn(2, n_kv, 128, generator=g, device=dev).to(torch.bfloat16)
+            rc.append(slots, k, v); oc.append(slots, k, v)
+        torch.cuda.synchronize()
+        same = bool(torch.equal(rc.S, oc.S) and torch.equal(rc.tail_len, oc.tail_len))
+        for a, b in ((rc.k, oc.k), (rc.v, oc.v)):
+            used = int(a.ovf_used.max())
+            same = same and all(torch.equal(getattr(a, f), getattr(b, f)) for f in ("sm", "codes", "flags", "tile_off", "ovf_used", "base3", "base4"))
+            same = same and torch.equal(a.ovf.view(a.H, -1)[:, :used], b.ovf.view(b.H, -1)[:, :used])
+            for h in range(a.H):
+                n = int(rc.tail_len[h])
+                same = same and torch.equal(a.tail[h, :n], b.tail[h, :n])
+        q = torch.randn(2, n_q, 128, generator=g, device=dev).to(torch.bfloat16)
+        o_r = rc.attention(q, slots, 128 ** -0.5); o_o = oc.attention(q, slots, 128 ** -0.5)
+        return {"slot_cache_bit_identical": same, "slot_cache_attn_max_abs_diff": float((o_r.float() - o_o.float()).abs().max())}
+    except Exception as e:                                      # a side check must not lose the timings above
+        return {"slot_cache_bit_identical": None, "slot_cache_error": repr(e)[:200]}
 
 
 if __name__ == "__main__":
