@@ -108,7 +108,56 @@ def main():
     out["attn_us_best"] = min(res.values())
     out["gaac_b200_us_same_protocol"] = timed(lambda i: ours.attention(q, *sets[i % N_SETS], scale=scale))
     out.update(slot_cache_parity(torch, ref, ours, dev))
+    out.update(paged_store_parity(torch, ref, ours, dev))
     print(json.dumps(out), flush=True)
+
+
+def paged_store_parity(torch, ref, ours, dev) -> dict:
+    """The paged store of both packages fed with the same entries (three prompts stored block by block, then 24 decode steps of one
+    token per sequence, so filling blocks pass through raw tiles and are finalised): the block buffers must be byte-identical, the
+    mode tables must agree on which tiles are compressed (raw tile numbers may differ: the pop order of concurrent programs is
+    free), and decoding every block back through each package's own decoder must give the same BF16 rows."""
+    from gaac_b200.synth import synth_kv
+    try:
+        from gaac.vllm.store import LayerState as RefState, OVF_OFF
+        from gaac_b200.vllm.store import LayerState as OurState
+        n_kv, num_blocks, ovf_slot = 4, 96, 128
+        TS = OVF_OFF + ovf_slot
+        cal_k, cal_v = synth_kv("k", n_kv, 2048, 700, dev), synth_kv("v", n_kv, 2048, 700, dev)
+        ck, cv = ref.Codec(n_kv, device=dev).calibrate(cal_k), ref.Codec(n_kv, device=dev).calibrate(cal_v)
+        bases = {"k3": ck.base3, "k4": ck.base4, "v3": cv.base3, "v4": cv.base4}
+        rs, os_ = RefState(num_blocks, n_kv, 64, bases, ovf_slot, dev), OurState(num_blocks, n_kv, 64, bases, ovf_slot, dev)
+        rbuf = torch.zeros(num_blocks * 2 * n_kv * TS, dtype=torch.uint8, device=dev); obuf = torch.zeros_like(rbuf)
+        lens, blocks, nxt = [150, 33, 64], [], 0
+        for i, L in enumerate(lens):
+            k = synth_kv("k", n_kv, L, 700, dev).transpose(0, 1).contiguous(); v = synth_kv("v", n_kv, L, 700, dev).transpose(0, 1).contiguous()
+            nb = (L + 15) // 16
+            bl = list(range(nxt, nxt + nb + 2)); nxt += nb + 2; blocks.append(bl)
+            ent = torch.tensor([[bl[t], t * 16, 0, min(16, L - t * 16)] for t in range(nb)], dtype=torch.int32, device=dev)
+            for st, buf in ((rs, rbuf), (os_, obuf)):
+                st.store(k.view(torch.int16), v.view(torch.int16), buf, ent, torch.empty(nb * 2 * n_kv, dtype=torch.int32, device=dev))
+        g = torch.Generator(device=dev).manual_seed(11)
+        for step in range(24):
+            k = (torch.randn(3, n_kv, 128, generator=g, device=dev) * cal_k[:, :3].transpose(0, 1).float().abs().clamp(min=0.05)).to(torch.bfloat16)
+            v = (torch.randn(3, n_kv, 128, generator=g, device=dev) * cal_v[:, :3].transpose(0, 1).float().abs().clamp(min=0.05)).to(torch.bfloat16)
+            ent = torch.tensor([[blocks[i][lens[i] // 16], i, lens[i] % 16, 1] for i in range(3)], dtype=torch.int32, device=dev)
+            for st, buf in ((rs, rbuf), (os_, obuf)):
+                st.store(k.view(torch.int16), v.view(torch.int16), buf, ent, torch.empty(3 * 2 * n_kv, dtype=torch.int32, device=dev))
+            lens = [l + 1 for l in lens]
+        torch.cuda.synchronize()
+        same = bool(torch.equal(rbuf, obuf) and torch.equal(rs.mt < 0, os_.mt < 0) and torch.equal(rs.mt[rs.mt >= 0], os_.mt[os_.mt >= 0])
+                    and int(rs.top) == int(os_.top) and int(rs.err) == int(os_.err) == 0)
+        pairs, row = [], 0
+        for i, L in enumerate(lens):
+            for t in range((L + 15) // 16):
+                pairs.append([blocks[i][t], row, min(16, L - t * 16)]); row += 16
+        pairs = torch.tensor(pairs, dtype=torch.int32, device=dev)
+        rk = torch.zeros(row, n_kv, 128, dtype=torch.bfloat16, device=dev); rv = torch.zeros_like(rk); ok = torch.zeros_like(rk); ov = torch.zeros_like(rk)
+        rs.decode_blocks(rbuf, pairs, rk, rv); os_.decode_blocks(obuf, pairs, ok, ov)
+        same = same and torch.equal(rk.view(torch.int16), ok.view(torch.int16)) and torch.equal(rv.view(torch.int16), ov.view(torch.int16))
+        return {"paged_store_bit_identical": bool(same), "paged_raw_tiles_in_use": int((os_.mt < 0).sum())}
+    except Exception as e:
+        return {"paged_store_bit_identical": None, "paged_store_error": repr(e)[:300]}
 
 
 def slot_cache_parity(torch, ref, ours, dev) -> dict:
