@@ -27,17 +27,18 @@ def _extension_dir() -> str:
     return ext
 
 
-def _preload_extension(ref_kernel) -> bool:
-    """Hand the prebuilt gaac_attn_v1.so to the reference's loader cache (gaac/kernel.py:329-337 keeps the loaded module in `_mod`).
+def _preload_extension(ref_kernel, name: str = "gaac_attn_v1") -> bool:
+    """Hand a prebuilt extension to the reference's loader cache (gaac/kernel.py:329-337 and gaac/vllm/paged_kernel.py:282-288
+    keep the loaded module in `_mod`).
     torch's JIT loader would rebuild it (over a minute of nvcc) because a copied tree does not keep the file times ninja logged;
     the library is the reference's own kernel, compiled from its own source by its own build step, only that step is not
     repeated.  Returns False (and the reference then builds it itself) when the library is not there or does not load."""
-    so = os.path.join(os.environ["TORCH_EXTENSIONS_DIR"], "gaac_attn_v1", "gaac_attn_v1.so")
+    so = os.path.join(os.environ["TORCH_EXTENSIONS_DIR"], name, name + ".so")
     try:
         import importlib.machinery, importlib.util
         import torch  # noqa: F401  (the extension links against libtorch)
-        loader = importlib.machinery.ExtensionFileLoader("gaac_attn_v1", so)
-        mod = importlib.util.module_from_spec(importlib.util.spec_from_loader("gaac_attn_v1", loader))
+        loader = importlib.machinery.ExtensionFileLoader(name, so)
+        mod = importlib.util.module_from_spec(importlib.util.spec_from_loader(name, loader))
         loader.exec_module(mod)
         ref_kernel._mod = mod
         return True
@@ -109,7 +110,49 @@ def main():
     out["gaac_b200_us_same_protocol"] = timed(lambda i: ours.attention(q, *sets[i % N_SETS], scale=scale))
     out.update(slot_cache_parity(torch, ref, ours, dev))
     out.update(paged_store_parity(torch, ref, ours, dev))
+    out.update(paged_attention_timing(torch, ref, dev, timed))
     print(json.dumps(out), flush=True)
+
+
+def paged_attention_timing(torch, ref, dev, timed) -> dict:
+    """The reference's paged kernel (gaac_vpaged + gaac_combine2) and ours on the same block buffer: 16 ragged sequences as in
+    bench.py --workload paged16, stored once (the stores are byte-identical, see paged_store_parity)."""
+    import numpy as np
+    from gaac_b200.synth import synth_kv
+    try:
+        import gaac.vllm.paged_kernel as rpk
+        from gaac_b200.vllm.store import LayerState, OVF_OFF
+        from gaac_b200.vllm.paged_kernel import paged_attention as our_paged
+        from gaac_b200.kernel import choose_nsplit_sm100
+        if not _preload_extension(rpk, "gaac_vpaged128_v1"):
+            return {"paged_attn_unavailable": "the reference's paged extension is not prebuilt"}
+        n_kv, G, B = 8, 4, 16
+        rng = np.random.default_rng(0)
+        lens = [int(l) // 16 * 16 + int(t) for l, t in zip(rng.integers(4096, 65537, B), rng.integers(0, 16, B))]
+        num_blocks = sum((l + 15) // 16 for l in lens) + 1024
+        ck = ref.Codec(n_kv, device=dev).calibrate(synth_kv("k", n_kv, 2048, 7, dev)); cv = ref.Codec(n_kv, device=dev).calibrate(synth_kv("v", n_kv, 2048, 7, dev))
+        st = LayerState(num_blocks, n_kv, raw_tiles=B * 2 * n_kv + 4096, ovf_slot=128, device=dev, bases={"k3": ck.base3, "k4": ck.base4, "v3": cv.base3, "v4": cv.base4})
+        buf = torch.zeros(num_blocks * 2 * n_kv * (OVF_OFF + 128), dtype=torch.uint8, device=dev)
+        perm = rng.permutation(num_blocks); used = 0
+        bt = np.zeros((B, (max(lens) + 15) // 16), np.int32)
+        for i, L in enumerate(lens):
+            k = synth_kv("k", n_kv, L, 7, dev).transpose(0, 1).contiguous(); v = synth_kv("v", n_kv, L, 7, dev).transpose(0, 1).contiguous()
+            nb = (L + 15) // 16
+            blocks = perm[used:used + nb]; used += nb; bt[i, :nb] = blocks
+            ent = np.array([[blocks[t], t * 16, 0, min(16, L - t * 16)] for t in range(nb)], np.int32)
+            st.store(k, v, buf, torch.from_numpy(ent).to(dev), torch.empty(nb * 2 * n_kv, dtype=torch.int32, device=dev))
+        btd = torch.from_numpy(bt).to(dev); sl = torch.tensor(lens, dtype=torch.int32, device=dev)
+        q = torch.randn(B, n_kv * G, 128, generator=torch.Generator(device=dev).manual_seed(2), device=dev).to(torch.bfloat16)
+        o_r = torch.empty(B, n_kv * G * 128, dtype=torch.bfloat16, device=dev); o_o = torch.empty_like(o_r)
+        ns0 = rpk.choose_nsplit(B, n_kv, max(lens))
+        res = {ns: timed(lambda i: rpk.paged_attention(q, o_r, buf, st.raw, st.mt, btd, sl, st.bases, st.TS, n_kv * G, n_kv, ns), n=20, warm=3) for ns in sorted({ns0, 4, 8, 16})}
+        rpk.paged_attention(q, o_r, buf, st.raw, st.mt, btd, sl, st.bases, st.TS, n_kv * G, n_kv, 8)
+        ns_o = choose_nsplit_sm100(B, n_kv, bt.shape[1] * 16, ragged=True)
+        us_o = timed(lambda i: our_paged(q, o_o, buf, st.raw, st.mt, btd, sl, st.bases, st.TS, n_kv * G, n_kv, ns_o), n=20, warm=3)
+        return {"paged_attn_us_by_nsplit": res, "paged_attn_us_own_nsplit": res[ns0], "paged_own_nsplit": ns0, "paged_attn_us_best": min(res.values()),
+                "paged_gaac_b200_us": us_o, "paged_attn_max_abs_diff_vs_gaac_b200": float((o_r.float() - o_o.float()).abs().max())}
+    except Exception as e:
+        return {"paged_attn_error": repr(e)[:300]}
 
 
 def paged_store_parity(torch, ref, ours, dev) -> dict:
