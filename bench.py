@@ -25,6 +25,7 @@ WORKLOAD = "decode attention, batch 1, 32 q heads / 8 kv heads (GQA 4), head_dim
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_attn_kernel launch at this workload, from the ncu capture
 # summarised in profiles/; None until a capture exists.
 NCU_TRAFFIC_BYTES = 196.6e6
+LAYERS_PER_GRAPH = 16              # layers captured in one CUDA graph of the timed region (a 32-layer model replays two of them per step)
 
 
 def measured_peak_gbs():
@@ -262,9 +263,10 @@ def run_ours(args):
         layer(i, q)
     barrier()
     # CUDA graphs: the launch path of a decode loop, which the reference's serving engine also captures.  One graph holds
-    # N_SETS consecutive layers (the kernels carry programmatic-dependent-launch edges, so a layer's CTAs become resident while
-    # the previous layer's split merge is finishing); single-layer graphs cover steps % N_SETS.
-    graphs, g_all, launch_mode = None, None, "eager"
+    # LAYERS_PER_GRAPH consecutive layers, as a decode step of a model does (the kernels carry programmatic-dependent-launch edges,
+    # so a layer's CTAs become resident while the previous layer's split merge is finishing); single-layer graphs cover the
+    # remainder of steps / LAYERS_PER_GRAPH.
+    graphs, g_all, g_four, launch_mode = None, None, None, "eager"
     if not (args.profile or args.no_graph):
         try:
             graphs = []
@@ -275,10 +277,13 @@ def run_ours(args):
                 graphs.append((g_, o_))
             g_all = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g_all):
-                o_all = [layer(i, q) for i in range(N_SETS)]
-            launch_mode = f"cuda graph replay, {N_SETS} layers per graph"
+                o_all = [layer(i, q) for i in range(LAYERS_PER_GRAPH)]
+            g_four = torch.cuda.CUDAGraph()                                              # for the remainder of steps / LAYERS_PER_GRAPH
+            with torch.cuda.graph(g_four):
+                o_four = [layer(i, q) for i in range(4)]
+            launch_mode = f"cuda graph replay, {LAYERS_PER_GRAPH} layers per graph"
         except Exception as e:                                                          # capture unsupported: same on every rank
-            graphs = g_all = None; launch_mode = f"eager (graph capture failed: {type(e).__name__})"
+            graphs = g_all = g_four = None; launch_mode = f"eager (graph capture failed: {type(e).__name__})"
         barrier()
 
     def run_steps(n, events=None):
@@ -289,9 +294,11 @@ def run_ours(args):
                 layer(i, q)
                 if events: events[i][1].record()
             return
-        for _ in range(n // N_SETS): g_all.replay()
-        for i in range(n % N_SETS): graphs[i][0].replay()
-    run_steps(2 * N_SETS + 1)
+        for _ in range(n // LAYERS_PER_GRAPH): g_all.replay()
+        n %= LAYERS_PER_GRAPH
+        for _ in range(n // 4): g_four.replay()
+        for i in range(n % 4): graphs[i % N_SETS][0].replay()
+    run_steps(2 * LAYERS_PER_GRAPH + 1)
     barrier()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)] if graphs is None else None
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
