@@ -1,8 +1,9 @@
 // Fused decode attention over GAAC-compressed K/V (sm_100a): slot layout and paged layout in one kernel template.
 //
 // CTA = (batch row, kv head, context split), ATT_WARPS warps, one CTA per SM.  Every warp streams its own 16-token tiles
-// through a private two-stage shared-memory ring filled with cp.async, rebuilds BF16 K/V fragments in registers (byte-SWAR,
-// gaac_tile.h) and feeds mma.sync m16n8k16:
+// through a private two-stage shared-memory ring filled by bulk asynchronous copies (the TMA engine without a tensor map,
+// completion counted in bytes on an mbarrier), rebuilds BF16 K/V fragments in registers (byte-SWAR, gaac_tile.h) and feeds
+// mma.sync m16n8k16:
 //   S^T[16 tok x 8 heads] = K[16 x 128] . Q^T        O^T[128 dims x 8 heads] += V^T[128 x 16 tok] . P^T
 // with an fp32 online softmax in the exp2 domain whose maximum is raised lazily.  Raw BF16 tiles (the slot layout's tail, the
 // paged layout's filling block and raw-fallback tiles) are read straight from global memory into the same fragments.  Tiles
@@ -10,16 +11,17 @@
 // one partial (m, l, acc[128]) per query head, and the last CTA of a (row, kv head) to finish merges the splits and writes
 // the output, so one launch does the whole layer.
 //
-// What the measurements on B200 say about the copies (they shaped the code below):
-//  * cp.async.cg (L1 bypass) sends one 32-byte sector request per LANE over the crossbar and writes shared memory one lane
-//    chunk per wavefront: twice the L2->SM traffic and ~6x the shared-memory write wavefronts of cp.async.ca, which
-//    coalesces the lanes of a warp.  The 16-byte copies therefore use .ca (GAAC_CP16_CA).
-//  * the 16-byte chunks of the sign/mantissa planes are stored XOR-swizzled (GAAC_SWZ) so that both the cp.async writes
-//    (32 consecutive global chunks per instruction) and the later 16-byte fragment reads (stride-2 / stride-4 chunks per
-//    lane) touch eight different bank groups per quarter-warp.
-//  * the kernel is bound by instruction issue (ALU pipe) and by the shared-memory pipe, not by HBM: the 4096-entry code
-//    table (GAAC_LUTC) trades four logic instructions per lookup for one load with ~3.5-way bank conflicts; both settings
-//    run within 2 % of each other.
+// What the measurements on B200 say (they shaped the code below):
+//  * per-lane cp.async copies (18 instructions per tile pair and warp) kept the load/store unit 60 % busy, and it is shared
+//    with the fragment reads: the L1-bypassing form sends one sector request per lane and writes shared memory one lane
+//    chunk per wavefront, the caching form coalesces but still costs ~22 cycles per instruction.  Bulk copies take that
+//    work off the SM; they want few large copies (one 128-byte copy per row, which would allow a conflict-free skewed
+//    layout, was 15 % slower), so shared memory holds the storage order and the 16-byte fragment reads accept a 2-way (K) /
+//    4-way (V) bank conflict (worth 0.7 us of 74).
+//  * the kernel is bound by instruction issue (ALU pipe) and by the shared-memory pipe, not by HBM: spreading the 3-bit
+//    codes through the 4096-entry table costs one load with ~3.5-way bank conflicts, by arithmetic two multiply-adds and
+//    three logic instructions; one half of each group through the table and the other by arithmetic is the fastest
+//    mix (GAAC_LUTC = 2; 1 = table only, 0 = arithmetic only).
 //
 // Fragment conventions follow the reference kernel (gaac/kernel.py:62-66,160-194), whose storage order they mirror.
 #include <cuda_bf16.h>
@@ -29,32 +31,20 @@
 
 namespace gaac {
 
-#ifndef GAAC_CP16_CA
-#define GAAC_CP16_CA 1
-#endif
 #ifndef GAAC_LUTC
 #define GAAC_LUTC 2
-#endif
-#ifndef GAAC_BULK
-#define GAAC_BULK 1
-#endif
-#ifndef GAAC_SWZ
-#define GAAC_SWZ 1
 #endif
 constexpr int ATT_WARPS = 16;
 constexpr int ATT_THREADS = ATT_WARPS * 32;
 constexpr int NSTAGE = 2;
 constexpr int ESC_WIN = 256;                         // escape bytes staged per tile and kind; longer tiles read theirs from global memory
-// stage layout (bytes)
-// stage layout (bytes); each escape window is preceded by 16 bytes that stay zero: a group without an escape byte reads one of them
-constexpr int ZPAD = 16;
-#if GAAC_BULK
+// ---- stage layout (bytes)
 // Stage = 16 bytes (mbarrier, then 8 bytes that stay zero) + a block per side:
 //   sign/mantissa (2048, storage order) | codes (768) | tag words (64) | escape window (ESC_WIN + 16: it starts at the
 //   16-byte boundary below the tile's first escape byte).  Every piece is ONE bulk copy: copies of 128 bytes (one per
 //   row, skewed to avoid the bank conflicts of the storage order) were measured 15 % slower, the copy engine wants few large
 //   copies, so the fragment reads accept a 2-way (K) / 4-way (V) conflict.
-// codes | tags | escapes are adjacent as in the paged tile slot, so the paged layout fetches them with one copy.
+// A side block is laid out as the paged tile slot is, so the paged layout fetches a whole slot with one copy.
 constexpr int ESC_COPY = ESC_WIN + 16;
 constexpr int SM_ROW = 128;
 constexpr int SB_SM = 0, SB_CD = SB_SM + 16 * SM_ROW, SB_FL = SB_CD + 768, SB_ESC = SB_FL + 64, SIDE_BYTES = SB_ESC + ESC_COPY;
@@ -63,24 +53,16 @@ constexpr int ST_KSM = ST_K + SB_SM, ST_KCD = ST_K + SB_CD, ST_KFL = ST_K + SB_F
 constexpr int ST_VSM = ST_V + SB_SM, ST_VCD = ST_V + SB_CD, ST_VFL = ST_V + SB_FL, ST_VESC = ST_V + SB_ESC;
 constexpr int STAGE_BYTES = ST_V + SIDE_BYTES;
 static_assert(SB_CD - SB_SM == SLOT_CD_OFF && SB_FL - SB_SM == SLOT_FL_OFF && SB_ESC - SB_SM == SLOT_OVF_OFF, "side block laid out as the paged tile slot");
-#else
-constexpr int ST_KSM = 0, ST_KCD = 2048, ST_VSM = 2816, ST_VCD = 4864, ST_KFL = 5632, ST_VFL = 5696;
-constexpr int ST_KZ = 5760, ST_KESC = ST_KZ + ZPAD, ST_VZ = ST_KESC + ESC_WIN, ST_VESC = ST_VZ + ZPAD;
-constexpr int STAGE_BYTES = ST_VESC + ESC_WIN;       // 6304
-#endif
-// CTA-wide tables in front of the rings: escape-byte table, K base words [j][g], V base words [r][g], a zero word
 constexpr int META_TILES = 512;                      // tiles of a CTA's range whose metadata is staged (longer ranges read the rest from global)
 // CTA tables: escape-byte table (2 KiB), K / V base words, per-tile metadata, and the code table: four 3-bit codes -> four bytes
 // for all 4096 values of a 12-bit field (16 KiB).  The table turns four logic instructions per lookup into one shared-memory load.
 constexpr int TB_LUTX = 0, TB_KB = 2048, TB_VB = TB_KB + 256, TB_META = TB_VB + 256, TB_LUTC = TB_META + 2 * META_TILES * 4;
 constexpr int TABLE_BYTES = TB_LUTC + (GAAC_LUTC ? 4096 * 4 : 0);
 constexpr int ATT_SMEM = TABLE_BYTES + ATT_WARPS * NSTAGE * STAGE_BYTES;
-#if GAAC_BULK
 static_assert(TABLE_BYTES % 16 == 0 && STAGE_BYTES % 16 == 0 && ST_KSM % 16 == 0 && ST_KCD % 16 == 0 && ST_KFL % 16 == 0 && ST_KESC % 16 == 0 &&
               ST_VSM % 16 == 0 && ST_VCD % 16 == 0 && ST_VFL % 16 == 0 && ST_VESC % 16 == 0 && ESC_COPY % 16 == 0 && ST_MBAR % 8 == 0 && SM_ROW % 16 == 0,
               "bulk copies need 16-byte aligned shared-memory destinations and sizes");
 static_assert(ATT_SMEM + 64 <= 232448, "one CTA per SM: at most 227 KB of shared memory, static part included");
-#endif
 constexpr unsigned FULLM = 0xffffffffu;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 
@@ -104,10 +86,6 @@ __device__ __forceinline__ void mma16816(float* c, const u32* a, u32 b0, u32 b1)
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void cp16(u32 dst, const void* src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src)); }
-__device__ __forceinline__ void cp4(u32 dst, const void* src) { asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src)); }
-__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 // ---- bulk asynchronous copies (TMA engine, no tensor map): global -> shared, completion counted in bytes on an mbarrier.
 // Both addresses are 16-byte aligned and the size is a multiple of 16 at every call site.
 __device__ __forceinline__ void mbar_init(u32 mbar, u32 count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(mbar), "r"(count)); }
@@ -137,78 +115,11 @@ __device__ __forceinline__ float fast_exp2(float x) { float y; asm("ex2.approx.f
 // of a raw tile of the pool).
 struct TileMeta { int mk, mv; };
 
-// Loop-invariant addressing of one lane.  The slot layout keeps byte offsets that are valid for both sides (K and V buffers
-// have the same geometry); the paged layout needs none (a tile is one contiguous slot).
+// Per-head values of the slot layout that the copy addressing needs.
 struct LaneAddr {
-  long sm_off, cd_off, fl_off;   // head offset inside sm / codes / flags (bytes) + the lane's share: 16*lane, 16*lane, 16*(lane&3)
   int ohk, ohv;                  // first escape byte of the head inside ovf
   int availk, availv;            // bytes from there to the end of the allocation (clamped to int)
-  u32 kdst, vdst;                // lane part of the permuted shared-memory destinations of the sign/mantissa chunks
 };
-
-// Escape bytes of one side of one tile: global address of the first one, bytes that may be read from there.
-struct EscRef { const uint8_t* p; int lim; };
-
-// Escape bytes, counted from the tile's first escape byte `esc`, that the staged window holds: the window starts at the
-// 4-byte boundary below `esc`, is ESC_WIN bytes long at most, is copied in whole words and stays inside the allocation
-// (alloc_left = bytes from `esc` to the end of the escape buffer).
-__device__ __forceinline__ int esc_window_bytes(const uint8_t* esc, int alloc_left) {
-  const int wsh = (int)(reinterpret_cast<uintptr_t>(esc) & 3);
-  return max(0, min(ESC_WIN, (alloc_left + wsh) & ~3) - wsh);
-}
-
-#if GAAC_BULK
-// Bytes of the bulk copy that stages the escape window of a tile whose first escape byte is `esc`: the copy starts at the
-// 16-byte boundary below `esc`, is ESC_COPY bytes long at most, a multiple of 16, and stays inside [base, end); 0 when the
-// boundary lies before `base` (the tile then reads its escapes from global memory).
-__device__ __forceinline__ int esc_copy_bytes(const uint8_t* esc, const uint8_t* base, const uint8_t* end) {
-  const uint8_t* a = reinterpret_cast<const uint8_t*>(reinterpret_cast<uintptr_t>(esc) & ~(uintptr_t)15);
-  if (a < base) return 0;
-  return (int)min((long)ESC_COPY, (long)((end - a) & ~(long)15));
-}
-#endif
-
-template <int DOFF, int SOFF> __device__ __forceinline__ void cp16i(u32 dst, const void* src) {
-#if GAAC_CP16_CA
-  asm volatile("cp.async.ca.shared.global [%0+%2], [%1+%3], 16;\n" ::"r"(dst), "l"(src), "n"(DOFF), "n"(SOFF));
-#else
-  asm volatile("cp.async.cg.shared.global [%0+%2], [%1+%3], 16;\n" ::"r"(dst), "l"(src), "n"(DOFF), "n"(SOFF));
-#endif
-}
-template <int DOFF, int SOFF> __device__ __forceinline__ void cp4i(u32 dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0+%2], [%1+%3], 4;\n" ::"r"(dst), "l"(src), "n"(DOFF), "n"(SOFF));
-}
-
-// cp.async copies of one tile into stage `st`.  sm / cd point at the lane's 16-byte chunk (tile base + 16*lane), fl at
-// chunk (lane & 3) of the tag words.  Shared-memory destinations of the sign/mantissa chunks are permuted so that the
-// later 16-byte reads of a warp are consecutive:
-//   K: global chunk c = (octet o = c>>6, lane l = (c>>1)&31, half = c&1)  ->  slot o*64 + half*32 + l
-//   V: global chunk c = (lane l = c>>2, token slot t = c&3)               ->  slot t*32 + l
-// With c = lane + 32k the lane part of the slot is constant (LaneAddr::kdst, vdst) and the k part is an immediate.
-__device__ __forceinline__ void issue_k(u32 st, const uint8_t* sm, const uint8_t* cd, const uint8_t* fl, const LaneAddr& L, int lane) {
-  const u32 d = st + L.kdst, dl = st + 16 * lane;
-  cp16i<ST_KSM, 0>(d, sm); cp16i<ST_KSM + 256, 512>(d, sm); cp16i<ST_KSM + 1024, 1024>(d, sm); cp16i<ST_KSM + 1280, 1536>(d, sm);
-  cp16i<ST_KCD, 0>(dl, cd);
-  if (lane < 16) cp16i<ST_KCD + 512, 512>(dl, cd);
-  if (lane < 4) cp16i<ST_KFL, 0>(dl, fl);
-}
-__device__ __forceinline__ void issue_v(u32 st, const uint8_t* sm, const uint8_t* cd, const uint8_t* fl, const LaneAddr& L, int lane) {
-  const u32 d = st + L.vdst, dl = st + 16 * lane;
-  cp16i<ST_VSM, 0>(d, sm); cp16i<ST_VSM + 128, 512>(d, sm); cp16i<ST_VSM + 256, 1024>(d, sm); cp16i<ST_VSM + 384, 1536>(d, sm);
-  cp16i<ST_VCD, 0>(dl, cd);
-  if (lane >= 16) cp16i<ST_VCD + 256, 256>(dl, cd);
-  if (lane >= 28) cp16i<ST_VFL - 16 * 28, 0>(dl, fl);
-}
-// Escape window: whole words from the 4-byte boundary below the first escape byte; win = shared-memory address of the window.
-__device__ __forceinline__ void issue_esc(u32 win, const EscRef& e, int lane) {
-  const int wsh = (int)(reinterpret_cast<uintptr_t>(e.p) & 3);
-  const int lim = min(ESC_WIN, (e.lim + wsh) & ~3);           // bytes to copy, counted from the boundary
-  const uint8_t* a = e.p - wsh + 4 * lane;
-  const u32 d = win + 4 * lane;
-  static_assert(ESC_WIN <= 256, "two words per lane");
-  if (4 * lane < lim) cp4i<0, 0>(d, a);
-  if (4 * lane + 128 < lim) cp4i<128, 128>(d, a);
-}
 
 // Running state of one warp.
 struct WarpAcc {
@@ -351,16 +262,8 @@ __device__ __forceinline__ void k_scores(float* sc, const uint8_t* stage, const 
     const u32 fl = __shfl_sync(FULLM, flrow, 8 * o + r);
     pos[o] = __shfl_sync(FULLM, rowoff, 8 * o + r) + esc_prefix(fl, 8 * j) + es.off;
     t8[o] = fl >> (8 * j);
-#if GAAC_BULK
     s0[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + (8 * o + (lane >> 2)) * SM_ROW + 32 * (lane & 3));   // storage order, skewed rows
     s1[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + (8 * o + (lane >> 2)) * SM_ROW + 32 * (lane & 3) + 16);
-#elif GAAC_SWZ
-    s0[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + lane));
-    s1[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + 32 + (lane ^ 4)));
-#else
-    s0[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + lane));
-    s1[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + 16 * (o * 64 + 32 + lane));
-#endif
     const u32* c = reinterpret_cast<const u32*>(stage + ST_KCD + o * 384 + 12 * lane);
     cd[o][0] = c[0]; cd[o][1] = c[1]; cd[o][2] = c[2];
   }
@@ -393,13 +296,7 @@ __device__ __forceinline__ void v_accum(WarpAcc& A, const uint8_t* stage, const 
     const u32 fl = __shfl_sync(FULLM, flrow, 16 + tok);
     pos[t] = __shfl_sync(FULLM, rowoff, 16 + tok) + esc_prefix(fl, 4 * r) + es.off;
     t4[t] = fl >> (4 * r);
-#if GAAC_BULK
     sm[t] = *reinterpret_cast<const uint4*>(stage + ST_VSM + (lane >> 1) * SM_ROW + 64 * (lane & 1) + 16 * t);
-#elif GAAC_SWZ
-    sm[t] = *reinterpret_cast<const uint4*>(stage + ST_VSM + 16 * (t * 32 + (lane ^ (2 * t))));
-#else
-    sm[t] = *reinterpret_cast<const uint4*>(stage + ST_VSM + 16 * (t * 32 + lane));
-#endif
   }
   {
     const uint2* c2 = reinterpret_cast<const uint2*>(stage + ST_VCD + 24 * lane);
@@ -508,14 +405,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
   uint8_t* ring = smem + TABLE_BYTES + warp * (NSTAGE * STAGE_BYTES);
   const u32 ring_s = (u32)__cvta_generic_to_shared(ring);
   LaneAddr L;
-  L.sm_off = smh + 16 * lane; L.cd_off = cdh + 16 * lane; L.fl_off = rowb * 4 + 16 * (lane & 3);
   L.ohk = ohk; L.ohv = ohv;
   L.availk = PAGED ? 0 : (int)min((long)(1 << 30), p.K.ovf_bytes - ohk); L.availv = PAGED ? 0 : (int)min((long)(1 << 30), p.V.ovf_bytes - ohv);
-#if GAAC_SWZ
-  L.kdst = 16 * (32 * (lane & 1) + ((lane >> 1) ^ (4 * (lane & 1)))); L.vdst = 16 * (32 * (lane & 3) + ((lane >> 2) ^ (2 * (lane & 3))));
-#else
-  L.kdst = 16 * (32 * (lane & 1) + (lane >> 1)); L.vdst = 16 * (32 * (lane & 3) + (lane >> 2));
-#endif
   const int* metak = reinterpret_cast<const int*>(smem + TB_META);
   const int* metav = metak + META_TILES;
   auto global_meta = [&](int tile) -> TileMeta {
@@ -526,32 +417,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     if (tile - tlo < META_TILES) return TileMeta{metak[tile - tlo], metav[tile - tlo]};
     return global_meta(tile);
   };
-  auto esc_k = [&](int mk) -> EscRef {
-    if (PAGED) return EscRef{p.buf + (long)mk * p.TS + SLOT_OVF_OFF, p.ovf_slot};
-    return EscRef{p.K.ovf + ((long)L.ohk + mk), min(ESC_WIN, L.availk - mk)};
-  };
-  auto esc_v = [&](int mv) -> EscRef {
-    if (PAGED) return EscRef{p.buf + (long)mv * p.TS + SLOT_OVF_OFF, p.ovf_slot};
-    return EscRef{p.V.ovf + ((long)L.ohv + mv), min(ESC_WIN, L.availv - mv)};
-  };
-  auto issue_payload = [&](u32 st, int tile, const TileMeta& m) {      // slot layout: needs no metadata
-    if (PAGED) {
-      if (m.mk >= 0) { const uint8_t* sk = p.buf + (long)m.mk * p.TS + 16 * lane; issue_k(st, sk, sk + SLOT_CD_OFF, sk + SLOT_FL_OFF, L, lane); }
-      if (m.mv >= 0) { const uint8_t* sv = p.buf + (long)m.mv * p.TS + 16 * lane; issue_v(st, sv, sv + SLOT_CD_OFF, sv + (SLOT_FL_OFF - 16 * 28), L, lane); }
-    } else {
-      const long so = L.sm_off + (long)tile * TILE_SM, co = L.cd_off + (long)tile * TILE_CD, fo = L.fl_off + (long)tile * (4 * T);
-      issue_k(st, p.K.sm + so, p.K.codes + co, reinterpret_cast<const uint8_t*>(p.K.flags) + fo, L, lane);
-      issue_v(st, p.V.sm + so, p.V.codes + co, reinterpret_cast<const uint8_t*>(p.V.flags) + fo, L, lane);
-    }
-  };
-  auto issue_escapes = [&](u32 st, const TileMeta& m) {
-    if (!PAGED || m.mk >= 0) issue_esc(st + ST_KESC, esc_k(m.mk), lane);
-    if (!PAGED || m.mv >= 0) issue_esc(st + ST_VESC, esc_v(m.mv), lane);
-  };
-#if GAAC_BULK
-  // Bulk copies of one tile into stage `st`, issued by lane 0: it arms the stage's mbarrier with the total byte count (one
-  // arrival per phase), then issues up to eight copies (K, V) x (sign/mantissa, codes, tag words, escape window); in the paged
-  // layout a whole slot is one copy.  (Spreading the copies over eight lanes was measured slower than this.)
   // Slot layout, escape window of a tile whose escapes start `m` bytes into the head's escape bytes, in 32-bit arithmetic:
   // w16 = its first byte's offset inside a 16-byte unit, n = bytes of the copy from the unit's start (a multiple of 16, at most
   // ESC_COPY, inside the allocation; 0 when the unit starts before the allocation).
@@ -592,13 +457,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     if (PAGED) return p.buf + (long)m * p.TS + SLOT_OVF_OFF;
     return (vside ? p.V.ovf : p.K.ovf) + ((long)(vside ? L.ohv : L.ohk) + m);
   };
-#endif
   // ---- prologue.  Everything that reads global memory is put in flight first and consumed afterwards: the payload of the
   // warp's first tile (needs no metadata in the slot layout), the tile's metadata, the metadata of the CTA's range, the
   // query rows; then the tables are built while those loads travel.
   int tile = tlo + warp;
   TileMeta cur{0, 0};
-#if GAAC_BULK
   if (lane == 0) {                                    // one barrier per stage, one arrival (this lane's) per phase; 8 zero bytes beside it
     mbar_init(ring_s + ST_MBAR, 1); mbar_init(ring_s + STAGE_BYTES + ST_MBAR, 1);
     *reinterpret_cast<unsigned long long*>(ring + ST_ZERO) = 0ull; *reinterpret_cast<unsigned long long*>(ring + STAGE_BYTES + ST_ZERO) = 0ull;
@@ -622,12 +485,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       cur = global_meta(tile);
     }
   }
-#else
-  if (tile < thi) {
-    if (PAGED) { cur = global_meta(tile); issue_payload(ring_s, tile, cur); }
-    else { issue_payload(ring_s, tile, cur); cur = global_meta(tile); }
-  }
-#endif
   int* mk_s = reinterpret_cast<int*>(smem + TB_META);
   int* mv_s = mk_s + META_TILES;
   const int nstaged = min(thi - tlo, META_TILES);
@@ -663,17 +520,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
 #if GAAC_LUTC
     for (int i = tid; i < 4096; i += ATT_THREADS) reinterpret_cast<u32*>(smem + TB_LUTC)[i] = spread_codes4((u32)i);
 #endif
-#if !GAAC_BULK
-    if (tid >= 320 && tid < 320 + ATT_WARPS * NSTAGE * 2) {      // the 16 zero bytes in front of every escape window
-      const int t = tid - 320, st = t >> 1;
-      *reinterpret_cast<uint4*>(smem + TABLE_BYTES + st * STAGE_BYTES + ((t & 1) ? ST_VZ : ST_KZ)) = make_uint4(0, 0, 0, 0);
-    }
-#endif
     if (tid == 0) s_next = tlo + ATT_WARPS;           // tiles tlo .. tlo+W-1 go to warps 0..W-1, the rest is handed out on demand
     if (tid < nstaged) { mk_s[tid] = m_first.mk; mv_s[tid] = m_first.mv; }
     for (int i = tid + ATT_THREADS; i < nstaged; i += ATT_THREADS) { const TileMeta m = global_meta(tlo + i); mk_s[i] = m.mk; mv_s[i] = m.mv; }
   }
-#if GAAC_BULK
   if (!PAGED && tile < thi && lane == 0) {
     const u32 mb = ring_s + ST_MBAR;
     int wk, nk, wv, nv;
@@ -683,10 +533,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     if (nv > 0) bulk_g2s(ring_s + ST_VESC, p.V.ovf + ((long)L.ohv + cur.mv - wv), (u32)nv, mb);
     mbar_arrive(mb);
   }
-#else
-  if (tile < thi) issue_escapes(ring_s, cur);
-  cp_commit();
-#endif
   WarpAcc A;
 #pragma unroll
   for (int n = 0; n < 8; n++) A.acc[n][0] = A.acc[n][1] = A.acc[n][2] = A.acc[n][3] = 0.f;
@@ -698,22 +544,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
   // other.  The counter is read at the top of the iteration and its value used after the K half, which hides the latency
   // of the shared-memory atomic; the copies of the next tile are issued between the K half and the V half.
   int stg = 0;
-#if GAAC_BULK
   u32 phase = 0;                                       // bit s: parity of the phase of stage s that is waited for next
-#endif
   while (tile < thi) {
     int t1 = 0;
     if (lane == 0) t1 = atomicAdd(&s_next, 1);
-#if GAAC_BULK
     if (!__all_sync(FULLM, mbar_wait(ring_s + stg * STAGE_BYTES + ST_MBAR, (phase >> stg) & 1u))) {     // the whole warp gives up together
       if (lane == 0) atomicExch(p.err, 1);
       break;
     }
     phase ^= 1u << stg;
-#else
-    cp_wait<0>();
-    __syncwarp();
-#endif
     const uint8_t* stage = ring + stg * STAGE_BYTES;
     const int nvalid = min(T, S - tile * T);
     const bool rawk = PAGED && cur.mk < 0, rawv = PAGED && cur.mv < 0;
@@ -721,21 +560,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     scan_rows(stage, rawk, rawv, lane, flrow, rowoff, total);
     float sc[4] = {0.f, 0.f, 0.f, 0.f};
     if (!rawk) {
-#if GAAC_BULK
       int off, avail;
       staged_escapes(false, cur.mk, off, avail);
       if (__shfl_sync(FULLM, total, 15) + 8 <= avail)                                         // +8: a raw payload is read as two aligned words
         k_scores<true>(sc, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off}, flrow, rowoff, lane, qa);
       else
         k_scores<false>(sc, stage, smem, EscSrc<false>{nullptr, global_escapes(false, cur.mk), 0}, flrow, rowoff, lane, qa);
-#else
-      const EscRef e = esc_k(cur.mk);
-      const int wsh = (int)(reinterpret_cast<uintptr_t>(e.p) & 3);
-      if (__shfl_sync(FULLM, total, 15) + 8 <= esc_window_bytes(e.p, e.lim))                  // +8: a raw payload is read as two aligned words
-        k_scores<true>(sc, stage, smem, EscSrc<true>{stage + ST_KESC + wsh - ZPAD, nullptr, ZPAD}, flrow, rowoff, lane, qa);
-      else
-        k_scores<false>(sc, stage, smem, EscSrc<false>{nullptr, e.p, 0}, flrow, rowoff, lane, qa);
-#endif
     } else {
       raw_scores(sc, p.raw + (long)(~cur.mk) * (T * D), nvalid, lane, qa);
     }
@@ -744,41 +574,22 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     if (t1 < thi) {
       nxt = meta_of(t1);
       const u32 st = ring_s + (stg ^ 1) * STAGE_BYTES;
-#if GAAC_BULK
       if (lane == 0) bulk_issue(st, t1, nxt);
-#else
-      issue_payload(st, t1, nxt); issue_escapes(st, nxt);
-#endif
     }
-#if !GAAC_BULK
-    cp_commit();
-#endif
     u32 pb0, pb1;
     softmax_step(A, sc, p.scale_log2, nvalid, lane, pb0, pb1);
     if (!rawv) {
-#if GAAC_BULK
       int off, avail;
       staged_escapes(true, cur.mv, off, avail);
       if (__shfl_sync(FULLM, total, 31) + 8 <= avail)
         v_accum<true>(A, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off}, flrow, rowoff, lane, pb0, pb1);
       else
         v_accum<false>(A, stage, smem, EscSrc<false>{nullptr, global_escapes(true, cur.mv), 0}, flrow, rowoff, lane, pb0, pb1);
-#else
-      const EscRef e = esc_v(cur.mv);
-      const int wsh = (int)(reinterpret_cast<uintptr_t>(e.p) & 3);
-      if (__shfl_sync(FULLM, total, 31) + 8 <= esc_window_bytes(e.p, e.lim))
-        v_accum<true>(A, stage, smem, EscSrc<true>{stage + ST_VESC + wsh - ZPAD, nullptr, ZPAD}, flrow, rowoff, lane, pb0, pb1);
-      else
-        v_accum<false>(A, stage, smem, EscSrc<false>{nullptr, e.p, 0}, flrow, rowoff, lane, pb0, pb1);
-#endif
     } else {
       raw_accum(A, p.raw + (long)(~cur.mv) * (T * D), nvalid, lane, pb0, pb1);
     }
     cur = nxt; stg ^= 1; tile = t1;
   }
-#if !GAAC_BULK
-  cp_wait<0>();
-#endif
   // ---- slot layout: the raw BF16 tail belongs to the last split's warp 0
   if (!PAGED && TL > 0 && split == p.nsplit - 1 && warp == 0) {
     const uint16_t* kraw = reinterpret_cast<const uint16_t*>(p.K.tail) + (long)ch * p.tail_cap * D;
