@@ -142,15 +142,25 @@ __device__ __forceinline__ void store_tile_payload(const LaneTile& lt, uint8_t* 
 template <int KIND_V>
 __device__ __forceinline__ void store_tile_escapes(const WarpScratch& ws, const LaneTile& lt, uint8_t* esc_dst, int lane) {
   if (lt.tags == 0) return;
+  // A lane's groups come in runs of consecutive groups of one row (K: 2 rows x 4 groups, V: 4 rows x 2 groups): the position of a
+  // run's first escape byte is computed once, the groups of the run then follow one another in the row's escape bytes.
+  constexpr int RUN = KIND_V ? 2 : 4;
 #pragma unroll
-  for (int idx = 0; idx < 8; idx++) {
-    u32 tag = (lt.tags >> (2 * idx)) & 3u;
-    if (tag) {
-      int row = lane_row(KIND_V, lane, idx), g = lane_group(KIND_V, lane, idx);
-      uint8_t* d = esc_dst + ws.rowoff[row] + esc_prefix(ws.fl[row], 2 * g);
-      u64 e = lt.esc[idx];
-      d[0] = (uint8_t)e;
-      if (tag & 2u) { d[1] = (uint8_t)(e >> 8); d[2] = (uint8_t)(e >> 16); d[3] = (uint8_t)(e >> 24); d[4] = (uint8_t)(e >> 32); }
+  for (int base = 0; base < 8; base += RUN) {
+    const u32 tr = (lt.tags >> (2 * base)) & ((1u << (2 * RUN)) - 1u);
+    if (tr) {
+      const int row = lane_row(KIND_V, lane, base), g0 = lane_group(KIND_V, lane, base);
+      uint8_t* d = esc_dst + ws.rowoff[row] + esc_prefix(ws.fl[row], 2 * g0);
+#pragma unroll
+      for (int i = 0; i < RUN; i++) {
+        const u32 tag = (tr >> (2 * i)) & 3u;
+        if (tag) {
+          const u64 e = lt.esc[base + i];
+          d[0] = (uint8_t)e;
+          if (tag & 2u) { d[1] = (uint8_t)(e >> 8); d[2] = (uint8_t)(e >> 16); d[3] = (uint8_t)(e >> 24); d[4] = (uint8_t)(e >> 32); }
+          d += tag_esc_bytes(tag);
+        }
+      }
     }
   }
 }
