@@ -19,9 +19,10 @@
 //    layout, was 15 % slower), so shared memory holds the storage order and the 16-byte fragment reads accept a 2-way (K) /
 //    4-way (V) bank conflict (worth 0.7 us of 74).
 //  * the kernel is bound by instruction issue (ALU pipe) and by the shared-memory pipe, not by HBM: spreading the 3-bit
-//    codes through the 4096-entry table costs one load with ~3.5-way bank conflicts, by arithmetic two multiply-adds and
-//    three logic instructions; one half of each group through the table and the other by arithmetic is the fastest
-//    mix (GAAC_LUTC = 2; 1 = table only, 0 = arithmetic only).
+//    codes through a 4096-entry table costs one load with ~3.5-way bank conflicts, by arithmetic two multiply-adds and
+//    three logic instructions.  Which is faster moved with the rest of the kernel (table while the copies loaded the
+//    load/store unit less than the integer pipe, half and half after the bulk copies brought the storage-order conflicts);
+//    in the final kernel arithmetic only is fastest by 1 %, table only slowest by 4 % (GAAC_LUTC = 0 / 2 / 1).
 //
 // Fragment conventions follow the reference kernel (gaac/kernel.py:62-66,160-194), whose storage order they mirror.
 #include <cuda_bf16.h>
@@ -32,7 +33,7 @@
 namespace gaac {
 
 #ifndef GAAC_LUTC
-#define GAAC_LUTC 2
+#define GAAC_LUTC 0
 #endif
 constexpr int ATT_WARPS = 16;
 constexpr int ATT_THREADS = ATT_WARPS * 32;
