@@ -24,7 +24,7 @@ SCALE = HEAD_DIM ** -0.5
 WORKLOAD = "decode attention, batch 1, 32 q heads / 8 kv heads (GQA 4), head_dim 128, 65536-token context, slot layout, 0-token tail"
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_attn_kernel launch at this workload, from the ncu capture
 # summarised in profiles/; None until a capture exists.
-NCU_TRAFFIC_BYTES = 196.6e6
+NCU_TRAFFIC_BYTES = 196.7e6
 LAYERS_PER_GRAPH = 16              # layers captured in one CUDA graph of the timed region (a 32-layer model replays two of them per step)
 
 
