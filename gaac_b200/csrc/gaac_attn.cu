@@ -134,9 +134,10 @@ struct WarpAcc {
 // Sums and accumulators are fp32 and P keeps its relative BF16 rounding, so the result is as exact as with the true
 // maximum, and the common tile needs no cross-lane reduction, no rescale factor and no accumulator multiply.
 constexpr float RESCALE_TAU = 16.f;
+template <bool FULL_TILE>
 __device__ __forceinline__ void softmax_step(WarpAcc& A, const float* sc, float scale_log2, int nvalid, int lane, u32& pb0, u32& pb1) {
   const int j = lane & 3, r = lane >> 2;
-  const bool v0 = r < nvalid, v8 = r + 8 < nvalid;
+  const bool v0 = FULL_TILE || r < nvalid, v8 = FULL_TILE || r + 8 < nvalid;     // a full tile needs no token masks
   const float s00 = v0 ? sc[0] * scale_log2 : -CUDART_INF_F, s01 = v0 ? sc[1] * scale_log2 : -CUDART_INF_F;
   const float s80 = v8 ? sc[2] * scale_log2 : -CUDART_INF_F, s81 = v8 ? sc[3] * scale_log2 : -CUDART_INF_F;
   float mt0 = fmaxf(s00, s80), mt1 = fmaxf(s01, s81);
@@ -578,7 +579,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       if (lane == 0) bulk_issue(st, t1, nxt);
     }
     u32 pb0, pb1;
-    softmax_step(A, sc, p.scale_log2, nvalid, lane, pb0, pb1);
+    if (nvalid == T) softmax_step<true>(A, sc, p.scale_log2, nvalid, lane, pb0, pb1);
+    else softmax_step<false>(A, sc, p.scale_log2, nvalid, lane, pb0, pb1);
     if (!rawv) {
       int off, avail;
       staged_escapes(true, cur.mv, off, avail);
@@ -600,7 +602,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       float sc[4] = {0.f, 0.f, 0.f, 0.f};
       raw_scores(sc, kraw, nvalid, lane, qa);
       u32 pb0, pb1;
-      softmax_step(A, sc, p.scale_log2, nvalid, lane, pb0, pb1);
+      softmax_step<false>(A, sc, p.scale_log2, nvalid, lane, pb0, pb1);
       raw_accum(A, vraw, nvalid, lane, pb0, pb1);
       kraw += T * D; vraw += T * D;
     }
