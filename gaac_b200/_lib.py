@@ -33,7 +33,8 @@ class Paged(C.Structure):
 
 class Exchange(C.Structure):
     """gaac_exchange"""
-    _fields_ = [("recv", vp), ("flags", vp), ("epoch", vp), ("ticket", vp), ("err", vp), ("rank", i32), ("world", i32)]
+    _fields_ = [("recv", vp), ("flags", vp), ("epoch", vp), ("ticket", vp), ("err", vp), ("rank", i32), ("world", i32),
+                ("rows_cap", i32), ("groups_cap", i32)]
 
 
 _SIGNATURES = {
@@ -48,24 +49,28 @@ _SIGNATURES = {
     "gaac_exponent_hist": (i32, [vp, i64, i64, vp, vp]),
     "gaac_bases_from_hist": (i32, [vp, i64, vp, vp, vp]),
     "gaac_attn_workspace_bytes": (sz, [i32, i32, i32]),
+    "gaac_attn_workspace_header_bytes": (sz, [i32, i32]),
+    "gaac_decode_attn_pages": (i32, [C.POINTER(Side), C.POINTER(Side), vp, i32, i32, i32, i64, i64, f32, i32, i32, vp, sz, vp, vp, vp, C.POINTER(Exchange), i32, vp]),
+    "gaac_decode_attn_exchange": (i32, [C.POINTER(Side), C.POINTER(Side), vp, vp, i32, i32, i32, vp, i64, f32, i32, vp, i32, i32, vp, sz, C.POINTER(Exchange), vp, vp, vp]),
+    "gaac_debug_decode_attn_rebuild": (i32, [C.POINTER(Side), C.POINTER(Side), vp, vp, i32, i32, i32, vp, i64, i64, f32, i32, vp, i32, i32, vp, sz, vp, vp, vp, vp, i64, vp]),
+    "gaac_debug_paged_decode_attn_rebuild": (i32, [C.POINTER(Paged), vp, i64, vp, vp, i32, i32, f32, i32, vp, sz, vp, vp, vp, vp, i64, vp]),
     "gaac_decode_attn": (i32, [C.POINTER(Side), C.POINTER(Side), vp, vp, i32, i32, i32, vp, i64, f32, i32, vp, i32, i32, vp, sz, vp, vp, vp]),
     "gaac_decode_attn_partial": (i32, [C.POINTER(Side), C.POINTER(Side), vp, vp, i32, i32, i32, vp, i64, f32, i32, vp, i32, i32, vp, sz, vp, vp]),
     "gaac_combine": (i32, [vp, vp, vp, i64, i32, vp, vp, vp]),
     "gaac_combine_parts": (i32, [vp, i64, i32, vp, vp, vp]),
     "gaac_decode_attn_push": (i32, [C.POINTER(Side), C.POINTER(Side), vp, vp, i32, i32, i32, vp, i64, f32, i32, vp, i32, i32, vp, sz, C.POINTER(Exchange), vp]),
     "gaac_exchange_merge": (i32, [C.POINTER(Exchange), i64, i32, vp, vp, vp]),
-    "gaac_append_kv": (i32, [C.POINTER(Store), C.POINTER(Store), vp, vp, vp, i32, i32, vp, vp, i64, i64, i32, vp]),
+    "gaac_append_kv": (i32, [C.POINTER(Store), C.POINTER(Store), vp, vp, vp, i32, i32, vp, vp, i64, i64, i32, vp, vp]),
     "gaac_paged_store": (i32, [C.POINTER(Paged), vp, vp, i64, i64, vp, i32, vp, vp]),
     "gaac_paged_release": (i32, [C.POINTER(Paged), vp, i32, vp]),
     "gaac_paged_decode_blocks": (i32, [C.POINTER(Paged), vp, i32, vp, vp, i64, vp]),
     "gaac_paged_decode_attn": (i32, [C.POINTER(Paged), vp, i64, vp, vp, i32, i32, f32, i32, vp, sz, vp, vp, vp]),
-}
-# entry points added after ABI version 1 are bound when present
-_OPTIONAL = {
     "gaac_decode_attn_static": (i32, [C.POINTER(Side), C.POINTER(Side), vp, vp, i32, i32, i32, vp, i64, f32, i32, vp, i32, i32, vp, vp, vp]),
     "gaac_static_workspace_bytes": (sz, []),
+    "gaac_static_workspace_error": (i32, [vp, i32, vp]),
 }
 EXPORTS = tuple(_SIGNATURES)
+ABI_VERSION = 2
 
 
 def lib():
@@ -78,10 +83,8 @@ def lib():
         for name, (res, args) in _SIGNATURES.items():
             fn = getattr(L, name)
             fn.restype, fn.argtypes = res, args
-        for name, (res, args) in _OPTIONAL.items():
-            if hasattr(L, name):
-                fn = getattr(L, name)
-                fn.restype, fn.argtypes = res, args
+        if L.gaac_abi_version() != ABI_VERSION:
+            raise RuntimeError(f"{LIB_PATH} has ABI version {L.gaac_abi_version()}, this package binds version {ABI_VERSION}: rebuild it (python -m gaac_b200.build --force)")
         _lib = L
     return _lib
 

@@ -79,49 +79,67 @@ def bases_from_hist(hist: torch.Tensor, n_kv: int) -> tuple[torch.Tensor, torch.
 
 @dataclass
 class Page:
-    """Compressed K or V of H heads x S tokens, all heads the same length (gaac/codec.py:87-102)."""
-    sm: torch.Tensor              # uint8 [H, S_pad*D]   sign+mantissa bytes, storage order
-    codes: torch.Tensor           # uint8 [H, S_pad*CB]  3-bit codes, storage order
-    flags: torch.Tensor           # int32 [H, S_pad]     per-row tag words (0 for padded rows)
-    ovf_off: torch.Tensor         # int32 [H, S]         row offset within the head's escape stream
-    ovf: torch.Tensor             # uint8 [total + 8]    escape bytes of all heads
-    ovf_head_start: torch.Tensor  # int32 [H+1]
-    tile_off: torch.Tensor        # int32 [H, S_pad/16]  tile offset within the head's escape stream
-    base3: torch.Tensor           # uint8 [n_kv, D]
-    base4: torch.Tensor           # uint8 [n_kv, D]
+    """One kind (K or V) of H heads, every head S tokens long, in compressed form.  Field set and layouts as in
+    gaac/codec.py:87-102.  Token rows are padded to whole tiles (S_pad = 16 * ceil(S / 16)); inside a tile the bytes are in the
+    order the attention kernel's fragments want them (storage_index).
+
+      sm, codes        uint8 [H, S_pad*128], [H, S_pad*48]   sign+mantissa byte and 3-bit code of every element
+      flags            int32 [H, S_pad]                      one tag word per token row, 2 bits per group; padding rows are 0
+      ovf              uint8 [n + 8]                         the escape bytes of all heads back to back, 8 spare bytes behind
+      ovf_head_start   int32 [H + 1]                         where each head's escape bytes begin in ovf
+      tile_off         int32 [H, S_pad/16]                   where each tile's escape bytes begin inside its head's share
+      ovf_off          int32 [H, S]                          the same per token row (only the reference's torch decoder reads it)
+      base3, base4     uint8 [n_kv, 128]                     the exponent window starts the codes are relative to
+    """
+    sm: torch.Tensor
+    codes: torch.Tensor
+    flags: torch.Tensor
+    ovf_off: torch.Tensor
+    ovf: torch.Tensor
+    ovf_head_start: torch.Tensor
+    tile_off: torch.Tensor
+    base3: torch.Tensor
+    base4: torch.Tensor
     H: int
     S: int
     n_kv: int
-    kind: str                     # 'k' | 'v'
+    kind: str                     # 'k' or 'v'
 
     @property
     def nbytes(self) -> int:
-        """Stored bytes: sign/mantissa + codes + escapes + tags + tile offsets (gaac/codec.py:104-108)."""
-        esc = int(self.ovf_head_start[-1] - self.ovf_head_start[0])
-        return self.H * self.S * (D + CB + 4) + esc + self.H * ((self.S + T - 1) // T) * 4
+        """Bytes that have to be read to use the Page: per token 128 + 48 + 4, the escape bytes, 4 per tile for its offset
+        (gaac/codec.py:104-108; the two small base tables are left out there as well)."""
+        escapes = int(self.ovf_head_start[-1] - self.ovf_head_start[0])
+        tiles = (self.S + T - 1) // T
+        return self.H * (self.S * (D + CB + 4) + tiles * 4) + escapes
 
     @property
     def ratio(self) -> float:
+        """BF16 bytes of the same tokens divided by nbytes."""
         return self.H * self.S * D * 2 / self.nbytes
 
 
 class Codec:
-    """Per-(kv head, channel) exponent bases + encoder / decoder (gaac/codec.py:115-218).  `encode` and `decode` produce the
-    same bytes as the reference's torch implementation; both run the CUDA kernels."""
+    """Holds the exponent bases of n_kv kv heads and turns [H, S, 128] bf16 into a Page and back (gaac/codec.py:115-218).
+    Encoding and decoding produce the reference's bytes, computed by the CUDA kernels."""
+
     def __init__(self, n_kv: int, device: str = "cuda"):
         self.n_kv, self.device = n_kv, device
         self.base3 = self.base4 = None
 
+    def _as_table(self, t: torch.Tensor) -> torch.Tensor:
+        return t.to(self.device, torch.uint8).reshape(self.n_kv, D).contiguous()
+
     def calibrate(self, sample: torch.Tensor) -> "Codec":
-        """sample: [H, T, D] bf16 with head h using bases of h % n_kv."""
-        H = sample.shape[0]
-        x = sample.to(self.device).reshape(H // self.n_kv, self.n_kv, -1, D).permute(0, 2, 1, 3)   # [., T, n_kv, D]
-        self.base3, self.base4 = bases_from_hist(exponent_hist(x, self.n_kv), self.n_kv)
+        """Pick the bases from sample [H, n_tokens, 128] bf16; H may be a multiple of n_kv, head h then counts for kv head h % n_kv."""
+        groups = sample.shape[0] // self.n_kv
+        token_major = sample.to(self.device).reshape(groups, self.n_kv, -1, D).permute(0, 2, 1, 3)     # [groups, n_tokens, n_kv, 128]
+        self.base3, self.base4 = bases_from_hist(exponent_hist(token_major, self.n_kv), self.n_kv)
         return self
 
     def set_bases(self, base3: torch.Tensor, base4: torch.Tensor) -> "Codec":
-        self.base3 = base3.to(self.device, torch.uint8).reshape(self.n_kv, D).contiguous()
-        self.base4 = base4.to(self.device, torch.uint8).reshape(self.n_kv, D).contiguous()
+        """Use given tables (any shape with n_kv*128 entries).  Values must leave room for the window: base3 <= 248, base4 <= 240."""
+        self.base3, self.base4 = self._as_table(base3), self._as_table(base4)
         return self
 
     def encode(self, x: torch.Tensor, kind: str) -> Page:

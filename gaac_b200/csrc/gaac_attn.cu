@@ -27,6 +27,7 @@
 // Fragment conventions follow the reference kernel (gaac/kernel.py:62-66,160-194), whose storage order they mirror.
 #include <cuda_bf16.h>
 #include <math_constants.h>
+#include <algorithm>
 #include "gaac_api.cuh"
 #include "gaac_tile.h"
 
@@ -71,6 +72,7 @@ struct AttnParams {
   // slot layout
   gaac_side K, V;
   const int* slot; const int* seq_len; const int* tail_len; int tail_cap; long S_pad; int n_base_rows;
+  int S_uniform;                 // tokens of every cache head when seq_len == NULL (slot == NULL: batch row b reads slot b)
   // paged layout
   const uint8_t* buf; const uint16_t* raw; const int* mt; const int* bt; long bt_stride; int TS; int ovf_slot;
   const uint8_t *b3k, *b4k, *b3v, *b4v;
@@ -79,8 +81,11 @@ struct AttnParams {
   int* counters; int* err; float* pm; float* pl; float* pa;     // err: set to 1 when a bounded wait inside the kernel ran out
   uint16_t* out; float* out_f32; float* part;
   // cross-GPU exchange (x_recv == NULL: unused): the partial of every query head is stored into every rank's receive
-  // buffer, then the rank's arrival counter on every rank is raised once per (row, kv head)
-  float* const* x_recv; int* const* x_flags; const int* x_epoch; int x_rank, x_world;
+  // buffer, then this rank's arrival flag of the (row, kv head) group on every rank is set to the exchange number; with
+  // x_fused the same CTA then waits (bounded) for the other ranks' flags, merges all ranks' rows and writes the output
+  float* const* x_recv; int* const* x_flags; int* x_epoch; int* x_ticket; int* x_err; int x_rank, x_world, x_rows_cap, x_fused;
+  // debug instantiation only: the rebuilt BF16 K / V rows are written to [B*n_kv, dump_S, 128] (row = token of the head)
+  uint16_t* dump_k; uint16_t* dump_v; long dump_S;
 };
 
 __device__ __forceinline__ void mma16816(float* c, const u32* a, u32 b0, u32 b1) {
@@ -252,9 +257,11 @@ __device__ __forceinline__ void decode_group_dev(u32 sm_lo, u32 sm_hi, u32 c24, 
 
 // Scores of one compressed K tile: sc += K . Q^T.  flrow / rowoff: tag word and escape offset of row (lane & 15) held by
 // lanes 0-15.
-template <bool WIN>
+// dump (debug instantiation only): where token 0 of this tile goes in the [token][128] dump of the head; every lane writes the
+// fragment words it rebuilt at the (token, channel) pairs they stand for, rows >= nvalid are left alone.
+template <bool WIN, bool DUMP>
 __device__ __forceinline__ void k_scores(float* sc, const uint8_t* stage, const uint8_t* tables, const EscSrc<WIN>& es, u32 flrow, int rowoff,
-                                         int lane, const u32 (&qa)[8][2]) {
+                                         int lane, const u32 (&qa)[8][2], uint16_t* dump = nullptr, int nvalid = T) {
   const int j = lane & 3, r = lane >> 2;
   const u32x2* lutx = reinterpret_cast<const u32x2*>(tables + TB_LUTX);
   u32 t8[2]; int pos[2]; uint4 s0[2], s1[2]; u32 cd[2][3];
@@ -279,6 +286,15 @@ __device__ __forceinline__ void k_scores(float* sc, const uint8_t* stage, const 
       const u32 smhi = g == 0 ? s0[o].y : g == 1 ? s0[o].w : g == 2 ? s1[o].y : s1[o].w;
       decode_group_dev<WIN>(smlo, smhi, k_group_codes(cd[o], g), t8[o] >> (2 * g), pos[o], es, lutx, tables + TB_LUTC, bw, f[o]);
     }
+    if (DUMP) {
+#pragma unroll
+      for (int o = 0; o < 2; o++)
+        if (8 * o + r < nvalid) {
+          u32* row = reinterpret_cast<u32*>(dump + (8 * o + r) * D);
+          row[(32 * g + 2 * j) >> 1] = f[o][0]; row[(32 * g + 2 * j + 8) >> 1] = f[o][1];
+          row[(32 * g + 16 + 2 * j) >> 1] = f[o][2]; row[(32 * g + 16 + 2 * j + 8) >> 1] = f[o][3];
+        }
+    }
     { const u32 a[4] = {f[0][0], f[1][0], f[0][1], f[1][1]}; mma16816(sc, a, qa[2 * g][0], qa[2 * g][1]); }
     { const u32 a[4] = {f[0][2], f[1][2], f[0][3], f[1][3]}; mma16816(s2, a, qa[2 * g + 1][0], qa[2 * g + 1][1]); }
   }
@@ -286,9 +302,9 @@ __device__ __forceinline__ void k_scores(float* sc, const uint8_t* stage, const 
 }
 
 // O^T += V^T . P^T for one compressed V tile.  flrow / rowoff of V row (lane & 15) are held by lanes 16-31.
-template <bool WIN>
+template <bool WIN, bool DUMP>
 __device__ __forceinline__ void v_accum(WarpAcc& A, const uint8_t* stage, const uint8_t* tables, const EscSrc<WIN>& es, u32 flrow, int rowoff,
-                                        int lane, u32 pb0, u32 pb1) {
+                                        int lane, u32 pb0, u32 pb1, uint16_t* dump = nullptr, int nvalid = T) {
   const int j = lane & 3, r = lane >> 2;
   const u32x2* lutx = reinterpret_cast<const u32x2*>(tables + TB_LUTX);
   u32 t4[4]; int pos[4]; uint4 sm[4]; u32 cd[6];
@@ -314,6 +330,19 @@ __device__ __forceinline__ void v_accum(WarpAcc& A, const uint8_t* stage, const 
       const u32 smlo = g == 0 ? sm[t].x : sm[t].z, smhi = g == 0 ? sm[t].y : sm[t].w;
       decode_group_dev<WIN>(smlo, smhi, v_group_codes(cd, t, g), t4[t] >> (2 * g), pos[t], es, lutx, tables + TB_LUTC, bw, f[t]);
     }
+    if (DUMP) {
+#pragma unroll
+      for (int t = 0; t < 4; t++) {
+        const int tok = 2 * j + (t & 1) + 8 * (t >> 1);
+        if (tok < nvalid) {
+#pragma unroll
+          for (int i = 0; i < 4; i++) {                // word i = stored positions 16r + 8g + 2i, +1  <->  channels 8(8g + 2i) + r, 8(8g + 2i + 1) + r
+            dump[tok * D + 8 * (8 * g + 2 * i) + r] = (uint16_t)(f[t][i] & 0xFFFFu);
+            dump[tok * D + 8 * (8 * g + 2 * i + 1) + r] = (uint16_t)(f[t][i] >> 16);
+          }
+        }
+      }
+    }
 #pragma unroll
     for (int h = 0; h < 2; h++) {
       const u32 u01[4] = {f[0][2 * h], f[1][2 * h], f[2][2 * h], f[3][2 * h]};
@@ -338,7 +367,8 @@ __device__ __forceinline__ void scan_rows(const uint8_t* stage, bool rawk, bool 
 }
 
 // Scores of a raw BF16 tile [16][128] in global memory (rows >= nvalid are not read).
-__device__ __forceinline__ void raw_scores(float* sc, const uint16_t* kraw, int nvalid, int lane, const u32 (&qa)[8][2]) {
+template <bool DUMP>
+__device__ __forceinline__ void raw_scores(float* sc, const uint16_t* kraw, int nvalid, int lane, const u32 (&qa)[8][2], uint16_t* dump = nullptr) {
   const int j = lane & 3, r = lane >> 2;
 #pragma unroll
   for (int s = 0; s < 8; s++) {
@@ -347,11 +377,16 @@ __device__ __forceinline__ void raw_scores(float* sc, const uint16_t* kraw, int 
     const uint16_t* k8 = k0 + 8 * D;
     a[0] = r < nvalid ? *reinterpret_cast<const u32*>(k0) : 0u; a[2] = r < nvalid ? *reinterpret_cast<const u32*>(k0 + 8) : 0u;
     a[1] = r + 8 < nvalid ? *reinterpret_cast<const u32*>(k8) : 0u; a[3] = r + 8 < nvalid ? *reinterpret_cast<const u32*>(k8 + 8) : 0u;
+    if (DUMP) {
+      if (r < nvalid) { u32* row = reinterpret_cast<u32*>(dump + r * D); row[(16 * s + 2 * j) >> 1] = a[0]; row[(16 * s + 2 * j + 8) >> 1] = a[2]; }
+      if (r + 8 < nvalid) { u32* row = reinterpret_cast<u32*>(dump + (r + 8) * D); row[(16 * s + 2 * j) >> 1] = a[1]; row[(16 * s + 2 * j + 8) >> 1] = a[3]; }
+    }
     mma16816(sc, a, qa[s][0], qa[s][1]);
   }
 }
 // O^T += V^T . P^T for a raw BF16 tile.
-__device__ __forceinline__ void raw_accum(WarpAcc& A, const uint16_t* vraw, int nvalid, int lane, u32 pb0, u32 pb1) {
+template <bool DUMP>
+__device__ __forceinline__ void raw_accum(WarpAcc& A, const uint16_t* vraw, int nvalid, int lane, u32 pb0, u32 pb1, uint16_t* dump = nullptr) {
   const int j = lane & 3, r = lane >> 2;
 #pragma unroll
   for (int w = 0; w < 4; w++) {
@@ -363,12 +398,43 @@ __device__ __forceinline__ void raw_accum(WarpAcc& A, const uint16_t* vraw, int 
       const bool ok = tok < nvalid;
       const u32 e0 = ok ? vr[0] : 0u, e1 = ok ? vr[8] : 0u, e2 = ok ? vr[16] : 0u, e3 = ok ? vr[24] : 0u;
       u01[t] = e0 | (e1 << 16); u23[t] = e2 | (e3 << 16);
+      if (DUMP && ok) {
+        uint16_t* o = dump + tok * D + 8 * (4 * w) + r;
+        o[0] = (uint16_t)e0; o[8] = (uint16_t)e1; o[16] = (uint16_t)e2; o[24] = (uint16_t)e3;
+      }
     }
     pv_words(A, w, u01, u23, pb0, pb1);
   }
 }
 
-template <bool PAGED>
+// ---- cross-GPU exchange helpers.  Every wait is bounded: after X_WAIT_LIMIT polls (about a second) the waiter gives up, so a
+// missing peer never hangs the GPU.  Flags are compared as wrapping differences, so the exchange number may wrap around.
+constexpr int X_WAIT_LIMIT = 1000000;
+__device__ __forceinline__ bool x_wait_flag(const int* f, int want) {
+  for (int it = 0; it < X_WAIT_LIMIT; it++) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+    if ((int)((unsigned)v - (unsigned)want) >= 0) return true;
+    if (it > 64) __nanosleep(100);
+  }
+  return false;
+}
+// Merge the rows of all ranks for query head qh, element d: base = this exchange's half of the receive buffer,
+// [world][rows_cap][130] floats of (m in natural-log units, l, acc[128]); same algebra as the split merge.
+__device__ __forceinline__ float x_merge_rows(const float* base, int world, long rows_cap, long qh, int d) {
+  float M = -CUDART_INF_F;
+  for (int s = 0; s < world; s++) M = fmaxf(M, __ldcg(base + (s * rows_cap + qh) * 130));
+  float L = 0.f, Ac = 0.f;
+  for (int s = 0; s < world; s++) {
+    const float* pp = base + (s * rows_cap + qh) * 130;
+    const float ms = __ldcg(pp);
+    const float f = (ms == -CUDART_INF_F) ? 0.f : __expf(ms - M);
+    L += __ldcg(pp + 1) * f; Ac += __ldcg(pp + 2 + d) * f;
+  }
+  return L > 0.f ? Ac / L : 0.f;
+}
+
+template <bool PAGED, bool DUMP>
 __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ int s_next, s_last;
@@ -384,13 +450,18 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
   asm volatile("griddepcontrol.launch_dependents;" ::);
 
   // ---- which cache head, how many tokens, this CTA's tile range [tlo, thi)
-  int S, ch = 0, TL = 0;
+  // (without a slot map row b reads slot b; without a length table every head holds S_uniform tokens: the two dependent
+  // loads at the head of the prologue disappear for callers whose heads are all alike, which is what two Pages are)
+  int S, ch = 0, TL = 0, ohk = 0, ohv = 0;
   if (PAGED) { S = p.seq_len[b]; }
   else {
-    const int sl = p.slot[b];
+    const int sl = p.slot ? p.slot[b] : b;
     ch = (sl < 0 ? 0 : sl) * p.n_kv + kvh;
-    S = sl < 0 ? 0 : p.seq_len[ch];
-    TL = (sl < 0 || !p.tail_len) ? 0 : p.tail_len[ch];
+    const int s_ld = p.seq_len ? p.seq_len[ch] : p.S_uniform;           // these four loads do not depend on one another
+    const int t_ld = p.tail_len ? p.tail_len[ch] : 0;
+    ohk = p.K.head_start[ch]; ohv = p.V.head_start[ch];
+    S = sl < 0 ? 0 : s_ld;
+    TL = sl < 0 ? 0 : t_ld;
   }
   // These values are the same in every thread, but they were loaded from memory: passing them through a shuffle tells the
   // compiler so, and the address arithmetic built on them (one lane issues the copies) stays in uniform registers.
@@ -398,8 +469,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
   const int ntiles = (S + 15) >> 4, chunk = (ntiles + p.nsplit - 1) / p.nsplit;
   const int tlo = min(split * chunk, ntiles), thi = min(tlo + chunk, ntiles);
   const long smh = (long)ch * p.S_pad * D, cdh = (long)ch * p.S_pad * CB, rowb = (long)ch * p.S_pad, tileb = (long)ch * (p.S_pad >> 4);
-  int ohk = 0, ohv = 0;
-  if (!PAGED && S > 0) { ohk = p.K.head_start[ch]; ohv = p.V.head_start[ch]; }
   ohk = __shfl_sync(FULLM, ohk, 0); ohv = __shfl_sync(FULLM, ohv, 0);
 
   // ---- addressing of this lane, and the copies of the warp's first tile: they are put in flight before the CTA builds its
@@ -541,6 +610,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
   A.m0 = A.m1 = -CUDART_INF_F; A.l0 = A.l1 = 0.f;
   __syncthreads();
 
+  uint16_t* const dump_k = DUMP ? p.dump_k + (long)bh * p.dump_S * D : nullptr;
+  uint16_t* const dump_v = DUMP ? p.dump_v + (long)bh * p.dump_S * D : nullptr;
   // ---- main loop.  The warp's first tile is tlo + warp; every further tile is taken from the CTA's counter while the
   // current one is being consumed, one tile ahead of its use, so fast and slow warps finish within about one tile of each
   // other.  The counter is read at the top of the iteration and its value used after the K half, which hides the latency
@@ -565,11 +636,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       int off, avail;
       staged_escapes(false, cur.mk, off, avail);
       if (__shfl_sync(FULLM, total, 15) + 8 <= avail)                                         // +8: a raw payload is read as two aligned words
-        k_scores<true>(sc, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off}, flrow, rowoff, lane, qa);
+        k_scores<true, DUMP>(sc, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off}, flrow, rowoff, lane, qa, dump_k + (long)tile * T * D, nvalid);
       else
-        k_scores<false>(sc, stage, smem, EscSrc<false>{nullptr, global_escapes(false, cur.mk), 0}, flrow, rowoff, lane, qa);
+        k_scores<false, DUMP>(sc, stage, smem, EscSrc<false>{nullptr, global_escapes(false, cur.mk), 0}, flrow, rowoff, lane, qa, dump_k + (long)tile * T * D, nvalid);
     } else {
-      raw_scores(sc, p.raw + (long)(~cur.mk) * (T * D), nvalid, lane, qa);
+      raw_scores<DUMP>(sc, p.raw + (long)(~cur.mk) * (T * D), nvalid, lane, qa, dump_k + (long)tile * T * D);
     }
     t1 = __shfl_sync(FULLM, t1, 0);
     TileMeta nxt{0, 0};
@@ -585,11 +656,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       int off, avail;
       staged_escapes(true, cur.mv, off, avail);
       if (__shfl_sync(FULLM, total, 31) + 8 <= avail)
-        v_accum<true>(A, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off}, flrow, rowoff, lane, pb0, pb1);
+        v_accum<true, DUMP>(A, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off}, flrow, rowoff, lane, pb0, pb1, dump_v + (long)tile * T * D, nvalid);
       else
-        v_accum<false>(A, stage, smem, EscSrc<false>{nullptr, global_escapes(true, cur.mv), 0}, flrow, rowoff, lane, pb0, pb1);
+        v_accum<false, DUMP>(A, stage, smem, EscSrc<false>{nullptr, global_escapes(true, cur.mv), 0}, flrow, rowoff, lane, pb0, pb1, dump_v + (long)tile * T * D, nvalid);
     } else {
-      raw_accum(A, p.raw + (long)(~cur.mv) * (T * D), nvalid, lane, pb0, pb1);
+      raw_accum<DUMP>(A, p.raw + (long)(~cur.mv) * (T * D), nvalid, lane, pb0, pb1, dump_v + (long)tile * T * D);
     }
     cur = nxt; stg ^= 1; tile = t1;
   }
@@ -600,10 +671,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     for (int t0 = 0; t0 < TL; t0 += T) {
       const int nvalid = min(T, TL - t0);
       float sc[4] = {0.f, 0.f, 0.f, 0.f};
-      raw_scores(sc, kraw, nvalid, lane, qa);
+      raw_scores<DUMP>(sc, kraw, nvalid, lane, qa, dump_k + ((long)S + t0) * D);
       u32 pb0, pb1;
       softmax_step<false>(A, sc, p.scale_log2, nvalid, lane, pb0, pb1);
-      raw_accum(A, vraw, nvalid, lane, pb0, pb1);
+      raw_accum<DUMP>(A, vraw, nvalid, lane, pb0, pb1, dump_v + ((long)S + t0) * D);
       kraw += T * D; vraw += T * D;
     }
   }
@@ -706,6 +777,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       if (g < G) *reinterpret_cast<float4*>(c_red + ((warp * 8 + g) * D) + 4 * lane) = acc4[g];
     __syncthreads();
     const int d = tid & 127;
+    const int x_ep = p.x_recv ? __ldcg(p.x_epoch) : 0;         // number of this exchange - 1; advanced only after every group has read it
     for (int g = tid >> 7; g < G; g += ATT_THREADS / 128) {
       float Ac = 0.f;
 #pragma unroll
@@ -713,8 +785,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       const float M = c_ML[2 * g], L = c_ML[2 * g + 1];
       const long qh = qh0 + g;
       if (p.x_recv) {                                // the same partial, pushed to every rank's receive buffer over NVLink
-        const int par = __ldcg(p.x_epoch) & 1;
-        const long row = ((long)(par * p.x_world + p.x_rank) * p.B * p.n_q + qh) * 130;
+        const long row = ((long)((x_ep & 1) * p.x_world + p.x_rank) * p.x_rows_cap + qh) * 130;
         for (int rk = 0; rk < p.x_world; rk++) {
           float* o = p.x_recv[rk] + row;
           if (d == 0) { o[0] = M * LN2; o[1] = L; }
@@ -730,53 +801,57 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
         if (p.out_f32) p.out_f32[qh * D + d] = v;
       }
     }
-    if (p.x_recv) {                                  // the stores above must be visible on the peers before the counter moves
-      __threadfence_system();
+    if (p.x_recv) {
+      // The rows of all ranks are written first; then ONE fence per flag writer makes them visible system-wide (the barrier
+      // orders the other threads' stores before it), and this rank's flag of the group is set to the exchange number on
+      // every rank.  Flags carry the number instead of counting arrivals, so the set of groups may differ between
+      // exchanges and a lost exchange does not shift the later ones.
       __syncthreads();
-      if (tid < p.x_world) atomicAdd_system(p.x_flags[tid] + p.x_rank, 1);
+      if (tid < p.x_world) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.x_flags[tid] + (long)bh * p.x_world + p.x_rank), "r"(x_ep + 1) : "memory");
+      }
+      if (!p.x_fused) return;                        // the wait-and-merge runs as its own launch (gaac_exchange_merge)
+      // ---- fused: wait (bounded) for the rows of this group from every rank, merge them, write the output
+      __shared__ int s_xok;
+      if (tid == 0) s_xok = 1;
+      __syncthreads();
+      if (tid < p.x_world && !x_wait_flag(p.x_flags[p.x_rank] + (long)bh * p.x_world + tid, x_ep + 1)) { s_xok = 0; atomicExch(p.x_err, 1); }
+      __syncthreads();
+      const bool ok = s_xok != 0;
+      const float* base = p.x_recv[p.x_rank] + (long)(x_ep & 1) * p.x_world * p.x_rows_cap * 130;
+      for (int g = tid >> 7; g < G; g += ATT_THREADS / 128) {
+        const long qh = qh0 + g;
+        const float v = ok ? x_merge_rows(base, p.x_world, p.x_rows_cap, qh, d) : 0.f;
+        if (p.out) p.out[qh * D + d] = __bfloat16_as_ushort(__float2bfloat16(v));
+        if (p.out_f32) p.out_f32[qh * D + d] = v;
+      }
+      // the exchange number advances when every group of this launch is through (each has read it by then)
+      __syncthreads();
+      if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(p.x_ticket, 1) == (int)gridDim.x - 1) { *p.x_ticket = 0; __threadfence(); atomicAdd(p.x_epoch, 1); }
+      }
     }
   }
 }
 
-// Second half of the cross-GPU exchange: wait until every rank's partials of this exchange have arrived in this GPU's
-// receive buffer, merge them, and advance the exchange counter.  One CTA per query head.  Every wait is bounded: after
-// X_WAIT_LIMIT polls (about a second) the kernel sets *err, writes zeros and returns, so a missing peer never hangs the GPU.
-constexpr int X_WAIT_LIMIT = 4000000;
+// Second half of the cross-GPU exchange as a launch of its own (the attention kernel was launched push-only): wait until
+// every rank's rows of this exchange have arrived in this GPU's receive buffer, merge them, and advance the exchange number.
+// One CTA per query head; heads_per_group consecutive query heads share the flags of one (row, kv head) group.  After
+// X_WAIT_LIMIT polls the kernel sets *err, writes zeros and returns.
 __global__ void __launch_bounds__(128) exchange_merge_kernel(float* const* x_recv, int* const* x_flags, int* epoch, int* ticket, int* err, int rank, int world,
-                                                              int groups, long n_heads, uint16_t* __restrict__ out, float* __restrict__ out_f32) {
+                                                              int heads_per_group, long rows_cap, uint16_t* __restrict__ out, float* __restrict__ out_f32) {
   __shared__ int ok_s;
   const long qh = blockIdx.x; const int d = threadIdx.x;
   asm volatile("griddepcontrol.wait;" ::: "memory");                   // resident early, runs after the attention kernel has completed
   asm volatile("griddepcontrol.launch_dependents;" ::);
-  const int ep = *reinterpret_cast<volatile int*>(epoch);               // advanced only after every CTA has taken its ticket
-  const int expected = (ep + 1) * groups;
+  const int ep = __ldcg(epoch);                                         // advanced only after every CTA has taken its ticket
   if (d == 0) ok_s = 1;
   __syncthreads();
-  if (d < world) {
-    const int* f = x_flags[rank] + d;
-    for (int it = 0;; it++) {
-      int v;
-      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-      if (v - expected >= 0) break;
-      if (it >= X_WAIT_LIMIT) { ok_s = 0; atomicExch(err, 1); break; }
-      __nanosleep(200);
-    }
-  }
+  if (d < world && !x_wait_flag(x_flags[rank] + (qh / heads_per_group) * world + d, ep + 1)) { ok_s = 0; atomicExch(err, 1); }
   __syncthreads();
-  float v = 0.f;
-  if (ok_s) {
-    const float* base = x_recv[rank] + (long)(ep & 1) * world * n_heads * 130;
-    float M = -CUDART_INF_F;
-    for (int s = 0; s < world; s++) M = fmaxf(M, __ldcg(base + (s * n_heads + qh) * 130));
-    float L = 0.f, Ac = 0.f;
-    for (int s = 0; s < world; s++) {
-      const float* pp = base + (s * n_heads + qh) * 130;
-      const float ms = __ldcg(pp);
-      const float f = (ms == -CUDART_INF_F) ? 0.f : __expf(ms - M);
-      L += __ldcg(pp + 1) * f; Ac += __ldcg(pp + 2 + d) * f;
-    }
-    v = L > 0.f ? Ac / L : 0.f;
-  }
+  const float v = ok_s ? x_merge_rows(x_recv[rank] + (long)(ep & 1) * world * rows_cap * 130, world, rows_cap, qh, d) : 0.f;
   if (out) out[qh * D + d] = __bfloat16_as_ushort(__float2bfloat16(v));
   if (out_f32) out_f32[qh * D + d] = v;
   __syncthreads();
@@ -823,38 +898,73 @@ __global__ void __launch_bounds__(128) combine_parts_kernel(const float* __restr
 }
 
 static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+// Workspace = header | pm | pl | pa.  Header: the error word at byte 0, the split counters from byte 256.  The header has a
+// fixed size for every B*n_q up to 16320, so the partials of a call never lie where the counters of a call of another shape
+// do: a workspace zeroed once can be reused across batch sizes and split counts.
+constexpr size_t WS_COUNTERS_OFF = 256, WS_MIN_HEADER = 64 << 10;
+static size_t ws_header_bytes(int B, int n_q) { return std::max(WS_MIN_HEADER, WS_COUNTERS_OFF + align256(4 * (size_t)B * n_q)); }
+static size_t ws_bytes_needed(int B, int n_q, int nsplit) {
+  const size_t n = (size_t)B * n_q * nsplit;
+  return ws_header_bytes(B, n_q) + align256(4 * n) * 2 + align256(4 * n * D);
+}
 static int carve_workspace(void* ws, size_t ws_bytes, int B, int n_q, int nsplit, AttnParams& p) {
   const size_t n = (size_t)B * n_q * nsplit;
-  const size_t need = align256(4 * ((size_t)B * n_q + 1)) + align256(4 * n) * 2 + align256(4 * n * D);
-  if (!ws || ws_bytes < need) return GAAC_E_WORKSPACE;
+  if (!ws || ws_bytes < ws_bytes_needed(B, n_q, nsplit)) return GAAC_E_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(ws) & 15) return GAAC_E_ALIGN;
   uint8_t* w = (uint8_t*)ws;
-  p.counters = (int*)w; p.err = p.counters + (size_t)B * n_q; w += align256(4 * ((size_t)B * n_q + 1));
+  p.err = (int*)w; p.counters = (int*)(w + WS_COUNTERS_OFF); w += ws_header_bytes(B, n_q);
   p.pm = (float*)w; w += align256(4 * n);
   p.pl = (float*)w; w += align256(4 * n);
   p.pa = (float*)w;
   return GAAC_OK;
 }
 
-template <bool PAGED>
+template <bool PAGED, bool DUMP>
 static int launch_attn(const AttnParams& p, cudaStream_t st) {
-  cudaFuncSetAttribute(decode_attn_kernel<PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
+  cudaFuncSetAttribute(decode_attn_kernel<PAGED, DUMP>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(p.B * p.n_kv), (unsigned)p.nsplit); cfg.blockDim = dim3(ATT_THREADS);
   cfg.dynamicSmemBytes = ATT_SMEM; cfg.stream = st;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, decode_attn_kernel<PAGED>, p) != cudaSuccess) { cudaGetLastError(); return GAAC_E_LAUNCH; }
+  if (cudaLaunchKernelEx(&cfg, decode_attn_kernel<PAGED, DUMP>, p) != cudaSuccess) { cudaGetLastError(); return GAAC_E_LAUNCH; }
   return launch_status();
 }
 
+static int sm_count_of_current_device() {
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+  if (!cached[dev]) { int n = 0; if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) cached[dev] = n; else cudaGetLastError(); }
+  return cached[dev];
+}
+
+static bool exchange_ok(const gaac_exchange* x) {
+  return x && x->recv && x->flags && x->epoch && x->ticket && x->err && x->world >= 1 && x->world <= 64 && x->rank >= 0 && x->rank < x->world &&
+         x->rows_cap > 0 && x->groups_cap > 0;
+}
+
+// What the slot-layout entry points differ in.
+struct SlotOut {
+  void* out = nullptr; float* out_f32 = nullptr; float* part = nullptr;
+  const gaac_exchange* x = nullptr; bool fused = false;
+  void* dump_k = nullptr; void* dump_v = nullptr; int64_t dump_S = 0;
+};
+
 static int slot_attn(const gaac_side* K, const gaac_side* V, const void* q, const int32_t* slot, int B, int n_q, int n_kv, const int32_t* seq_len,
-                     int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap, int n_base_rows, void* ws, size_t ws_bytes,
-                     void* out, float* out_f32, float* part, void* stream, const gaac_exchange* x = nullptr) {
-  if (!K || !V || !q || !slot || !seq_len || (!out && !part && !x)) return GAAC_E_ARG;
-  if (x && (!x->recv || !x->flags || !x->epoch || !x->ticket || !x->err || x->world < 1 || x->world > 64 || x->rank < 0 || x->rank >= x->world)) return GAAC_E_ARG;
+                     int64_t S_uniform, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap, int n_base_rows, void* ws, size_t ws_bytes,
+                     const SlotOut& o, void* stream) {
+  const gaac_exchange* x = o.x;
+  if (!K || !V || !q || (!o.out && !o.part && !x) || (x && o.fused && !o.out)) return GAAC_E_ARG;
+  if (x && !exchange_ok(x)) return GAAC_E_ARG;
   if (B <= 0 || n_q <= 0 || n_kv <= 0 || nsplit <= 0 || nsplit > 1024 || S_pad <= 0 || S_pad % T || n_base_rows <= 0) return GAAC_E_ARG;
+  if (!seq_len && (S_uniform < 0 || S_uniform > S_pad)) return GAAC_E_ARG;
   if (n_q % n_kv || n_q / n_kv < 1 || n_q / n_kv > 8) return GAAC_E_UNSUPPORTED;
+  if (x && ((int64_t)B * n_q > x->rows_cap || (int64_t)B * n_kv > x->groups_cap)) return GAAC_E_ARG;
+  // fused exchange: a CTA per (row, kv head) waits for the other GPUs inside the kernel, so every CTA of the grid must be
+  // resident at once (one CTA per SM); larger grids use the push + gaac_exchange_merge pair
+  if (x && o.fused && (int64_t)B * n_kv * nsplit > sm_count_of_current_device()) return GAAC_E_UNSUPPORTED;
   for (const gaac_side* s : {K, V}) {
     if (!s->sm || !s->codes || !s->flags || !s->tile_off || !s->ovf || !s->head_start || !s->base3 || !s->base4 || s->ovf_bytes < 0) return GAAC_E_ARG;
     if (!aligned16(s->sm) || !aligned16(s->codes) || !aligned16(s->flags) || (reinterpret_cast<uintptr_t>(s->ovf) & 3)) return GAAC_E_ALIGN;
@@ -862,13 +972,41 @@ static int slot_attn(const gaac_side* K, const gaac_side* V, const void* q, cons
   }
   if (tail_len && tail_cap <= 0) return GAAC_E_ARG;
   if (reinterpret_cast<uintptr_t>(q) & 3) return GAAC_E_ALIGN;
+  if ((o.dump_k || o.dump_v) && (!o.dump_k || !o.dump_v || o.dump_S <= 0 || (reinterpret_cast<uintptr_t>(o.dump_k) & 3) || (reinterpret_cast<uintptr_t>(o.dump_v) & 3))) return GAAC_E_ARG;
   AttnParams p{};
-  p.K = *K; p.V = *V; p.slot = slot; p.seq_len = seq_len; p.tail_len = tail_len; p.tail_cap = tail_cap; p.S_pad = S_pad; p.n_base_rows = n_base_rows;
+  p.K = *K; p.V = *V; p.slot = slot; p.seq_len = seq_len; p.S_uniform = (int)S_uniform; p.tail_len = tail_len; p.tail_cap = tail_cap; p.S_pad = S_pad; p.n_base_rows = n_base_rows;
   p.q = (const uint16_t*)q; p.B = B; p.n_q = n_q; p.n_kv = n_kv; p.G = n_q / n_kv; p.scale_log2 = scale * LOG2E; p.nsplit = nsplit;
-  p.out = (uint16_t*)out; p.out_f32 = out_f32; p.part = part;
-  if (x) { p.x_recv = x->recv; p.x_flags = x->flags; p.x_epoch = x->epoch; p.x_rank = x->rank; p.x_world = x->world; }
+  p.out = (uint16_t*)o.out; p.out_f32 = o.out_f32; p.part = o.part;
+  if (x) {
+    p.x_recv = x->recv; p.x_flags = x->flags; p.x_epoch = x->epoch; p.x_ticket = x->ticket; p.x_err = x->err;
+    p.x_rank = x->rank; p.x_world = x->world; p.x_rows_cap = x->rows_cap; p.x_fused = o.fused ? 1 : 0;
+  }
   if (int e = carve_workspace(ws, ws_bytes, B, n_q, nsplit, p)) return e;
-  return launch_attn<false>(p, (cudaStream_t)stream);
+  if (o.dump_k) {
+    p.dump_k = (uint16_t*)o.dump_k; p.dump_v = (uint16_t*)o.dump_v; p.dump_S = o.dump_S;
+    return launch_attn<false, true>(p, (cudaStream_t)stream);
+  }
+  return launch_attn<false, false>(p, (cudaStream_t)stream);
+}
+
+static int paged_attn(const gaac_paged* st, const int32_t* bt, int64_t bt_stride, const int32_t* seq_lens, const void* q_bf16, int B, int n_q, float scale,
+                      int nsplit, void* workspace, size_t workspace_bytes, void* out_bf16, float* out_f32, void* dump_k, void* dump_v, int64_t dump_S, void* stream) {
+  if (!st || !bt || !seq_lens || !q_bf16 || !out_bf16 || !st->buf || !st->raw || !st->mt || !st->b3k || !st->b4k || !st->b3v || !st->b4v) return GAAC_E_ARG;
+  if (B <= 0 || n_q <= 0 || st->n_kv <= 0 || nsplit <= 0 || nsplit > 1024 || bt_stride <= 0) return GAAC_E_ARG;
+  if (n_q % st->n_kv || n_q / st->n_kv < 1 || n_q / st->n_kv > 8 || st->TS % 16 || st->TS != SLOT_OVF_OFF + st->ovf_slot) return GAAC_E_UNSUPPORTED;
+  if (!aligned16(st->buf) || (reinterpret_cast<uintptr_t>(st->raw) & 3) || (reinterpret_cast<uintptr_t>(q_bf16) & 3)) return GAAC_E_ALIGN;
+  if ((dump_k || dump_v) && (!dump_k || !dump_v || dump_S <= 0 || (reinterpret_cast<uintptr_t>(dump_k) & 3) || (reinterpret_cast<uintptr_t>(dump_v) & 3))) return GAAC_E_ARG;
+  AttnParams p{};
+  p.buf = st->buf; p.raw = (const uint16_t*)st->raw; p.mt = st->mt; p.bt = bt; p.bt_stride = bt_stride; p.TS = st->TS; p.ovf_slot = st->ovf_slot;
+  p.b3k = st->b3k; p.b4k = st->b4k; p.b3v = st->b3v; p.b4v = st->b4v; p.seq_len = seq_lens;
+  p.q = (const uint16_t*)q_bf16; p.B = B; p.n_q = n_q; p.n_kv = st->n_kv; p.G = n_q / st->n_kv; p.scale_log2 = scale * LOG2E; p.nsplit = nsplit;
+  p.out = (uint16_t*)out_bf16; p.out_f32 = out_f32; p.part = nullptr;
+  if (int e = carve_workspace(workspace, workspace_bytes, B, n_q, nsplit, p)) return e;
+  if (dump_k) {
+    p.dump_k = (uint16_t*)dump_k; p.dump_v = (uint16_t*)dump_v; p.dump_S = dump_S;
+    return launch_attn<true, true>(p, (cudaStream_t)stream);
+  }
+  return launch_attn<true, false>(p, (cudaStream_t)stream);
 }
 
 }  // namespace gaac
@@ -877,24 +1015,36 @@ using namespace gaac;
 
 extern "C" size_t gaac_attn_workspace_bytes(int B, int n_q, int nsplit) {
   if (B <= 0 || n_q <= 0 || nsplit <= 0) return 0;
-  const size_t n = (size_t)B * n_q * nsplit;
-  return align256(4 * ((size_t)B * n_q + 1)) + align256(4 * n) * 2 + align256(4 * n * D);
+  return ws_bytes_needed(B, n_q, nsplit);
+}
+
+extern "C" size_t gaac_attn_workspace_header_bytes(int B, int n_q) {
+  if (B <= 0 || n_q <= 0) return 0;
+  return ws_header_bytes(B, n_q);
 }
 
 extern "C" int gaac_decode_attn(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
                                 const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
                                 int n_base_rows, void* workspace, size_t workspace_bytes, void* out_bf16, float* out_f32, void* stream) {
-  if (!out_bf16) return GAAC_E_ARG;
-  return slot_attn(K, V, q_bf16, slot, B, n_q, n_kv, seq_len, S_pad, scale, nsplit, tail_len, tail_cap, n_base_rows, workspace, workspace_bytes,
-                   out_bf16, out_f32, nullptr, stream);
+  if (!out_bf16 || !slot || !seq_len) return GAAC_E_ARG;
+  SlotOut o; o.out = out_bf16; o.out_f32 = out_f32;
+  return slot_attn(K, V, q_bf16, slot, B, n_q, n_kv, seq_len, 0, S_pad, scale, nsplit, tail_len, tail_cap, n_base_rows, workspace, workspace_bytes, o, stream);
+}
+
+extern "C" int gaac_decode_attn_pages(const gaac_side* K, const gaac_side* V, const void* q_bf16, int B, int n_q, int n_kv, int64_t S, int64_t S_pad,
+                                      float scale, int nsplit, int n_base_rows, void* workspace, size_t workspace_bytes, void* out_bf16, float* out_f32,
+                                      float* part, const gaac_exchange* x, int fused, void* stream) {
+  if ((out_bf16 != nullptr) + (part != nullptr) + (x != nullptr && !fused) != 1) return GAAC_E_ARG;      // exactly one destination
+  SlotOut o; o.out = out_bf16; o.out_f32 = out_f32; o.part = part; o.x = x; o.fused = x && fused;
+  return slot_attn(K, V, q_bf16, nullptr, B, n_q, n_kv, nullptr, S, S_pad, scale, nsplit, nullptr, 0, n_base_rows, workspace, workspace_bytes, o, stream);
 }
 
 extern "C" int gaac_decode_attn_partial(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
                                         const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
                                         int n_base_rows, void* workspace, size_t workspace_bytes, float* part, void* stream) {
-  if (!part) return GAAC_E_ARG;
-  return slot_attn(K, V, q_bf16, slot, B, n_q, n_kv, seq_len, S_pad, scale, nsplit, tail_len, tail_cap, n_base_rows, workspace, workspace_bytes,
-                   nullptr, nullptr, part, stream);
+  if (!part || !slot || !seq_len) return GAAC_E_ARG;
+  SlotOut o; o.part = part;
+  return slot_attn(K, V, q_bf16, slot, B, n_q, n_kv, seq_len, 0, S_pad, scale, nsplit, tail_len, tail_cap, n_base_rows, workspace, workspace_bytes, o, stream);
 }
 
 extern "C" int gaac_combine(const float* pm, const float* pl, const float* pa, int64_t n_heads, int n_parts, void* out_bf16, float* out_f32, void* stream) {
@@ -906,21 +1056,30 @@ extern "C" int gaac_combine(const float* pm, const float* pl, const float* pa, i
 extern "C" int gaac_decode_attn_push(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
                                      const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
                                      int n_base_rows, void* workspace, size_t workspace_bytes, const gaac_exchange* x, void* stream) {
-  if (!x) return GAAC_E_ARG;
-  return slot_attn(K, V, q_bf16, slot, B, n_q, n_kv, seq_len, S_pad, scale, nsplit, tail_len, tail_cap, n_base_rows, workspace, workspace_bytes,
-                   nullptr, nullptr, nullptr, stream, x);
+  if (!x || !slot || !seq_len) return GAAC_E_ARG;
+  SlotOut o; o.x = x;
+  return slot_attn(K, V, q_bf16, slot, B, n_q, n_kv, seq_len, 0, S_pad, scale, nsplit, tail_len, tail_cap, n_base_rows, workspace, workspace_bytes, o, stream);
+}
+
+extern "C" int gaac_decode_attn_exchange(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
+                                         const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
+                                         int n_base_rows, void* workspace, size_t workspace_bytes, const gaac_exchange* x, void* out_bf16, float* out_f32,
+                                         void* stream) {
+  if (!x || !slot || !seq_len || !out_bf16) return GAAC_E_ARG;
+  SlotOut o; o.x = x; o.fused = true; o.out = out_bf16; o.out_f32 = out_f32;
+  return slot_attn(K, V, q_bf16, slot, B, n_q, n_kv, seq_len, 0, S_pad, scale, nsplit, tail_len, tail_cap, n_base_rows, workspace, workspace_bytes, o, stream);
 }
 
 extern "C" int gaac_exchange_merge(const gaac_exchange* x, int64_t n_heads, int groups, void* out_bf16, float* out_f32, void* stream) {
-  if (!x || !x->recv || !x->flags || !x->epoch || !x->ticket || !x->err || x->world < 1 || x->world > 64 || x->rank < 0 || x->rank >= x->world) return GAAC_E_ARG;
-  if (n_heads <= 0 || groups <= 0 || (!out_bf16 && !out_f32)) return GAAC_E_ARG;
+  if (!exchange_ok(x)) return GAAC_E_ARG;
+  if (n_heads <= 0 || groups <= 0 || n_heads % groups || n_heads > x->rows_cap || groups > x->groups_cap || (!out_bf16 && !out_f32)) return GAAC_E_ARG;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)n_heads); cfg.blockDim = dim3(128); cfg.stream = (cudaStream_t)stream;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, exchange_merge_kernel, x->recv, x->flags, x->epoch, x->ticket, x->err, x->rank, x->world, groups,
-                         (long)n_heads, (uint16_t*)out_bf16, out_f32) != cudaSuccess) { cudaGetLastError(); return GAAC_E_LAUNCH; }
+  if (cudaLaunchKernelEx(&cfg, exchange_merge_kernel, x->recv, x->flags, x->epoch, x->ticket, x->err, x->rank, x->world, (int)(n_heads / groups),
+                         (long)x->rows_cap, (uint16_t*)out_bf16, out_f32) != cudaSuccess) { cudaGetLastError(); return GAAC_E_LAUNCH; }
   return launch_status();
 }
 
@@ -933,15 +1092,22 @@ extern "C" int gaac_combine_parts(const float* parts, int64_t n_heads, int n_par
 extern "C" int gaac_paged_decode_attn(const gaac_paged* st, const int32_t* bt, int64_t bt_stride, const int32_t* seq_lens, const void* q_bf16,
                                       int B, int n_q, float scale, int nsplit, void* workspace, size_t workspace_bytes,
                                       void* out_bf16, float* out_f32, void* stream) {
-  if (!st || !bt || !seq_lens || !q_bf16 || !out_bf16 || !st->buf || !st->raw || !st->mt || !st->b3k || !st->b4k || !st->b3v || !st->b4v) return GAAC_E_ARG;
-  if (B <= 0 || n_q <= 0 || st->n_kv <= 0 || nsplit <= 0 || nsplit > 1024 || bt_stride <= 0) return GAAC_E_ARG;
-  if (n_q % st->n_kv || n_q / st->n_kv < 1 || n_q / st->n_kv > 8 || st->TS % 16 || st->TS != SLOT_OVF_OFF + st->ovf_slot) return GAAC_E_UNSUPPORTED;
-  if (!aligned16(st->buf) || (reinterpret_cast<uintptr_t>(st->raw) & 3) || (reinterpret_cast<uintptr_t>(q_bf16) & 3)) return GAAC_E_ALIGN;
-  AttnParams p{};
-  p.buf = st->buf; p.raw = (const uint16_t*)st->raw; p.mt = st->mt; p.bt = bt; p.bt_stride = bt_stride; p.TS = st->TS; p.ovf_slot = st->ovf_slot;
-  p.b3k = st->b3k; p.b4k = st->b4k; p.b3v = st->b3v; p.b4v = st->b4v; p.seq_len = seq_lens;
-  p.q = (const uint16_t*)q_bf16; p.B = B; p.n_q = n_q; p.n_kv = st->n_kv; p.G = n_q / st->n_kv; p.scale_log2 = scale * LOG2E; p.nsplit = nsplit;
-  p.out = (uint16_t*)out_bf16; p.out_f32 = out_f32; p.part = nullptr;
-  if (int e = carve_workspace(workspace, workspace_bytes, B, n_q, nsplit, p)) return e;
-  return launch_attn<true>(p, (cudaStream_t)stream);
+  return paged_attn(st, bt, bt_stride, seq_lens, q_bf16, B, n_q, scale, nsplit, workspace, workspace_bytes, out_bf16, out_f32, nullptr, nullptr, 0, stream);
+}
+
+// ---- test hooks: the same kernels, instantiated so that every rebuilt BF16 fragment is also written to memory
+extern "C" int gaac_debug_decode_attn_rebuild(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
+                                              const int32_t* seq_len, int64_t S_uniform, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len,
+                                              int tail_cap, int n_base_rows, void* workspace, size_t workspace_bytes, void* out_bf16, float* out_f32,
+                                              void* k_rebuilt, void* v_rebuilt, int64_t rebuilt_S, void* stream) {
+  if (!out_bf16 || !k_rebuilt || !v_rebuilt) return GAAC_E_ARG;
+  SlotOut o; o.out = out_bf16; o.out_f32 = out_f32; o.dump_k = k_rebuilt; o.dump_v = v_rebuilt; o.dump_S = rebuilt_S;
+  return slot_attn(K, V, q_bf16, slot, B, n_q, n_kv, seq_len, S_uniform, S_pad, scale, nsplit, tail_len, tail_cap, n_base_rows, workspace, workspace_bytes, o, stream);
+}
+
+extern "C" int gaac_debug_paged_decode_attn_rebuild(const gaac_paged* st, const int32_t* bt, int64_t bt_stride, const int32_t* seq_lens, const void* q_bf16,
+                                                    int B, int n_q, float scale, int nsplit, void* workspace, size_t workspace_bytes, void* out_bf16,
+                                                    float* out_f32, void* k_rebuilt, void* v_rebuilt, int64_t rebuilt_S, void* stream) {
+  if (!k_rebuilt || !v_rebuilt) return GAAC_E_ARG;
+  return paged_attn(st, bt, bt_stride, seq_lens, q_bf16, B, n_q, scale, nsplit, workspace, workspace_bytes, out_bf16, out_f32, k_rebuilt, v_rebuilt, rebuilt_S, stream);
 }

@@ -11,24 +11,30 @@ struct AppendParams {
   const int* slot; int n_kv;
   int *tail_len, *seq_len;
   long S_cap, ovf_cap; int n_base_rows;
+  int* err;
 };
 
 // One CTA per (batch row, kv head): warp 0 appends K, warp 1 appends V; the shared counters are advanced once both are done
 // (the reference needs a second launch for that: gaac/kv_cache.py:72-73,87-96).
+// First half: the new row goes into the tail; when that fills the tail, the 16 rows are encoded into registers.  Returns the
+// tile's escape bytes, or -1 when there is no tile to store (tail not full, or the head is at its token capacity).
 template <int KIND_V>
-__device__ __forceinline__ void append_one(WarpScratch& ws, const gaac_store& st, const uint16_t* xrow, long h, int pos, int tile, long S_cap, long ovf_cap,
-                                           int n_base_rows, int lane) {
+__device__ __forceinline__ int append_encode(WarpScratch& ws, const gaac_store& st, const uint16_t* xrow, long h, int pos, int tile, long S_cap,
+                                             int n_base_rows, int lane, LaneTile& lt) {
   uint16_t* tail = reinterpret_cast<uint16_t*>(st.tail) + h * (T * D);
   reinterpret_cast<uint2*>(tail + (long)pos * D)[lane] = reinterpret_cast<const uint2*>(xrow)[lane];       // 32 lanes x 8 B = one row
-  if (pos + 1 != T) return;
-  if ((long)tile * T + T > S_cap) return;             // cache full: never write past the head's capacity (callers check capacity at prefill)
+  if (pos + 1 != T) return -1;
+  if ((long)tile * T + T > S_cap) return -1;          // cache full: never write past the head's capacity (callers check capacity at prefill)
   __syncwarp();
   stage_rows(ws, tail, D, T, lane);                   // rows written by this warp just now are visible to it after the barrier
   const int brow = (int)(h % n_base_rows);
   u32 b3w[8], b4w[8];
   load_base_words<KIND_V>(st.base3 + (long)brow * D, st.base4 + (long)brow * D, lane, b3w, b4w);
-  LaneTile lt;
-  const int total = encode_tile_warp<KIND_V>(ws, T, b3w, b4w, lane, lt);
+  return encode_tile_warp<KIND_V>(ws, T, b3w, b4w, lane, lt);
+}
+// Second half: the encoded tile goes to the head's streams, its escape bytes behind the bytes in use.
+template <int KIND_V>
+__device__ __forceinline__ void append_store(WarpScratch& ws, const gaac_store& st, const LaneTile& lt, long h, int tile, int total, long S_cap, long ovf_cap, int lane) {
   const long trow = h * S_cap + (long)tile * T;
   store_tile_payload<KIND_V>(lt, st.sm + trow * D, st.codes + trow * CB, lane);
   if (lane < T) st.flags[trow + lane] = (int)ws.fl[lane];
@@ -40,16 +46,28 @@ __device__ __forceinline__ void append_one(WarpScratch& ws, const gaac_store& st
 
 __global__ void __launch_bounds__(64) append_kv_kernel(const __grid_constant__ AppendParams p) {
   __shared__ __align__(16) WarpScratch scratch[2];
+  __shared__ int s_fit[2];
   const int i = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sl = p.slot[i / p.n_kv];
   if (sl < 0) return;
   const long h = (long)sl * p.n_kv + i % p.n_kv;
   const int pos = p.tail_len[h], tile = p.seq_len[h] / T;
-  if (warp == 0) append_one<0>(scratch[0], p.K, p.k_new + (long)i * D, h, pos, tile, p.S_cap, p.ovf_cap, p.n_base_rows, lane);
-  else append_one<1>(scratch[1], p.V, p.v_new + (long)i * D, h, pos, tile, p.S_cap, p.ovf_cap, p.n_base_rows, lane);
+  LaneTile lt;
+  const gaac_store& st = warp == 0 ? p.K : p.V;
+  const int total = warp == 0 ? append_encode<0>(scratch[0], p.K, p.k_new + (long)i * D, h, pos, tile, p.S_cap, p.n_base_rows, lane, lt)
+                              : append_encode<1>(scratch[1], p.V, p.v_new + (long)i * D, h, pos, tile, p.S_cap, p.n_base_rows, lane, lt);
+  // A tile whose escape bytes (plus the 8 bytes a reader may touch behind them) do not fit what is left of the head's escape
+  // stream is not stored, for K and V alike: nothing is written outside the head's share, the counters stay, *err counts it.
+  if (lane == 0) s_fit[warp] = total < 0 || (long)st.ovf_used[h] + total + 8 <= p.ovf_cap;
   __syncthreads();                                    // both warps have read the counters
+  const bool fits = s_fit[0] && s_fit[1];
+  if (total >= 0 && fits) {
+    if (warp == 0) append_store<0>(scratch[0], p.K, lt, h, tile, total, p.S_cap, p.ovf_cap, lane);
+    else append_store<1>(scratch[1], p.V, lt, h, tile, total, p.S_cap, p.ovf_cap, lane);
+  }
   if (threadIdx.x == 0) {
     const int t = pos + 1, full = (t == T);
+    if (full && !fits) { if (p.err) atomicAdd(p.err, 1); return; }
     if (full && (long)tile * T + T > p.S_cap) return;   // cache full: the tile was not stored, keep the counters (the last tail row is overwritten next time)
     p.tail_len[h] = full ? 0 : t;
     if (full) p.seq_len[h] = p.seq_len[h] + T;
@@ -190,7 +208,7 @@ static int check_paged(const gaac_paged* st) {
 using namespace gaac;
 
 extern "C" int gaac_append_kv(const gaac_store* K, const gaac_store* V, const void* k_new, const void* v_new, const int32_t* slot, int B, int n_kv,
-                              int32_t* tail_len, int32_t* seq_len, int64_t S_cap, int64_t ovf_cap, int n_base_rows, void* stream) {
+                              int32_t* tail_len, int32_t* seq_len, int64_t S_cap, int64_t ovf_cap, int n_base_rows, int32_t* err, void* stream) {
   if (!K || !V || !k_new || !v_new || !slot || !tail_len || !seq_len) return GAAC_E_ARG;
   if (B <= 0 || n_kv <= 0 || S_cap <= 0 || S_cap % T || ovf_cap <= 0 || n_base_rows <= 0) return GAAC_E_ARG;
   for (const gaac_store* s : {K, V}) {
@@ -198,7 +216,7 @@ extern "C" int gaac_append_kv(const gaac_store* K, const gaac_store* V, const vo
     if (!aligned16(s->sm) || !aligned16(s->codes) || !aligned16(s->tail)) return GAAC_E_ALIGN;
   }
   if ((reinterpret_cast<uintptr_t>(k_new) & 7) || (reinterpret_cast<uintptr_t>(v_new) & 7)) return GAAC_E_ALIGN;
-  AppendParams p{*K, *V, (const uint16_t*)k_new, (const uint16_t*)v_new, slot, n_kv, tail_len, seq_len, S_cap, ovf_cap, n_base_rows};
+  AppendParams p{*K, *V, (const uint16_t*)k_new, (const uint16_t*)v_new, slot, n_kv, tail_len, seq_len, S_cap, ovf_cap, n_base_rows, err};
   append_kv_kernel<<<(unsigned)(B * n_kv), 64, 0, (cudaStream_t)stream>>>(p);
   return launch_status();
 }
@@ -247,4 +265,4 @@ extern "C" const char* gaac_status_string(int status) {
   }
 }
 
-extern "C" int gaac_abi_version(void) { return 1; }
+extern "C" int gaac_abi_version(void) { return 2; }

@@ -8,7 +8,7 @@
 // The workspace (split partials + the per-head ticket counters of the fused kernel) lives in a file-scope device array of a
 // fixed, modest size.  Every GPU that loads the library holds these bytes until the process exits.  All calls on a device
 // share the array: it keeps the previous call's contents, the part that has to start at zero (the counters) is cleared on
-// the stream in front of every launch, and two calls that overlap on the same GPU (different streams, or two host threads)
+// the stream in front of every launch (the error word in front of them is sticky and read with gaac_static_workspace_error), and two calls that overlap on the same GPU (different streams, or two host threads)
 // race on it - callers serialise such calls themselves or use gaac_decode_attn with separate workspaces.
 #include <mutex>
 #include "gaac_api.cuh"
@@ -52,9 +52,26 @@ extern "C" int gaac_decode_attn_static(const gaac_side* K, const gaac_side* V, c
   if (need == 0 || need > STATIC_SCRATCH_BYTES) return GAAC_E_WORKSPACE;
   void* ws = nullptr;
   if (int e = scratch_for_current_device(&ws)) return e;
-  // the ticket counters at the head of the workspace must start at zero whatever an earlier call left behind
-  const size_t header = ((size_t)4 * ((size_t)B * n_q + 1) + 255) & ~(size_t)255;     // split counters + the error word
-  if (cudaMemsetAsync(ws, 0, header, (cudaStream_t)stream) != cudaSuccess) { cudaGetLastError(); return GAAC_E_LAUNCH; }
+  // The split counters (everything in the header behind its first 256 bytes) must start at zero whatever an earlier call left
+  // behind.  The first 256 bytes hold the error word, which is sticky: it is left alone here so that a caller can still read
+  // it with gaac_static_workspace_error after later calls.
+  const size_t header = gaac_attn_workspace_header_bytes(B, n_q);
+  if (cudaMemsetAsync((unsigned char*)ws + 256, 0, header - 256, (cudaStream_t)stream) != cudaSuccess) { cudaGetLastError(); return GAAC_E_LAUNCH; }
   return gaac_decode_attn(K, V, q_bf16, slot, B, n_q, n_kv, seq_len, S_pad, scale, nsplit, tail_len, tail_cap, n_base_rows,
                           ws, STATIC_SCRATCH_BYTES, out_bf16, out_f32, stream);
+}
+
+// The error word of the shared array on the current device: *err_host becomes 1 when a bounded wait inside one of the
+// gaac_decode_attn_static calls made so far on this device ran out (the output of that call was not valid), else 0; with
+// clear != 0 the word is reset afterwards.  Waits for `stream` (it copies four bytes to the host), so it is not for the hot
+// path: call it where the caller synchronises anyway.
+extern "C" int gaac_static_workspace_error(int32_t* err_host, int clear, void* stream) {
+  if (!err_host) return GAAC_E_ARG;
+  void* ws = nullptr;
+  if (int e = scratch_for_current_device(&ws)) return e;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (cudaMemcpyAsync(err_host, ws, sizeof(int32_t), cudaMemcpyDeviceToHost, st) != cudaSuccess) { cudaGetLastError(); return GAAC_E_LAUNCH; }
+  if (clear && cudaMemsetAsync(ws, 0, sizeof(int32_t), st) != cudaSuccess) { cudaGetLastError(); return GAAC_E_LAUNCH; }
+  if (cudaStreamSynchronize(st) != cudaSuccess) { cudaGetLastError(); return GAAC_E_LAUNCH; }
+  return GAAC_OK;
 }

@@ -58,56 +58,65 @@ def merge_partials(part: torch.Tensor, group=None, combine_fn=None, out_f32: tor
 
 
 class PeerExchange:
-    """Receive buffers and arrival counters of all ranks, mapped into every rank (peer memory over NVLink), for the fused
-    partial exchange: the attention kernel stores its partial rows into every rank's buffer and gaac_exchange_merge waits for
-    all of them.  Built on torch's symmetric memory (one rendezvous at construction); raises when that is unavailable, and
-    the caller falls back to the NCCL all-gather.  n_heads = B * n_q rows per exchange."""
+    """Receive buffers and arrival flags of all ranks, mapped into every rank (peer memory over NVLink), for the fused
+    partial exchange: the attention kernel stores its partial rows into every rank's buffer, sets its flag there, and either
+    the same launch (fused) or gaac_exchange_merge waits for all ranks' rows and merges them.  Built on torch's symmetric
+    memory (one rendezvous at construction) with NVLink multicast binding switched off (plain peer loads and stores only);
+    raises when the mapping is unavailable, and the caller falls back to the NCCL all-gather.
+    n_heads = B * n_q rows per exchange at most, groups = B * n_kv flag groups at most."""
 
-    def __init__(self, n_heads: int, device, group=None):
+    def __init__(self, n_heads: int, device, group=None, groups: int | None = None):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")      # before the first rendezvous of the process
         import torch.distributed._symmetric_memory as symm
-        from . import _lib
         group = group if group is not None else dist.group.WORLD
-        self.world, self.rank, self.n_heads = dist.get_world_size(group), dist.get_rank(group), n_heads
-        recv_floats = 2 * self.world * n_heads * 130
-        self._flag_off = (recv_floats * 4 + 255) // 256 * 256
-        nbytes = self._flag_off + 256 * ((self.world * 4 + 255) // 256)
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.n_heads, self.groups = n_heads, groups if groups is not None else n_heads
+        self._flag_off, nbytes = self._layout(self.world, self.n_heads, self.groups)
         self._buf = symm.empty(nbytes, dtype=torch.uint8, device=device)
         self._buf.zero_()
         self._hdl = symm.rendezvous(self._buf, group)
         ptrs = [int(p) for p in self._hdl.buffer_ptrs]
         self._setup(ptrs, device)
         torch.cuda.synchronize(device)
-        dist.barrier(group)                                     # every rank's counters are zero before anyone pushes
+        dist.barrier(group)                                     # every rank's flags are zero before anyone pushes
+
+    @staticmethod
+    def _layout(world: int, n_heads: int, groups: int) -> tuple[int, int]:
+        """(byte offset of the flags, total bytes): 2 x world x n_heads rows of 130 floats, then groups x world int32 flags."""
+        flag_off = (2 * world * n_heads * 130 * 4 + 255) // 256 * 256
+        return flag_off, flag_off + (groups * world * 4 + 255) // 256 * 256
 
     def _setup(self, ptrs, device):
         from . import _lib
         self._recv = torch.tensor(ptrs, dtype=torch.int64, device=device)
         self._flags = torch.tensor([p + self._flag_off for p in ptrs], dtype=torch.int64, device=device)
-        self._state = torch.zeros(3, dtype=torch.int32, device=device)                     # epoch, ticket, err
+        self._state = torch.zeros(3, dtype=torch.int32, device=device)                     # exchange number, ticket, err
         self.x = _lib.Exchange(self._recv.data_ptr(), self._flags.data_ptr(), self._state.data_ptr(), self._state.data_ptr() + 4,
-                               self._state.data_ptr() + 8, self.rank, self.world)
+                               self._state.data_ptr() + 8, self.rank, self.world, self.n_heads, self.groups)
 
     @classmethod
-    def local(cls, bufs, rank: int, n_heads: int):
-        """An exchange whose 'ranks' are buffers on one GPU (uint8 tensors made by local_buffer): lets one process run all
-        ranks' pushes and then all ranks' merges in stream order, with nothing left to wait for."""
+    def local(cls, bufs, rank: int, n_heads: int, groups: int | None = None):
+        """An exchange whose 'ranks' are buffers on one GPU (uint8 tensors made by local_buffer): lets one process run the ranks
+        one after the other in stream order.  Only the last rank to push may use the fused launch (everything it waits for is
+        there already); the others push and merge with separate launches."""
         self = cls.__new__(cls)
-        self.world, self.rank, self.n_heads = len(bufs), rank, n_heads
-        self._flag_off = (2 * self.world * n_heads * 130 * 4 + 255) // 256 * 256
+        self.world, self.rank, self.n_heads, self.groups = len(bufs), rank, n_heads, groups if groups is not None else n_heads
+        self._flag_off, _ = cls._layout(self.world, self.n_heads, self.groups)
         self._buf = bufs[rank]
         self._setup([b.data_ptr() for b in bufs], bufs[rank].device)
         return self
 
-    @staticmethod
-    def local_buffer(world: int, n_heads: int, device) -> torch.Tensor:
-        flag_off = (2 * world * n_heads * 130 * 4 + 255) // 256 * 256
-        return torch.zeros(flag_off + 256 * ((world * 4 + 255) // 256), dtype=torch.uint8, device=device)
+    @classmethod
+    def local_buffer(cls, world: int, n_heads: int, device, groups: int | None = None) -> torch.Tensor:
+        return torch.zeros(cls._layout(world, n_heads, groups if groups is not None else n_heads)[1], dtype=torch.uint8, device=device)
 
-    def merge(self, groups: int, out_f32: torch.Tensor | None = None) -> torch.Tensor:
-        """Launch the wait-and-merge kernel on the current stream (after the push); returns [n_heads, 128] bf16."""
+    def merge(self, groups: int, out_f32: torch.Tensor | None = None, n_heads: int | None = None) -> torch.Tensor:
+        """Launch the wait-and-merge kernel on the current stream (after a push-only launch); returns [n_heads, 128] bf16."""
         from . import _lib
-        out = torch.empty(self.n_heads, 128, dtype=torch.bfloat16, device=self._state.device)
-        _lib.check(_lib.lib().gaac_exchange_merge(self.x, self.n_heads, groups, out.data_ptr(), _lib.ptr(out_f32),
+        n_heads = self.n_heads if n_heads is None else n_heads
+        out = torch.empty(n_heads, 128, dtype=torch.bfloat16, device=self._state.device)
+        _lib.check(_lib.lib().gaac_exchange_merge(self.x, n_heads, groups, out.data_ptr(), _lib.ptr(out_f32),
                                                   _lib.stream_ptr(self._state.device)), "gaac_exchange_merge")
         return out
 
@@ -119,46 +128,42 @@ class PeerExchange:
 class ContextSplitAttention:
     """Batch-1 decode attention with the context split across the ranks of a process group.
 
-    Every rank holds the Pages of its own token range (kp, vp: kinds 'k' / 'v', H = n_kv heads).  __call__(q) runs the fused
-    kernel in partial mode and merges the ranks' partials; every rank returns the full [n_q, 128] output."""
+    Every rank holds the Pages of its own token range (kp, vp: kinds 'k' / 'v', H = n_kv heads).  __call__(q) attends over the
+    local range and merges the ranks' partials; every rank returns the full [n_q, 128] output."""
 
-    def __init__(self, kp, vp, n_q: int, scale: float | None = None, nsplit: int | None = None, group=None, exchange: str = "auto"):
+    def __init__(self, kp, vp, n_q: int, scale: float | None = None, nsplit: int | None = None, group=None, exchange: str = "auto", fused: bool = True):
         """exchange: 'p2p' = partial rows pushed by the attention kernel into peer memory (PeerExchange), 'nccl' = NCCL
-        all-gather + merge kernel, 'auto' = p2p when the symmetric-memory rendezvous succeeds, else nccl."""
-        from .kernel import choose_nsplit_sm100
+        all-gather + merge kernel, 'auto' = p2p when the symmetric-memory rendezvous succeeds, else nccl.  fused (p2p only):
+        the attention launch also waits for the other ranks and merges (one launch per layer); it needs the whole grid
+        resident, so it is dropped when n_kv * nsplit exceeds the SM count."""
+        from .kernel import choose_nsplit_sm100, SM_COUNT_B200
         self.kp, self.vp, self.n_q, self.group = kp, vp, n_q, group
+        self.n_kv = kp.H
         self.peer = None
         if exchange in ("auto", "p2p") and dist.is_initialized() and dist.get_world_size(group) > 1 and kp.sm.is_cuda:
             try:
-                self.peer = PeerExchange(n_q, kp.sm.device, group)
+                self.peer = PeerExchange(n_q, kp.sm.device, group, groups=self.n_kv)
             except Exception:
                 if exchange == "p2p":
                     raise
-        self.n_kv = kp.H
         self.scale = scale if scale is not None else 128 ** -0.5
         self.nsplit = nsplit or choose_nsplit_sm100(1, self.n_kv, max(kp.S, 1))
-        dev = kp.sm.device
-        self._slots = torch.zeros(1, dtype=torch.int32, device=dev)
-        self._SL = torch.full((self.n_kv,), kp.S, dtype=torch.int32, device=dev)
-        self._e32 = torch.empty(0, dtype=torch.int32, device=dev); self._ebf = torch.empty(0, dtype=torch.bfloat16, device=dev)
-        self._part = torch.empty(n_q, 130, dtype=torch.float32, device=dev)
+        self.fused = fused and self.n_kv * self.nsplit <= SM_COUNT_B200
+        self._part = torch.empty(n_q, 130, dtype=torch.float32, device=kp.sm.device)
 
     def partial(self, q: torch.Tensor) -> torch.Tensor:
-        from .kernel import _ext
-        kp, vp = self.kp, self.vp
-        _ext().gaac_attn_launch(kp.sm, kp.codes, kp.flags, kp.tile_off, kp.ovf, kp.ovf_head_start, kp.base3, kp.base4,
-                                vp.sm, vp.codes, vp.flags, vp.tile_off, vp.ovf, vp.ovf_head_start, vp.base3, vp.base4,
-                                q.reshape(self.n_q, 128), self._slots, self.n_q, self.n_kv, self._SL, kp.sm.shape[1] // 128, self.scale, self.nsplit,
-                                self._ebf, self._ebf, self._e32, 0, partial=self._part)
+        from .kernel import _pages_call
+        _pages_call(q.reshape(1, self.n_q, 128), self.kp, self.vp, 1, self.n_q, self.n_kv, self.scale, self.nsplit, part=self._part)
         return self._part
 
     def __call__(self, q: torch.Tensor, out_f32: torch.Tensor | None = None) -> torch.Tensor:
-        if self.peer is not None:
-            from .kernel import _ext
-            kp, vp = self.kp, self.vp
-            _ext().gaac_attn_launch(kp.sm, kp.codes, kp.flags, kp.tile_off, kp.ovf, kp.ovf_head_start, kp.base3, kp.base4,
-                                    vp.sm, vp.codes, vp.flags, vp.tile_off, vp.ovf, vp.ovf_head_start, vp.base3, vp.base4,
-                                    q.reshape(self.n_q, 128), self._slots, self.n_q, self.n_kv, self._SL, kp.sm.shape[1] // 128, self.scale,
-                                    self.nsplit, self._ebf, self._ebf, self._e32, 0, exchange=self.peer.x)
-            return self.peer.merge(self.n_kv, out_f32=out_f32)
-        return merge_partials(self.partial(q), self.group, out_f32=out_f32)
+        if self.peer is None:
+            return merge_partials(self.partial(q), self.group, out_f32=out_f32)
+        from .kernel import _pages_call
+        q3 = q.reshape(1, self.n_q, 128)
+        if self.fused:
+            out = torch.empty(self.n_q, 128, dtype=torch.bfloat16, device=q.device)
+            _pages_call(q3, self.kp, self.vp, 1, self.n_q, self.n_kv, self.scale, self.nsplit, out=out, out_f32=out_f32, exchange=self.peer.x, fused=True)
+            return out
+        _pages_call(q3, self.kp, self.vp, 1, self.n_q, self.n_kv, self.scale, self.nsplit, exchange=self.peer.x)
+        return self.peer.merge(self.n_kv, out_f32=out_f32)

@@ -9,7 +9,8 @@ from __future__ import annotations
 import torch
 from . import _lib
 
-_WS = {}        # (device index, stream) -> workspace tensor; the kernel leaves its counters zeroed, so the buffer is reusable
+_WS = {}        # (device index, stream) -> workspace tensor, zeroed once: every call leaves its split counters at zero and the
+                # header in front of the partials has a fixed size, so calls of any shape can share it (B*n_q up to 16320)
 SM_COUNT_B200 = 148
 ATT_WARPS = 16  # warps per CTA of the CUDA kernel (one CTA per SM)
 
@@ -18,17 +19,19 @@ def workspace(dev, B: int, n_q: int, nsplit: int) -> torch.Tensor:
     need = _lib.lib().gaac_attn_workspace_bytes(B, n_q, nsplit)
     key = (torch.device(dev).index, torch.cuda.current_stream(dev).cuda_stream)
     ws = _WS.get(key)
-    if ws is None or ws.numel() < need:
+    if ws is None or ws.numel() < need or B * n_q > 16320 or getattr(ws, "_gaac_big", False):
+        # a fresh zeroed buffer when none fits, and for the rare shapes whose counters outgrow the fixed-size header
         ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+        ws._gaac_big = B * n_q > 16320
         _WS[key] = ws
     return ws
 
 
-def workspace_error(dev, B: int, n_q: int) -> bool:
+def workspace_error(dev, B: int = 0, n_q: int = 0) -> bool:
     """True when a kernel that used the cached workspace of the current stream gave up on a bounded wait for its own asynchronous
-    copies (the int32 behind the B*n_q split counters).  Reads device memory, so it synchronises; meant for tests and debugging."""
+    copies (the int32 at the start of the workspace).  Reads device memory, so it synchronises; meant for tests and debugging."""
     ws = _WS.get((torch.device(dev).index, torch.cuda.current_stream(dev).cuda_stream))
-    return bool(ws is not None and ws[4 * B * n_q:4 * B * n_q + 4].view(torch.int32).item() != 0)
+    return bool(ws is not None and ws[0:4].view(torch.int32).item() != 0)
 
 
 def choose_nsplit(B: int, n_kv: int, S: int, target_ctas: int = 96, min_tok: int = 512, cap: int = 48) -> int:
@@ -70,12 +73,13 @@ class _Ext:
 
     @staticmethod
     def gaac_attn_launch(smk, ck, fk, tok, ovk, ohsk, b3k, b4k, smv, cv, fv, tov, ovv, ohsv, b3v, b4v,
-                         q, slot, n_q, n_kv, SL, S_pad, scale, nsplit, kt, vt, TL, TCAP, out_f32=None, partial=None, exchange=None):
+                         q, slot, n_q, n_kv, SL, S_pad, scale, nsplit, kt, vt, TL, TCAP, out_f32=None, partial=None, exchange=None, fused=False):
         """Same positional arguments as the reference launcher (gaac/kernel.py:296-300): 16 K/V buffers, q [B*n_q, 128] bf16,
         slot int32 [B], n_q, n_kv, SL int32 [heads], S_pad, scale, nsplit, K/V tails [heads, TCAP, 128] bf16 (empty = none),
         TL int32 [heads], TCAP.  Returns out [B*n_q, 128] bf16.  Extras: out_f32 (fp32 tensor to receive the un-rounded
         result), partial ([B*n_q, 130] fp32 tensor: write (m, l, acc) there instead of the output), exchange (a
-        gaac_b200._lib.Exchange: push the partial rows into every rank's receive buffer instead; returns None)."""
+        gaac_b200._lib.Exchange: push the partial rows into every rank's receive buffer instead and return None; with fused=True
+        the same launch also waits for the other ranks' rows, merges them and returns the output)."""
         D = 128
         if q.size(-1) != D:
             raise RuntimeError("head_dim must be 128")
@@ -93,6 +97,10 @@ class _Ext:
         L = _lib.lib()
         common = (K, V, q.data_ptr(), slot.data_ptr(), B, n_q, n_kv, SL.data_ptr(), S_pad, float(scale), int(nsplit),
                   TL.data_ptr() if has_tail else None, int(TCAP) if has_tail else 0, b3k.size(0), ws.data_ptr(), ws.numel())
+        if exchange is not None and fused:
+            out = torch.empty(B * n_q, D, dtype=q.dtype, device=dev)
+            _lib.check(L.gaac_decode_attn_exchange(*common, exchange, out.data_ptr(), _lib.ptr(out_f32), _lib.stream_ptr(dev)), "gaac_decode_attn_exchange")
+            return out
         if exchange is not None:
             _lib.check(L.gaac_decode_attn_push(*common, exchange, _lib.stream_ptr(dev)), "gaac_decode_attn_push")
             return None
@@ -118,9 +126,8 @@ def _ext():
 def attention(q, kp, vp, scale=None, nsplit=None, out_f32=None):
     """Decode attention over two Pages (kinds 'k' / 'v', H = B*n_kv heads of equal length).
     q: [B, n_q, D] bf16 (one query token per sequence) -> [B, n_q, D] bf16.  (gaac/kernel.py:345-359)
-    nsplit=None picks the B200 heuristic; an explicit nsplit is honoured as given.
-    What depends only on the Pages (identity slot map, per-head lengths, the two gaac_side descriptors) is built once and kept
-    on the Page objects, so a decode loop pays one library call per layer."""
+    nsplit=None picks the B200 heuristic; an explicit nsplit is honoured as given.  The two gaac_side descriptors are built
+    once and kept on the Page objects, so a decode loop pays one library call per layer."""
     B, n_q, Dq = q.shape
     if Dq != 128:
         raise RuntimeError("head_dim must be 128")
@@ -132,24 +139,32 @@ def attention(q, kp, vp, scale=None, nsplit=None, out_f32=None):
         raise RuntimeError("GQA group size must be 1..8")
     dev = q.device
     if nsplit is None: nsplit = choose_nsplit_sm100(B, n_kv, kp.S)
-    cache = getattr(kp, "_attn_meta", None)          # identity slot map, per-head lengths, K descriptor: built once per Page
-    if cache is None or cache[0].device != dev or cache[0].numel() != B or cache[2].ovf != kp.ovf.data_ptr():
-        cache = (torch.arange(B, dtype=torch.int32, device=dev), torch.full((kp.H,), kp.S, dtype=torch.int32, device=dev),
-                 _side(kp.sm, kp.codes, kp.flags, kp.tile_off, kp.ovf, kp.ovf_head_start, kp.base3, kp.base4, None))
-        kp._attn_meta = cache
-    slots, SL, K = cache
-    V = getattr(vp, "_attn_side", None)
-    if V is None or V.ovf != vp.ovf.data_ptr():
-        V = _side(vp.sm, vp.codes, vp.flags, vp.tile_off, vp.ovf, vp.ovf_head_start, vp.base3, vp.base4, None)
-        vp._attn_side = V
-    q2 = q.reshape(B * n_q, Dq)
+    out = torch.empty(B * n_q, Dq, dtype=q.dtype, device=dev)
+    _pages_call(q, kp, vp, B, n_q, n_kv, scale, nsplit, out=out, out_f32=out_f32)
+    return out.view(B, n_q, Dq)
+
+
+def _page_side(pg) -> _lib.Side:
+    """The gaac_side descriptor of a Page, built once and kept on the Page object (rebuilt when its escape stream was replaced)."""
+    sd = getattr(pg, "_attn_side", None)
+    if sd is None or sd.ovf != pg.ovf.data_ptr() or sd.sm != pg.sm.data_ptr():
+        sd = _side(pg.sm, pg.codes, pg.flags, pg.tile_off, pg.ovf, pg.ovf_head_start, pg.base3, pg.base4, None)
+        pg._attn_side = sd
+    return sd
+
+
+def _pages_call(q, kp, vp, B, n_q, n_kv, scale, nsplit, out=None, out_f32=None, part=None, exchange=None, fused=False):
+    """One gaac_decode_attn_pages call: every head of the two Pages holds kp.S tokens and batch row b reads heads b*n_kv ..,
+    which is all the identity slot map and the constant length table of the reference's entry point said
+    (gaac/kernel.py:349-352); the kernel needs neither table."""
+    dev = q.device
+    q2 = q.reshape(B * n_q, 128)
     if not q2.is_contiguous(): q2 = q2.contiguous()
     ws = workspace(dev, B, n_q, nsplit)
-    out = torch.empty(B * n_q, Dq, dtype=q.dtype, device=dev)
-    _lib.check(_lib.lib().gaac_decode_attn(K, V, q2.data_ptr(), slots.data_ptr(), B, n_q, n_kv, SL.data_ptr(), kp.sm.shape[1] // 128,
-                                           float(scale if scale is not None else Dq ** -0.5), int(nsplit), None, 0, kp.base3.size(0),
-                                           ws.data_ptr(), ws.numel(), out.data_ptr(), _lib.ptr(out_f32), _lib.stream_ptr(dev)), "gaac_decode_attn")
-    return out.view(B, n_q, Dq)
+    _lib.check(_lib.lib().gaac_decode_attn_pages(_page_side(kp), _page_side(vp), q2.data_ptr(), B, n_q, n_kv, kp.S, kp.sm.shape[1] // 128,
+                                                 float(scale if scale is not None else 128 ** -0.5), int(nsplit), kp.base3.size(0),
+                                                 ws.data_ptr(), ws.numel(), _lib.ptr(out), _lib.ptr(out_f32), _lib.ptr(part), exchange,
+                                                 1 if fused else 0, _lib.stream_ptr(dev)), "gaac_decode_attn_pages")
 
 
 def combine(pm: torch.Tensor, pl: torch.Tensor, pa: torch.Tensor, out_f32: torch.Tensor | None = None) -> torch.Tensor:

@@ -1,120 +1,161 @@
-"""Compressed KV cache of one attention layer for serving, slot layout (mirror of gaac/kv_cache.py).
+"""Serving cache of one attention layer in the slot layout (drop-in for gaac/kv_cache.py).
 
-Each sequence owns a slot = n_kv cache heads with a fixed token capacity.  A head holds compressed 16-token tiles plus a raw
-BF16 tail of 0..15 tokens; when a decode step fills the tail, the tile is compressed in place and its escape bytes are
-appended to the head's escape stream.  All decode-step work (append + attention) runs on the device with no host
-synchronisation and is CUDA-graph capturable: batch rows reach their slot through a device slot map, rows with slot -1 are
-skipped.  Exponent bases are either calibrated per model ([n_kv, D] tables) or per sequence from its own prompt at prefill
-([n_slots*n_kv, D] tables).
+A slot is the storage of one sequence: n_kv cache heads, each with room for `capacity` tokens.  Tokens live in two places:
+whole 16-token tiles in compressed form, and the 0..15 tokens that do not fill a tile yet as plain BF16 rows (the tail).  The
+decode step appends one token per batch row; the append that completes a tail turns it into a compressed tile on the device
+and adds the tile's escape bytes to the head's escape stream.  Nothing in a decode step (append, attention) talks to the host,
+so the step can be captured in a CUDA graph; batch rows find their slot through a device tensor, and a row whose slot is -1 is
+left alone (its attention output is zero).  The exponent bases come either from an offline calibration ([n_kv, 128] tables
+shared by all sequences) or, when none are given, from each sequence's own prompt at prefill time (one table row per cache
+head).
+
+Buffer shapes, field names and the byte accounting follow gaac/kv_cache.py:99-146 because callers and the attention launcher
+read them; the device work goes through libgaac_b200.so.
 """
 from __future__ import annotations
 import torch
 from . import _lib
-from .codec import Codec, Page, D, T, CB, row_offsets
+from .codec import Codec, Page, D, T, CB
 from .encoder import TileEncoder
 from .kernel import _ext, choose_nsplit, choose_nsplit_sm100
 
-TAIL = 16
-TILE_MAX_ESC = 1280    # worst-case escape bytes of one 16-token tile (all 256 groups raw)
+TAIL = T                       # rows of the raw tail buffer of a head
+TILE_MAX_ESC = 1280            # a tile whose 256 groups are all raw has 256 * 5 escape bytes
+_OVER_READ = 8                 # the readers may touch up to 8 bytes behind the last escape byte of a head
+
+
+def _round_up_tokens(n: int) -> int:
+    return -(-n // T) * T
 
 
 class _Store:
-    """Compressed buffers of one kind ('k' or 'v') for H cache heads (gaac/kv_cache.py:99-119)."""
+    """What one kind ('k' or 'v') keeps for H cache heads (gaac/kv_cache.py:99-119): sign/mantissa bytes, codes, tag words and
+    tile offsets per head, one escape stream of ovf_cap bytes per head inside `ovf`, the raw tails, and the base tables."""
+
     def __init__(self, kind, H, cap, ovf_cap, base3, base4, dev):
-        self.kind, self.H, self.ovf_cap = kind, H, ovf_cap
-        self.sm = torch.zeros(H, cap * D, dtype=torch.uint8, device=dev)
-        self.codes = torch.zeros(H, cap * CB, dtype=torch.uint8, device=dev)
-        self.flags = torch.zeros(H, cap, dtype=torch.int32, device=dev)
-        self.tile_off = torch.zeros(H, cap // T, dtype=torch.int32, device=dev)
-        self.ovf = torch.zeros(H * ovf_cap, dtype=torch.uint8, device=dev)
-        self.head_start = (torch.arange(H + 1, device=dev, dtype=torch.int32) * ovf_cap).contiguous()
-        self.ovf_used = torch.zeros(H, dtype=torch.int32, device=dev)
-        self.tail = torch.zeros(H, TAIL, D, dtype=torch.bfloat16, device=dev)
+        self.kind, self.H = kind, H
         self.base3, self.base4 = base3, base4
+        u8 = dict(dtype=torch.uint8, device=dev)
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.sm = torch.zeros(H, cap * D, **u8)
+        self.codes = torch.zeros(H, cap * CB, **u8)
+        self.flags = torch.zeros(H, cap, **i32)
+        self.tile_off = torch.zeros(H, cap // T, **i32)
+        self.ovf_used = torch.zeros(H, **i32)
+        self.tail = torch.zeros(H, TAIL, D, dtype=torch.bfloat16, device=dev)
         self.enc = TileEncoder(kind, dev)
+        self._set_escape_stream(torch.zeros(H * ovf_cap, **u8), ovf_cap)
+
+    def _set_escape_stream(self, ovf, ovf_cap):
+        self.ovf, self.ovf_cap = ovf, ovf_cap
+        self.head_start = torch.arange(self.H + 1, dtype=torch.int32, device=ovf.device) * ovf_cap
 
     def grow(self, ovf_cap):
-        new = torch.zeros(self.H * ovf_cap, dtype=torch.uint8, device=self.ovf.device)
-        new.view(self.H, ovf_cap)[:, :self.ovf_cap] = self.ovf.view(self.H, self.ovf_cap)
-        self.ovf, self.ovf_cap = new, ovf_cap
-        self.head_start = (torch.arange(self.H + 1, device=new.device, dtype=torch.int32) * ovf_cap).contiguous()
+        """Give every head an escape stream of ovf_cap bytes, keeping what is stored."""
+        wider = torch.zeros(self.H, ovf_cap, dtype=torch.uint8, device=self.ovf.device)
+        wider[:, :self.ovf_cap].copy_(self.ovf.view(self.H, self.ovf_cap))
+        self._set_escape_stream(wider.view(-1), ovf_cap)
 
     def c_store(self) -> _lib.Store:
-        return _lib.Store(self.sm.data_ptr(), self.codes.data_ptr(), self.flags.data_ptr(), self.tile_off.data_ptr(), self.ovf.data_ptr(),
-                          self.ovf_used.data_ptr(), self.tail.data_ptr(), self.base3.data_ptr(), self.base4.data_ptr())
+        p = lambda t: t.data_ptr()
+        return _lib.Store(p(self.sm), p(self.codes), p(self.flags), p(self.tile_off), p(self.ovf), p(self.ovf_used), p(self.tail), p(self.base3), p(self.base4))
 
 
 class CompressedKVCache:
     def __init__(self, n_slots: int, n_kv: int, capacity: int, bases: dict | None = None,
                  ovf_bytes_per_tile: int = 128, device="cuda"):
-        """capacity: max tokens per sequence; bases: {'k3','k4','v3','v4'} uint8 [n_kv, D] (None = per-sequence calibration);
-        ovf_bytes_per_tile: escape-stream reservation per 16-token tile."""
-        if not torch.device(device).type == "cuda":
+        """capacity: tokens a sequence may hold (rounded up to whole tiles).  bases: {'k3','k4','v3','v4'} -> uint8 [n_kv, 128],
+        or None to calibrate every sequence on its own prompt.  ovf_bytes_per_tile: escape bytes reserved per tile of capacity."""
+        if torch.device(device).type != "cuda":
             raise RuntimeError("CompressedKVCache needs a CUDA device: gaac_b200 has no CPU path")
         _lib.lib()
         self.n_slots, self.n_kv = n_slots, n_kv
-        self.cap = (capacity + T - 1) // T * T
-        self.H = H = n_slots * n_kv
+        self.cap = _round_up_tokens(capacity)
+        self.H = n_slots * n_kv
         self.per_sequence_bases = bases is None
-        NB = H if bases is None else n_kv
-        def table(key):
-            if bases is None: return torch.zeros(NB, D, dtype=torch.uint8, device=device)
-            return bases[key].to(device, torch.uint8).reshape(n_kv, D).contiguous()
-        ovf_cap = (self.cap // T) * ovf_bytes_per_tile + 8
-        self.k = _Store("k", H, self.cap, ovf_cap, table("k3"), table("k4"), device)
-        self.v = _Store("v", H, self.cap, ovf_cap, table("v3"), table("v4"), device)
-        self.S = torch.zeros(H, dtype=torch.int32, device=device)          # compressed tokens per head
-        self.tail_len = torch.zeros(H, dtype=torch.int32, device=device)
-        self.growable = True       # set False once CUDA graphs captured the buffer addresses
+        ovf_cap = (self.cap // T) * ovf_bytes_per_tile + _OVER_READ
+        tables = {}
+        for key in ("k3", "k4", "v3", "v4"):
+            if self.per_sequence_bases:
+                tables[key] = torch.zeros(self.H, D, dtype=torch.uint8, device=device)           # filled per sequence by prefill
+            else:
+                tables[key] = bases[key].to(device, torch.uint8).reshape(n_kv, D).contiguous()
+        self.k = _Store("k", self.H, self.cap, ovf_cap, tables["k3"], tables["k4"], device)
+        self.v = _Store("v", self.H, self.cap, ovf_cap, tables["v3"], tables["v4"], device)
+        self.S = torch.zeros(self.H, dtype=torch.int32, device=device)                           # tokens in compressed tiles, per head
+        self.tail_len = torch.zeros(self.H, dtype=torch.int32, device=device)                    # tokens in the raw tail, per head
+        self.append_errors = torch.zeros(1, dtype=torch.int32, device=device)                    # tiles an append refused for lack of escape room
+        self.growable = True                                                                     # False: the buffers may not move (their addresses are baked into CUDA graphs)
 
     @staticmethod
     def bytes_per_slot(n_kv: int, capacity: int, ovf_bytes_per_tile: int = 128, per_sequence_bases: bool = True) -> int:
-        """gaac/kv_cache.py:142-146."""
-        cap = (capacity + T - 1) // T * T
-        per_head = cap * (D + CB + 4) + (cap // T) * 4 + (cap // T) * ovf_bytes_per_tile + 8 + 8 + TAIL * D * 2 + (2 * D if per_sequence_bases else 0)
-        return 2 * n_kv * per_head + 8 * n_kv
+        """Device bytes one slot costs, the figure an engine divides its memory budget by (gaac/kv_cache.py:142-146)."""
+        cap = _round_up_tokens(capacity)
+        tiles = cap // T
+        payload = cap * (D + CB + 4)                                   # sign/mantissa + codes + tag word per token
+        escapes = tiles * ovf_bytes_per_tile + _OVER_READ
+        counters = tiles * 4 + 8                                       # tile offsets; head_start and ovf_used entries
+        tail = TAIL * D * 2
+        own_bases = 2 * D if per_sequence_bases else 0
+        one_kind_one_head = payload + escapes + counters + tail + own_bases
+        return 2 * n_kv * one_kind_one_head + 8 * n_kv                 # K and V; the token and tail counters of the heads
+
+    def _heads(self, slot: int) -> slice:
+        return slice(slot * self.n_kv, (slot + 1) * self.n_kv)
 
     # ------------------------------------------------------------------ prefill
     def prefill(self, slot: int, k: torch.Tensor, v: torch.Tensor):
-        """Store a sequence's prompt K/V ([L, n_kv, D] bf16, token-major as produced by the model) in `slot`.
-        (gaac/kv_cache.py:149-169)"""
+        """Put a prompt's K and V ([L, n_kv, 128] bf16, one row per token as the model produces them) into `slot`: whole tiles
+        compressed, the remainder into the tail.  Replaces whatever the slot held.  (gaac/kv_cache.py:149-169)"""
         L = k.shape[0]
         assert L <= self.cap, f"sequence of {L} tokens exceeds the cache capacity {self.cap}"
-        h0, h1 = slot * self.n_kv, (slot + 1) * self.n_kv
-        Sf = L // T * T
+        hs = self._heads(slot)
+        n_full = L // T * T
         for st, x in ((self.k, k), (self.v, v)):
-            xh = x.transpose(0, 1).contiguous()                                # [n_kv, L, D]
+            per_head = x.transpose(0, 1).contiguous()                                         # [n_kv, L, 128]
             if self.per_sequence_bases:
-                c = Codec(self.n_kv, x.device).calibrate(xh)
-                st.base3[h0:h1] = c.base3; st.base4[h0:h1] = c.base4
-            st.ovf_used[h0:h1] = 0
-            if Sf:
-                bidx = (torch.arange(h0, h1, device=x.device, dtype=torch.int32) % st.base3.shape[0]).contiguous()
-                tb = st.enc.encode_tiles(xh[:, :Sf], st.base3, st.base4, st.sm[h0:h1], st.codes[h0:h1], st.flags[h0:h1], Sf, self.cap, self.n_kv, bidx=bidx)
-                _, head_bytes = st.enc.tile_offsets(tb)
-                need = int(head_bytes.max()) + TILE_MAX_ESC + 8        # headroom for the next decode tile before check_capacity runs
-                if need > st.ovf_cap: self._grow(need)
-                st.tile_off[h0:h1, :Sf // T] = st.enc.compact(tb, st.head_start[h0:h1 + 1], st.ovf)
-                st.ovf_used[h0:h1] = head_bytes
-            if L > Sf: st.tail[h0:h1, :L - Sf] = xh[:, Sf:]
-        self.S[h0:h1] = Sf; self.tail_len[h0:h1] = L - Sf
+                own = Codec(self.n_kv, x.device).calibrate(per_head)
+                st.base3[hs], st.base4[hs] = own.base3, own.base4
+            st.ovf_used[hs] = 0
+            if n_full:
+                self._store_tiles(st, hs, per_head[:, :n_full], n_full)
+            if L > n_full:
+                st.tail[hs, :L - n_full] = per_head[:, n_full:]
+        self.S[hs] = n_full
+        self.tail_len[hs] = L - n_full
+
+    def _store_tiles(self, st: _Store, hs: slice, x: torch.Tensor, n_tok: int):
+        """Compress x [n_kv, n_tok, 128] (n_tok a multiple of 16) into the heads hs of st, escape streams from offset 0."""
+        rows = torch.arange(hs.start, hs.stop, device=x.device, dtype=torch.int32) % st.base3.shape[0]     # base row of each head
+        tile_bytes = st.enc.encode_tiles(x, st.base3, st.base4, st.sm[hs], st.codes[hs], st.flags[hs], n_tok, self.cap, self.n_kv, bidx=rows.contiguous())
+        _, head_bytes = st.enc.tile_offsets(tile_bytes)
+        # room for these tiles and for one more worst-case tile, which an append may add before the next check_capacity
+        wanted = int(head_bytes.max()) + TILE_MAX_ESC + _OVER_READ
+        if wanted > st.ovf_cap:
+            self._grow(wanted)
+        st.tile_off[hs, :n_tok // T] = st.enc.compact(tile_bytes, st.head_start[hs.start:hs.stop + 1], st.ovf)
+        st.ovf_used[hs] = head_bytes
 
     # ------------------------------------------------------------------ decode step
     def append(self, slots: torch.Tensor, k: torch.Tensor, v: torch.Tensor):
-        """One new token per batch row: slots int32 [B] (-1 = skip), k/v [B, n_kv, D] bf16.  One launch, graph-safe.
-        (gaac/kv_cache.py:172-181)"""
-        k, v = k.contiguous(), v.contiguous()
-        K, V = self.k, self.v
+        """One new token for every batch row: slots int32 [B] (-1: skip the row), k / v [B, n_kv, 128] bf16.  A single kernel
+        launch that also advances the counters; safe inside a CUDA graph.  (gaac/kv_cache.py:172-181)"""
         B = slots.numel()
-        if B == 0: return
-        _lib.check(_lib.lib().gaac_append_kv(K.c_store(), V.c_store(), k.data_ptr(), v.data_ptr(), slots.data_ptr(), B, self.n_kv,
-                                             self.tail_len.data_ptr(), self.S.data_ptr(), self.cap, K.ovf_cap, K.base3.shape[0],
-                                             _lib.stream_ptr(k.device)), "gaac_append_kv")
+        if B == 0:
+            return
+        k, v = k.contiguous(), v.contiguous()
+        rc = _lib.lib().gaac_append_kv(self.k.c_store(), self.v.c_store(), k.data_ptr(), v.data_ptr(), slots.data_ptr(), B, self.n_kv,
+                                       self.tail_len.data_ptr(), self.S.data_ptr(), self.cap, self.k.ovf_cap, self.k.base3.shape[0],
+                                       self.append_errors.data_ptr(), _lib.stream_ptr(k.device))
+        _lib.check(rc, "gaac_append_kv")
 
     def attention(self, q: torch.Tensor, slots: torch.Tensor, scale: float, max_len: int | None = None, nsplit: int | None = None, out_f32=None):
-        """q: [B, n_q, D] bf16 (row b attends over slot slots[b]) -> [B, n_q, D] bf16.  (gaac/kv_cache.py:183-192)"""
+        """q [B, n_q, 128] bf16, row b attending over slot slots[b] -> [B, n_q, 128] bf16; rows with slot -1 come back as
+        zeros.  max_len (longest sequence in the batch, the capacity when omitted) only steers the split count.
+        (gaac/kv_cache.py:183-192)"""
         B, n_q, _ = q.shape
-        if nsplit is None: nsplit = choose_nsplit_sm100(B, self.n_kv, max_len or self.cap)
+        if nsplit is None:
+            nsplit = choose_nsplit_sm100(B, self.n_kv, max_len or self.cap)
         K, V = self.k, self.v
         out = _ext().gaac_attn_launch(K.sm, K.codes, K.flags, K.tile_off, K.ovf, K.head_start, K.base3, K.base4,
                                       V.sm, V.codes, V.flags, V.tile_off, V.ovf, V.head_start, V.base3, V.base4,
@@ -124,43 +165,51 @@ class CompressedKVCache:
 
     # ------------------------------------------------------------------ housekeeping
     def max_escape_bytes(self) -> torch.Tensor:
+        """Fullest escape stream over all heads and both kinds (a device scalar)."""
         return torch.maximum(self.k.ovf_used.max(), self.v.ovf_used.max())
 
     def check_capacity(self, used: int | None = None):
-        """Call at least once every 16 decode steps: each head finalizes at most one tile in 16 steps, so keeping one
-        worst-case tile of headroom makes the escape streams overflow-proof between checks.  (gaac/kv_cache.py:198-203)"""
-        used = int(self.max_escape_bytes()) if used is None else used
-        if used + TILE_MAX_ESC + 8 > self.k.ovf_cap: self._grow(used + TILE_MAX_ESC + 8)
+        """Keep one worst-case tile of escape room free in every head.  A head completes at most one tile per 16 decode steps, so
+        calling this every 16 steps (or more often) means an append never runs out of room.  `used`: the caller's own reading of
+        max_escape_bytes(), to save the device read.  (gaac/kv_cache.py:198-203)"""
+        if used is None:
+            used = int(self.max_escape_bytes())
+        wanted = used + TILE_MAX_ESC + _OVER_READ
+        if wanted > self.k.ovf_cap:
+            self._grow(wanted)
 
     def _grow(self, need: int):
         if not self.growable:
             raise RuntimeError(f"escape stream needs {need} B per head but holds {self.k.ovf_cap} B and CUDA graphs are captured; "
                                "raise gaac_ovf_bytes_per_tile or calibrate the exponent bases on representative prompts")
-        cap = max(2 * self.k.ovf_cap, need + 4096 + 7) // 8 * 8
-        self.k.grow(cap); self.v.grow(cap)
+        new_cap = max(2 * self.k.ovf_cap, need + 4096 + 7) // 8 * 8       # at least double, so growth is rare
+        for st in (self.k, self.v):
+            st.grow(new_cap)
 
     def decompress(self, slot: int) -> tuple[torch.Tensor, torch.Tensor]:
-        """Bit-exact BF16 K/V of `slot` ([L, n_kv, D] each) from the compressed tiles + raw tail.  (gaac/kv_cache.py:211-226)"""
-        h0, h1 = slot * self.n_kv, (slot + 1) * self.n_kv
-        S, tl_ = int(self.S[h0]), int(self.tail_len[h0])
-        out = []
+        """The slot's K and V back as BF16 [L, n_kv, 128], bit for bit what went in: decoded tiles followed by the tail.
+        (gaac/kv_cache.py:211-226)"""
+        hs = self._heads(slot)
+        n_comp, n_tail = int(self.S[hs.start]), int(self.tail_len[hs.start])
+        result = []
         for st in (self.k, self.v):
-            parts = []
-            if S:
-                per_seq = st.base3.shape[0] != self.n_kv
-                b3, b4 = (st.base3[h0:h1], st.base4[h0:h1]) if per_seq else (st.base3, st.base4)
-                pg = Page(st.sm[h0:h1], st.codes[h0:h1], st.flags[h0:h1], None,
-                          st.ovf, st.head_start[h0:h1 + 1], st.tile_off[h0:h1], b3, b4, self.n_kv, S, self.n_kv, st.kind)
-                parts.append(Codec.decode(pg))
-            parts.append(st.tail[h0:h1, :tl_])
-            out.append(torch.cat(parts, 1).transpose(0, 1).contiguous())
-        return out[0], out[1]
+            pieces = [st.tail[hs, :n_tail]]
+            if n_comp:
+                own_rows = st.base3.shape[0] != self.n_kv
+                b3 = st.base3[hs] if own_rows else st.base3
+                b4 = st.base4[hs] if own_rows else st.base4
+                view = Page(st.sm[hs], st.codes[hs], st.flags[hs], None, st.ovf, st.head_start[hs.start:hs.stop + 1], st.tile_off[hs],
+                            b3, b4, self.n_kv, n_comp, self.n_kv, st.kind)
+                pieces.insert(0, Codec.decode(view))
+            result.append(torch.cat(pieces, 1).transpose(0, 1).contiguous())
+        return result[0], result[1]
 
     def stats(self) -> dict:
-        """Bytes in use (compressed tiles + escapes + metadata + raw tails) vs the BF16 bytes of the same tokens.
+        """Bytes the stored tokens occupy (tiles, escapes, tag words, tile offsets, raw tails) against their size as plain BF16.
         (gaac/kv_cache.py:228-234)"""
-        S = int(self.S.sum()); tl_ = int(self.tail_len.sum())
-        esc = int(self.k.ovf_used.sum() + self.v.ovf_used.sum())
-        used = 2 * (S * (D + CB + 4) + (S // T) * 4 + tl_ * D * 2) + esc
-        bf16 = 2 * (S + tl_) * D * 2
-        return dict(tokens=(S + tl_) // max(1, self.n_kv), bytes_used=used, bf16_bytes=bf16, ratio=bf16 / max(1, used))
+        comp_tokens, tail_tokens = int(self.S.sum()), int(self.tail_len.sum())                 # summed over heads
+        escapes = int(self.k.ovf_used.sum()) + int(self.v.ovf_used.sum())
+        per_kind = comp_tokens * (D + CB + 4) + (comp_tokens // T) * 4 + tail_tokens * D * 2
+        used = 2 * per_kind + escapes
+        plain = 2 * (comp_tokens + tail_tokens) * D * 2
+        return dict(tokens=(comp_tokens + tail_tokens) // max(1, self.n_kv), bytes_used=used, bf16_bytes=plain, ratio=plain / max(1, used))

@@ -1,24 +1,28 @@
-"""Store path of the paged layout (mirror of gaac/vllm/store.py): writes new K/V tokens into the compressed block buffer.
+"""Writing new K/V tokens into the paged block buffer (drop-in for gaac/vllm/store.py).
 
-Block (16 tokens, all n_kv heads, K and V) = 2*n_kv tile slots of TS bytes, slot t = 2*kvh + kind; physical tile
-p = block*(2*n_kv) + t.  Entry e (built on the host) = (block id, first token row of this step in the K/V tensors, block
-offset of that row, number of new rows).
-  * block not full after this step -> new rows go to the raw side pool RAW[r] (popped from a per-layer free stack when the
-                                      block starts), MT[p] = ~r
-  * block completes this step      -> the 16 rows are compressed into the block's tile slot when the escape bytes fit the
-                                      slot (MT[p] = p, raw tile released) or kept raw (MT[p] = ~r)
-Pops happen only in the store kernel, pushes only in the free kernel that follows it.
+The serving engine owns one flat uint8 buffer per layer, cut into 16-token blocks.  A block has one tile slot of TS bytes for
+every (kv head, kind): slot index inside the block t = 2*kvh + kind (kind 0 = K, 1 = V), so tile slot p = block*2*n_kv + t sits
+at byte p*TS.  What the engine tells the store per decode or prefill step is a list of entries, one per touched block:
+(block id, row of the step's K/V tensors where this block's new tokens start, position inside the block where they go, how many).
+
+Two cases per tile slot.  A block that is still filling keeps its rows as plain BF16 in a tile of a side pool (`raw`); the
+pool tile is taken from a free stack the first time the block is written, and the mode table remembers it as mt[p] = ~r.  A block
+that the step completes is compressed: if the tile's escape bytes fit the slot's escape area the tile goes into its slot,
+mt[p] = p again, and the pool tile goes back on the stack; if they do not fit the tile simply stays in the pool for good.
+Pool tiles are popped only by the store kernel and pushed back only by the kernel launched right behind it, so the two never
+race on the stack.  A pop from an empty stack is counted in `err` instead of trapping.
 """
 from __future__ import annotations
 import torch
 from .. import _lib
 
 D = 128
-SM_OFF, CD_OFF, FL_OFF, OVF_OFF = 0, 2048, 2816, 2880   # byte layout of a tile slot; TS = OVF_OFF + OVF_SLOT
+SM_OFF, CD_OFF, FL_OFF, OVF_OFF = 0, 2048, 2816, 2880   # where sign/mantissa, codes, tag words and escapes start inside a tile slot; TS = OVF_OFF + ovf_slot
 
 
 class LayerState:
-    """Per-layer device state outside the block buffer: raw side pool, mode table, free stack, bases (gaac/vllm/store.py:177-203)."""
+    """Everything of one layer that lives outside the block buffer (gaac/vllm/store.py:177-203): the side pool of raw tiles, the
+    mode table, the free stack with its top index, the error counter and the four base tables."""
 
     def __init__(self, num_blocks: int, n_kv: int, raw_tiles: int, bases: dict, ovf_slot: int, device):
         if torch.device(device).type != "cuda":
@@ -26,11 +30,14 @@ class LayerState:
         _lib.lib()
         self.n_kv, self.ovf_slot, self.TS = n_kv, ovf_slot, OVF_OFF + ovf_slot
         assert self.TS % 16 == 0, "OVF_SLOT must be a multiple of 16"
-        self.mt = torch.arange(num_blocks * 2 * n_kv, dtype=torch.int32, device=device)          # every tile starts 'compressed at itself'
+        i32 = dict(dtype=torch.int32, device=device)
+        n_slots = num_blocks * 2 * n_kv
+        self.mt = torch.arange(n_slots, **i32)                                   # mt[p] == p: nothing of the block is in the pool
         self.raw = torch.zeros(raw_tiles, 16, D, dtype=torch.bfloat16, device=device)
-        self.stack = torch.arange(raw_tiles, dtype=torch.int32, device=device); self.top = torch.tensor([raw_tiles], dtype=torch.int32, device=device)
-        self.err = torch.zeros(1, dtype=torch.int32, device=device)
-        self.b3k, self.b4k, self.b3v, self.b4v = (bases[k].to(device).to(torch.uint8).contiguous() for k in ("k3", "k4", "v3", "v4"))
+        self.stack = torch.arange(raw_tiles, **i32)                              # all pool tiles free
+        self.top = torch.full((1,), raw_tiles, **i32)
+        self.err = torch.zeros(1, **i32)
+        self.b3k, self.b4k, self.b3v, self.b4v = (bases[name].to(device).to(torch.uint8).contiguous() for name in ("k3", "k4", "v3", "v4"))
 
     @property
     def bases(self):

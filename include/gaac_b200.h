@@ -102,17 +102,23 @@ typedef struct {
   const void* tail;           /* [heads, tail_cap, 128] bf16 raw tail, or NULL */
 } gaac_side;
 
-/* Bytes of workspace gaac_decode_attn / gaac_paged_decode_attn need for (B, n_q, nsplit). */
+/* Bytes of workspace gaac_decode_attn / gaac_paged_decode_attn need for (B, n_q, nsplit), and the size of the header at its
+ * start.  Workspace = header | split partials.  Header: an int32 error word at byte 0, the int32 split counters (one per row
+ * and kv head) from byte 256.  The header must be zero on the first use; every call leaves the counters zero, so a workspace
+ * is reusable as it is.  The header is 64 KiB for every B*n_q up to 16320, so calls of different shapes (batch size, head
+ * count, split count) can share one workspace: no call's partials lie where another call's counters do.  Only a workspace that
+ * has been used with B*n_q > 16320 must be zeroed again before it is used with a different B*n_q.  The error word is set to
+ * 1 when a bounded wait of the kernel on its own asynchronous copies ran out (the output of that call is then not valid); it
+ * is never cleared by the library and stays 0 in normal operation.  A workspace must be 16-byte aligned and must not be shared
+ * by calls that overlap on the GPU. */
 size_t gaac_attn_workspace_bytes(int B, int n_q, int nsplit);
+size_t gaac_attn_workspace_header_bytes(int B, int n_q);
 
 /* Fused decode attention over compressed K/V.  q [B, n_q, 128] bf16; batch row b reads cache head slot[b]*n_kv + kvh
  * (slot[b] < 0: padded row, output exactly 0); seq_len[cache head] compressed tokens; tail_len[cache head] raw tail tokens
  * (NULL when there is no tail).  nsplit >= 1 context splits per (row, kv head).  out [B, n_q, 128] bf16; when out_f32 is
- * non-NULL the un-rounded fp32 result is written there as well.  workspace: gaac_attn_workspace_bytes bytes, its first
- * 4*(B*n_q + 1) bytes (rounded up to 256) must be zero on the first use: B*n_q int32 split counters, left zero by every call,
- * then one int32 error word that the kernel sets to 1 if a bounded wait on its own asynchronous copies ever ran out (the
- * output of that call is then not valid; it stays 0 in normal operation).  n_base_rows: rows of the base tables
- * (cache head h uses row h % n_base_rows).  Replaces gaac_attn_launch = gaac_attn<G> + gaac_tail<G> + gaac_combine<128>
+ * non-NULL the un-rounded fp32 result is written there as well.  workspace: gaac_attn_workspace_bytes bytes with a zeroed
+ * header (see above).  n_base_rows: rows of the base tables (cache head h uses row h % n_base_rows).  Replaces gaac_attn_launch = gaac_attn<G> + gaac_tail<G> + gaac_combine<128>
  * (gaac/kernel.py:48-326). */
 int gaac_decode_attn(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
                      const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
@@ -125,8 +131,12 @@ int gaac_decode_attn(const gaac_side* K, const gaac_side* V, const void* q_bf16,
  * Limits: gaac_attn_workspace_bytes(B, n_q, nsplit) must not exceed gaac_static_workspace_bytes(), else GAAC_E_WORKSPACE;
  * every GPU that loads the library holds the array until the process exits; all calls on a GPU share it, so calls that
  * overlap on one GPU race (serialise them, or use gaac_decode_attn with one workspace each).  The first call on a device
- * resolves the array's device address; make that call outside of any stream capture. */
+ * resolves the array's device address; make that call outside of any stream capture.
+ * gaac_static_workspace_error copies the array's error word (see gaac_attn_workspace_bytes) of the current device to
+ * *err_host, clears it afterwards when clear != 0, and waits for `stream`: the one way to learn that a bounded wait ran out in
+ * an earlier gaac_decode_attn_static call; call it where the caller synchronises anyway. */
 size_t gaac_static_workspace_bytes(void);
+int gaac_static_workspace_error(int32_t* err_host, int clear, void* stream);
 int gaac_decode_attn_static(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
                             const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
                             int n_base_rows, void* out_bf16, float* out_f32, void* stream);
@@ -151,15 +161,19 @@ int gaac_decode_attn_partial(const gaac_side* K, const gaac_side* V, const void*
                              int n_base_rows, void* workspace, size_t workspace_bytes, float* part, void* stream);
 
 /* Cross-GPU context split without a collective library on the data path: one process per GPU, every rank's receive buffer
- * and arrival counters mapped into every rank's address space (peer memory over NVLink).  No counterpart in the reference,
+ * and arrival flags mapped into every rank's address space (peer memory over NVLink).  No counterpart in the reference,
  * which is single-GPU.
- *   recv[r]  : rank r's receive buffer, 2 * world * n_heads * 130 floats (two exchanges deep, indexed by the parity of the
- *              exchange counter, then by sending rank, then by query head)
- *   flags[r] : rank r's arrival counters, int[world], zero before the first exchange, never reset (they count (row, kv head)
- *              groups received from each rank since the start)
- *   epoch, ticket, err : this rank's own device ints, zero before the first exchange; epoch counts finished exchanges and must
- *              advance in step on all ranks (every rank makes the same sequence of calls); err becomes 1 when a wait ran out
- * recv and flags are DEVICE arrays of `world` pointers. */
+ *   recv[r]  : rank r's receive buffer, 2 * world * rows_cap * 130 floats (two exchanges deep, indexed by the parity of the
+ *              exchange number, then by sending rank, then by query-head row b*n_q + head)
+ *   flags[r] : rank r's arrival flags, int[groups_cap * world], zero before the first exchange: flag (g, s) holds the number
+ *              of the last exchange for which rank s delivered the rows of (row, kv head) group g.  Flags carry numbers, they
+ *              do not count, so B and n_kv may change from one exchange to the next (within rows_cap / groups_cap), and an
+ *              exchange that timed out leaves the following ones intact
+ *   epoch, ticket, err : this rank's own device ints, zero before the first exchange; epoch = number of finished exchanges
+ *              and must advance in step on all ranks (every rank makes the same sequence of calls); err becomes 1 when a
+ *              wait ran out
+ * recv and flags are DEVICE arrays of `world` pointers.  Buffers are two exchanges deep, which is enough as long as
+ * consecutive exchanges use the same B, n_q and n_kv; ranks that change the shape synchronise with one another first. */
 typedef struct {
   float* const* recv;
   int32_t* const* flags;
@@ -167,19 +181,41 @@ typedef struct {
   int32_t* ticket;
   int32_t* err;
   int rank, world;
+  int rows_cap, groups_cap;
 } gaac_exchange;
 
 /* gaac_decode_attn_partial whose last CTA of every (row, kv head) stores its partial rows straight into every rank's
- * receive buffer (plain stores over NVLink, a system-scope fence, then one system-scope add per rank on the arrival counter):
- * the exchange rides on the attention kernel's epilogue, there is no separate send. */
+ * receive buffer (plain stores over NVLink, one system-scope fence, then this rank's flag of the group is set on every
+ * rank): the exchange rides on the attention kernel's epilogue, there is no separate send.  Finish with
+ * gaac_exchange_merge on the same stream. */
 int gaac_decode_attn_push(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
                           const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
                           int n_base_rows, void* workspace, size_t workspace_bytes, const gaac_exchange* x, void* stream);
 
 /* Wait (bounded: about one second, then *err = 1 and a zero output) until the partials of all ranks for the current
- * exchange have arrived, merge them as gaac_combine does and advance the exchange counter.  n_heads = B * n_q,
+ * exchange have arrived, merge them as gaac_combine does and advance the exchange number.  n_heads = B * n_q,
  * groups = B * n_kv of the matching gaac_decode_attn_push.  Launch it on the stream of the push, after it. */
 int gaac_exchange_merge(const gaac_exchange* x, int64_t n_heads, int groups, void* out_bf16, float* out_f32, void* stream);
+
+/* Push, wait and merge in ONE launch: the CTA that pushed the rows of a (row, kv head) group goes on to wait (same bound)
+ * for the other ranks' rows of that group, merges them and writes out [B, n_q, 128] (out_f32 optional); the exchange number
+ * advances when all groups are through.  Because CTAs wait for other GPUs inside the kernel, the whole grid must be resident
+ * at once: B*n_kv*nsplit may not exceed the SM count (GAAC_E_UNSUPPORTED otherwise; use the pair above).  Every rank must
+ * launch it for every exchange, one process per GPU: two "ranks" launched one after the other on ONE GPU would wait for each
+ * other until the bound runs out. */
+int gaac_decode_attn_exchange(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
+                              const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
+                              int n_base_rows, void* workspace, size_t workspace_bytes, const gaac_exchange* x, void* out_bf16, float* out_f32,
+                              void* stream);
+
+/* Decode attention over two Pages (all B*n_kv heads hold S tokens, row b reads heads b*n_kv .., no tail): the
+ * `attention(q, kp, vp)` entry of the reference (gaac/kernel.py:345-359), which builds an identity slot map and a constant
+ * length table for its launcher; here both are implied, so the kernel's prologue has no dependent table loads.  Exactly one
+ * destination: out_bf16 (out_f32 optional) | part (as gaac_decode_attn_partial) | x with fused == 0 (as
+ * gaac_decode_attn_push); x with fused != 0 and out_bf16 = gaac_decode_attn_exchange. */
+int gaac_decode_attn_pages(const gaac_side* K, const gaac_side* V, const void* q_bf16, int B, int n_q, int n_kv, int64_t S, int64_t S_pad,
+                           float scale, int nsplit, int n_base_rows, void* workspace, size_t workspace_bytes, void* out_bf16, float* out_f32,
+                           float* part, const gaac_exchange* x, int fused, void* stream);
 
 /* ---------------------------------------------------------------------------------------------- slot cache (layout A) append */
 
@@ -192,9 +228,13 @@ typedef struct {
 /* One new token per batch row: k_new/v_new [B, n_kv, 128] bf16, row b goes to cache head slot[b]*n_kv + kvh (slot < 0:
  * skipped).  Writes the token into the head's 16-token tail; when the tail fills, encodes it as tile seq_len/16, appends
  * its escapes at ovf + h*ovf_cap + ovf_used[h], sets tile_off and advances ovf_used; finally advances tail_len / seq_len.
+ * A tile that would pass the head's token capacity, or whose escape bytes (+ 8 bytes of read padding) do not fit what is left of
+ * the head's ovf_cap bytes, is not stored: nothing is written outside the head's share and the head's counters stay as they
+ * were (the reference writes past the share in the second case, gaac/kv_cache.py:63-66; its callers avoid it with
+ * check_capacity); the second case increments *err when err != NULL (device int32, e.g. polled with check_capacity).
  * Replaces _append_kv + _advance (gaac/kv_cache.py:22-96, 172-181). */
 int gaac_append_kv(const gaac_store* K, const gaac_store* V, const void* k_new, const void* v_new, const int32_t* slot, int B, int n_kv,
-                   int32_t* tail_len, int32_t* seq_len, int64_t S_cap, int64_t ovf_cap, int n_base_rows, void* stream);
+                   int32_t* tail_len, int32_t* seq_len, int64_t S_cap, int64_t ovf_cap, int n_base_rows, int32_t* err, void* stream);
 
 /* ---------------------------------------------------------------------------------------------- paged layout (layout B) */
 
@@ -229,6 +269,22 @@ int gaac_paged_decode_blocks(const gaac_paged* st, const int32_t* pairs, int P, 
 int gaac_paged_decode_attn(const gaac_paged* st, const int32_t* bt, int64_t bt_stride, const int32_t* seq_lens, const void* q_bf16,
                            int B, int n_q, float scale, int nsplit, void* workspace, size_t workspace_bytes,
                            void* out_bf16, float* out_f32, void* stream);
+
+/* ---------------------------------------------------------------------------------------------- test hooks */
+
+/* gaac_decode_attn / gaac_paged_decode_attn compiled so that every BF16 fragment word the kernel rebuilds on its way to the
+ * tensor cores is also written out: k_rebuilt / v_rebuilt [B*n_kv, rebuilt_S, 128] bf16, row t of (row b, kv head) = token t
+ * of that head (compressed tiles, raw tiles, the filling block and the slot layout's tail behind the compressed tokens);
+ * rows the kernel never reads are left untouched.  Same arguments otherwise (slot and seq_len may be NULL with S_uniform as
+ * in gaac_decode_attn_pages), same attention output.  For tests: the rebuild inside the fused kernel (gaac/kernel.py:24-46,
+ * 96-135 in the reference) is otherwise visible only through a softmax-weighted sum.  Slower than the regular entry. */
+int gaac_debug_decode_attn_rebuild(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
+                                   const int32_t* seq_len, int64_t S_uniform, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len,
+                                   int tail_cap, int n_base_rows, void* workspace, size_t workspace_bytes, void* out_bf16, float* out_f32,
+                                   void* k_rebuilt, void* v_rebuilt, int64_t rebuilt_S, void* stream);
+int gaac_debug_paged_decode_attn_rebuild(const gaac_paged* st, const int32_t* bt, int64_t bt_stride, const int32_t* seq_lens, const void* q_bf16,
+                                         int B, int n_q, float scale, int nsplit, void* workspace, size_t workspace_bytes, void* out_bf16,
+                                         float* out_f32, void* k_rebuilt, void* v_rebuilt, int64_t rebuilt_S, void* stream);
 
 #ifdef __cplusplus
 }

@@ -244,13 +244,17 @@ def f32_to_bf16(x: np.ndarray) -> np.ndarray:
     return r.astype(np.uint16)
 
 
-def attention_ref(q16: np.ndarray, k16: np.ndarray, v16: np.ndarray, scale: float) -> np.ndarray:
+def attention_ref(q16: np.ndarray, k16: np.ndarray, v16: np.ndarray, scale: float, with_abs: bool = False):
     """q16 [n_q, D], k16/v16 [L, n_kv, D] uint16 -> [n_q, D] float64.  GQA: q head j uses kv head j // G
-    (tests/common.py:15-22, computed in float64 here).  L == 0 gives zeros (gaac/kernel.py:293)."""
+    (tests/common.py:15-22, computed in float64 here).  L == 0 gives zeros (gaac/kernel.py:293).
+    with_abs=True returns (out, out_abs) with out_abs = sum_i p_i |v_i|, the magnitude that a relative error of the softmax
+    weights is multiplied by: the kernels round the weights to BF16 before the PV product (gaac/kernel.py:178), a relative
+    error of at most 2^-9 per weight, so |result - out| <= 2^-9 * out_abs plus fp32 accumulation noise."""
     n_q, n_kv = q16.shape[0], k16.shape[1]
     G = n_q // n_kv
     if k16.shape[0] == 0:
-        return np.zeros((n_q, D))
+        z = np.zeros((n_q, D))
+        return (z, z.copy()) if with_abs else z
     q = bf16_to_f64(q16)
     k = np.repeat(bf16_to_f64(k16), G, axis=1).transpose(1, 0, 2)      # [n_q, L, D]
     v = np.repeat(bf16_to_f64(v16), G, axis=1).transpose(1, 0, 2)
@@ -258,7 +262,19 @@ def attention_ref(q16: np.ndarray, k16: np.ndarray, v16: np.ndarray, scale: floa
     s = s - s.max(-1, keepdims=True)
     p = np.exp(s)
     p /= p.sum(-1, keepdims=True)
-    return np.einsum("hl,hld->hd", p, v)
+    out = np.einsum("hl,hld->hd", p, v)
+    if with_abs:
+        return out, np.einsum("hl,hld->hd", p, np.abs(v))
+    return out
+
+
+ATTN_TOL = 2e-3        # max-abs bound on the fp32 attention result at unit scale
+
+
+def attention_bound(out_abs: np.ndarray) -> np.ndarray:
+    """Per-element bound on |fp32 result - float64 reference|: 2e-3 where the weighted magnitude sum_i p_i |v_i| is at most 1,
+    2e-3 times that magnitude where it is larger (values far above unit scale carry the weights' BF16 rounding with them)."""
+    return ATTN_TOL * np.maximum(1.0, out_abs)
 
 
 def combine_partials(pm: np.ndarray, pl: np.ndarray, pa: np.ndarray) -> np.ndarray:

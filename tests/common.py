@@ -40,9 +40,13 @@ def assert_pages_equal(got: dict, ref: dict):
     assert got["ovf"].size == n + 8
 
 
-def attn_tol(ref: np.ndarray, v16: np.ndarray) -> float:
-    """Bound on |fp32 result - fp64 reference|: 2e-3 max-abs at unit scale.  The kernel rounds the softmax weights to BF16
-    before the PV product (as the reference kernel does, gaac/kernel.py:178), a relative error of 2^-9 = 1.95e-3 per weight,
-    so the bound scales with the largest |v| attended over when that exceeds 1."""
-    vmax = float(np.abs((v16.astype(np.uint32) << 16).view(np.float32)).max()) if v16.size else 0.0
-    return 2e-3 * max(1.0, float(np.abs(ref).max()), vmax)
+def assert_attention_close(o32: np.ndarray, q16: np.ndarray, k16: np.ndarray, v16: np.ndarray, scale: float, what=""):
+    """fp32 attention result against the float64 oracle, element by element: |o32 - ref| <= 2e-3 * max(1, sum_i p_i |v_i|)
+    (oracle.attention_bound).  q16 [n_q, D], k16 / v16 [L, n_kv, D] BF16 bit patterns.  Returns (ref, worst error / bound)."""
+    from oracle import gaac_oracle as O
+    ref, ref_abs = O.attention_ref(q16, k16, v16, scale, with_abs=True)
+    err = np.abs(np.asarray(o32, dtype=np.float64) - ref)
+    bound = O.attention_bound(ref_abs)
+    worst = float((err / bound).max()) if err.size else 0.0
+    assert worst <= 1.0, (what, "max |err| / bound", worst, "max |err|", float(err.max()))
+    return ref, worst

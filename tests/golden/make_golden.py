@@ -2,7 +2,7 @@
 
 Usage (needs the reference checkout; the fixtures themselves are committed, so tests never need it):
 
-    TRITON_INTERPRET=1 python tests/golden/make_golden.py /path/to/GAAC
+    TRITON_INTERPRET=1 python tests/golden/make_golden.py /path/to/GAAC [--only-tables]
 
 What runs: the reference torch codec (gaac/codec.py) on CPU tensors, and the reference Triton kernels
 (gaac/encoder.py, gaac/kv_cache.py, gaac/vllm/store.py) under the Triton interpreter, on small seeded inputs.
@@ -43,6 +43,41 @@ def page_fields(pg):
     n = int(pg.ovf_head_start[-1])
     return dict(sm=pg.sm.numpy(), codes=pg.codes.numpy(), flags=pg.flags.numpy(), ovf_off=pg.ovf_off.numpy(),
                 ovf=pg.ovf[:n].numpy(), ovf_head_start=pg.ovf_head_start.numpy(), tile_off=pg.tile_off.numpy())
+
+
+def tables_and_calibration(ref_root: str):
+    """tables.npz: the reference's index tables (gaac/codec.py:29-67, gaac/encoder.py:84-88), row_offsets on a tag-word sample,
+    and a calibration case with its input: exponent histogram, bases, BaseCollector over two steps."""
+    sys.path.insert(0, ref_root)
+    from gaac import TileEncoder, BaseCollector
+    from gaac.codec import perm_k, perm_v, perm, storage_index, exponent_hist, bases_from_hist, row_offsets
+    out = {"perm_k": perm_k().numpy(), "perm_v": perm_v().numpy()}
+    for kind in "kv":
+        si, ci = storage_index(kind, "cpu")
+        out[f"storage_sm_{kind}"], out[f"storage_cd_{kind}"] = si.numpy(), ci.numpy()
+        te = TileEncoder(kind, device="cpu")
+        out[f"enc_perm_{kind}"], out[f"enc_inv_sm_{kind}"], out[f"enc_inv_cd_{kind}"] = te.perm.numpy(), te.inv_sm.numpy(), te.inv_cd.numpy()
+        assert torch.equal(perm(kind), perm_k() if kind == "k" else perm_v())
+    g = torch.Generator(device="cpu").manual_seed(11)
+    tag = torch.tensor([0, 1, 3], dtype=torch.int64)[torch.randint(0, 3, (3, 48, 16), generator=g)]
+    flags = (tag << (2 * torch.arange(16))).sum(-1)
+    flags = torch.where(flags >= 2 ** 31, flags - 2 ** 32, flags).to(torch.int32)
+    out["ro_flags"], out["ro_offsets"] = flags.numpy(), row_offsets(flags, 41).numpy()
+    n_kv = 2
+    x = kv_like(4, 300, seed=5)                                          # [H, T, D], head h -> kv head h % n_kv
+    xt = x.reshape(2, n_kv, -1, 128).permute(0, 2, 1, 3).contiguous()    # token-major [., T, n_kv, D]
+    hist = exponent_hist(xt, n_kv)
+    b3, b4 = bases_from_hist(hist, n_kv)
+    out["cal_x"], out["cal_hist"], out["cal_base3"], out["cal_base4"] = u16(x), hist.numpy(), b3.numpy(), b4.numpy()
+    col = BaseCollector()
+    k1, v1, k2, v2 = (kv_like(n_kv, 200, seed=s).transpose(0, 1).contiguous() for s in (6, 7, 8, 9))      # [N, n_kv, D]
+    col.observe(0, k1, v1); col.observe(0, k2, v2); col.observe(3, k2, v1)
+    bases = col.bases()
+    for i, t in enumerate((k1, v1, k2, v2)): out[f"col_in_{i}"] = u16(t)
+    for layer in (0, 3):
+        for name in ("k3", "k4", "v3", "v4"): out[f"col_{layer}_{name}"] = bases[layer][name].numpy()
+    np.savez_compressed(os.path.join(HERE, "tables.npz"), **out)
+    print("tables.npz written to", HERE)
 
 
 def main(ref_root: str):
@@ -187,4 +222,8 @@ def main(ref_root: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("GAAC_REFERENCE", ""))
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    root = args[0] if args else os.environ.get("GAAC_REFERENCE", "")
+    if "--only-tables" not in sys.argv:
+        main(root)
+    tables_and_calibration(root)

@@ -117,6 +117,31 @@ def test_base_collector_matches_oracle(tmp_path):
     assert set(torch.load(str(tmp_path / "bases.pt"))[0]) == {"k3", "k4", "v3", "v4"}
 
 
+def test_calibration_and_collector_match_reference_fixture():
+    """Histogram kernel, window search and BaseCollector against outputs of the reference's exponent_hist / bases_from_hist /
+    BaseCollector (tests/golden/tables.npz)."""
+    import torch
+    from gaac_b200 import BaseCollector, Codec
+    from gaac_b200.codec import exponent_hist, bases_from_hist
+    g = golden("tables")
+    x = to_bf16_cuda(g["cal_x"])
+    xt = x.reshape(2, 2, -1, 128).permute(0, 2, 1, 3).contiguous()
+    hist = exponent_hist(xt, 2)
+    assert hist.dtype == torch.int64 and np.array_equal(hist.cpu().numpy(), g["cal_hist"])
+    b3, b4 = bases_from_hist(hist, 2)
+    assert np.array_equal(b3.cpu().numpy(), g["cal_base3"]) and np.array_equal(b4.cpu().numpy(), g["cal_base4"])
+    c = Codec(2).calibrate(x)
+    assert np.array_equal(c.base3.cpu().numpy(), g["cal_base3"]) and np.array_equal(c.base4.cpu().numpy(), g["cal_base4"])
+    k1, v1, k2, v2 = (to_bf16_cuda(g[f"col_in_{i}"]) for i in range(4))
+    col = BaseCollector()
+    col.observe(0, k1, v1); col.observe(0, k2, v2); col.observe(3, k2, v1)
+    got = col.bases()
+    assert sorted(got) == [0, 3]
+    for layer in (0, 3):
+        for name in ("k3", "k4", "v3", "v4"):
+            assert np.array_equal(got[layer][name].numpy(), g[f"col_{layer}_{name}"]), (layer, name)
+
+
 def test_full_size_roundtrip_property():
     """[8, 65536, 128] per kind: round trip bit-exact on the GPU, ratio and tier shares against the oracle on a 4096-token slice."""
     import torch

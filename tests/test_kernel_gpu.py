@@ -1,7 +1,7 @@
 """Fused decode attention against the fp64 oracle (cases of the reference's tests/test_kernel.py:6-19 and more)."""
 import numpy as np
 import pytest
-from common import golden, to_bf16_cuda, bits, attn_tol
+from common import golden, to_bf16_cuda, bits, assert_attention_close
 from oracle import gaac_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -20,10 +20,8 @@ def _check(out, out32, q16, k16, v16, B, n_kv, scale):
     o16, o32 = bits(out), out32.cpu().numpy()
     for b in range(B):
         kb = k16[b * n_kv:(b + 1) * n_kv].transpose(1, 0, 2); vb = v16[b * n_kv:(b + 1) * n_kv].transpose(1, 0, 2)
-        ref = O.attention_ref(q16[b], kb, vb, scale)
+        ref, _ = assert_attention_close(o32[b], q16[b], kb, vb, scale, b)          # fp32 result: 2e-3 x max(1, sum p|v|) per element
         mag = np.abs(ref).max()
-        err32 = np.abs(o32[b] - ref).max()
-        assert err32 <= attn_tol(ref, vb), (b, err32, mag)                        # fp32 result: 2e-3 max-abs at unit scale
         assert np.array_equal(o16[b], O.f32_to_bf16(o32[b]))                      # the bf16 output is the rounded fp32 result
         err16 = np.abs(O.bf16_to_f64(o16[b]) - ref).max()
         assert err16 <= 2e-2 * mag + 1e-3, (b, err16, mag)                        # the reference's own bound
@@ -57,8 +55,9 @@ def test_attention_matches_reference_fixture(tag):
     kp, vp = _pages(kh, vh, n_kv)
     o32 = torch.empty(1, n_kv * G, 128, dtype=torch.float32, device="cuda")
     out = attention(to_bf16_cuda(q16[None]), kp, vp, SCALE, out_f32=o32)
-    ref = g[f"o_{tag}"]
-    assert np.abs(o32[0].cpu().numpy() - ref).max() <= attn_tol(ref, v16)
+    ref = g[f"o_{tag}"]                                                    # fp32 output of the reference's own formula
+    oref, _ = assert_attention_close(o32[0].cpu().numpy(), q16, k16, v16, SCALE, tag)
+    assert np.abs(oref - ref).max() <= 1e-4 * max(1.0, np.abs(ref).max())    # the oracle agrees with the reference's formula
     assert np.abs(out[0].float().cpu().numpy() - ref).max() <= 2e-2 * np.abs(ref).max() + 1e-3
 
 
@@ -76,8 +75,7 @@ def test_attention_long_escape_tiles_and_default_scale():
     q16 = O.f32_to_bf16((rng.standard_normal((1, 8, 128)) * 0.05).astype(np.float32))
     o32 = torch.empty(1, 8, 128, dtype=torch.float32, device="cuda")
     out = attention(to_bf16_cuda(q16), kp, vp, out_f32=o32)
-    ref = O.attention_ref(q16[0], k16.transpose(1, 0, 2), v16.transpose(1, 0, 2), SCALE)
-    assert np.abs(o32[0].cpu().numpy() - ref).max() <= attn_tol(ref, v16)
+    assert_attention_close(o32[0].cpu().numpy(), q16[0], k16.transpose(1, 0, 2), v16.transpose(1, 0, 2), SCALE)
     assert np.isfinite(out.float().cpu().numpy()).all()
 
 
@@ -120,8 +118,7 @@ def test_partial_mode_equals_full_attention():
     allp = torch.stack(parts, 1)                                   # [n_q, 2, 130]
     o32 = torch.empty(n_kv * G, 128, dtype=torch.float32, device="cuda")
     combine(allp[:, :, 0].contiguous(), allp[:, :, 1].contiguous(), allp[:, :, 2:].contiguous(), out_f32=o32)
-    ref = O.attention_ref(q16[0], k16.transpose(1, 0, 2), v16.transpose(1, 0, 2), SCALE)
-    assert np.abs(o32.cpu().numpy() - ref).max() <= attn_tol(ref, v16)
+    assert_attention_close(o32.cpu().numpy(), q16[0], k16.transpose(1, 0, 2), v16.transpose(1, 0, 2), SCALE)
     # the packed form (what an all-gather of the ranks' partials holds) merges to the same values in one launch
     from gaac_b200.kernel import combine_parts
     o32b = torch.empty_like(o32)
@@ -142,47 +139,73 @@ def _half_pages(n_kv, S, seed):
 
 
 def test_peer_exchange_two_ranks_on_one_gpu():
-    """Fused exchange (gaac_decode_attn_push + gaac_exchange_merge) with both ranks' buffers on one GPU: every push is launched
-    before any merge, so no kernel ever waits for another launch.  Three exchanges in a row use both buffer parities."""
+    """Cross-GPU exchange with both ranks' buffers on one GPU, run in stream order so that no launch ever waits for a later
+    one: rank 0 pushes only, rank 1 runs the fused launch (push, wait, merge: rank 0's rows are there already), then rank 0
+    merges with the separate kernel.  Four exchanges in a row use both buffer parities; the third one goes through the slot-map
+    entry points instead of the Pages entry, and the (row, kv head) group count changes for the last."""
     import torch
-    from gaac_b200.kernel import _ext
+    from gaac_b200.kernel import _ext, _pages_call
     from gaac_b200.dist import PeerExchange
     n_kv, G, S = 2, 4, 2048
     n_q = n_kv * G
     k16, v16, halves = _half_pages(n_kv, S, 3)
-    bufs = [PeerExchange.local_buffer(2, n_q, "cuda") for _ in range(2)]
-    xs = [PeerExchange.local(bufs, r, n_q) for r in range(2)]
+    k16b, v16b, halves_b = _half_pages(1, 512, 4)                               # a second cache with one kv head: one flag group
+    bufs = [PeerExchange.local_buffer(2, n_q, "cuda", groups=n_kv) for _ in range(2)]
+    xs = [PeerExchange.local(bufs, r, n_q, groups=n_kv) for r in range(2)]
     slots = torch.zeros(1, dtype=torch.int32, device="cuda")
     e = torch.empty(0, dtype=torch.int32, device="cuda"); eq = torch.empty(0, dtype=torch.bfloat16, device="cuda")
     rng = np.random.default_rng(5)
-    for step in range(3):
-        q16 = O.f32_to_bf16(rng.standard_normal((1, n_q, 128)).astype(np.float32))
+    for step in range(4):
+        hv, kk, vv, nkv = (halves, k16, v16, n_kv) if step < 3 else (halves_b, k16b, v16b, 1)
+        nq = nkv * G
+        q16 = O.f32_to_bf16(rng.standard_normal((1, nq, 128)).astype(np.float32))
         q = to_bf16_cuda(q16)
-        for r, (kp, vp, n) in enumerate(halves):
-            SL = torch.full((n_kv,), n, dtype=torch.int32, device="cuda")
-            _ext().gaac_attn_launch(kp.sm, kp.codes, kp.flags, kp.tile_off, kp.ovf, kp.ovf_head_start, kp.base3, kp.base4,
-                                    vp.sm, vp.codes, vp.flags, vp.tile_off, vp.ovf, vp.ovf_head_start, vp.base3, vp.base4,
-                                    q.reshape(-1, 128), slots, n_q, n_kv, SL, n, SCALE, 4, eq, eq, e, 0, exchange=xs[r].x)
-        o32 = [torch.empty(n_q, 128, dtype=torch.float32, device="cuda") for _ in range(2)]
-        outs = [xs[r].merge(n_kv, out_f32=o32[r]) for r in range(2)]
-        ref = O.attention_ref(q16[0], k16.transpose(1, 0, 2), v16.transpose(1, 0, 2), SCALE)
+        o32 = [torch.empty(nq, 128, dtype=torch.float32, device="cuda") for _ in range(2)]
+        outs = [None, None]
+        for r, (kp, vp, n) in enumerate(hv):
+            if step == 2:
+                SL = torch.full((nkv,), n, dtype=torch.int32, device="cuda")
+                outs[r] = _ext().gaac_attn_launch(kp.sm, kp.codes, kp.flags, kp.tile_off, kp.ovf, kp.ovf_head_start, kp.base3, kp.base4,
+                                                  vp.sm, vp.codes, vp.flags, vp.tile_off, vp.ovf, vp.ovf_head_start, vp.base3, vp.base4,
+                                                  q.reshape(-1, 128), slots, nq, nkv, SL, n, SCALE, 4, eq, eq, e, 0, exchange=xs[r].x, fused=(r == 1),
+                                                  out_f32=o32[r] if r == 1 else None)
+            elif r == 0:
+                _pages_call(q, kp, vp, 1, nq, nkv, SCALE, 4, exchange=xs[0].x)
+            else:
+                outs[1] = torch.empty(nq, 128, dtype=torch.bfloat16, device="cuda")
+                _pages_call(q, kp, vp, 1, nq, nkv, SCALE, 4, out=outs[1], out_f32=o32[1], exchange=xs[1].x, fused=True)
+        outs[0] = xs[0].merge(nkv, out_f32=o32[0], n_heads=nq)
         for r in range(2):
-            assert np.abs(o32[r].cpu().numpy() - ref).max() <= attn_tol(ref, v16)
+            assert_attention_close(o32[r].cpu().numpy(), q16[0], kk.transpose(1, 0, 2), vv.transpose(1, 0, 2), SCALE, (step, r))
             assert not xs[r].error()
-        assert torch.equal(o32[0], o32[1]) and torch.equal(outs[0], outs[1])
+        assert torch.equal(o32[0], o32[1]) and torch.equal(outs[0].view(-1), outs[1].view(-1))
+    assert int(xs[0]._state[0]) == 4 and int(xs[1]._state[0]) == 4               # both ranks counted four exchanges
 
 
 def test_peer_exchange_wait_runs_out():
-    """A merge whose peers never push gives up after its bounded wait: error flag set, output zero, GPU still usable."""
+    """A merge whose peers never push gives up after its bounded wait: error flag set, output zero, GPU still usable; and the
+    exchange after it works again (flags carry the exchange number, so a lost exchange does not shift the later ones)."""
     import torch
+    from gaac_b200.kernel import _pages_call
     from gaac_b200.dist import PeerExchange
-    n_q = 8
-    bufs = [PeerExchange.local_buffer(2, n_q, "cuda") for _ in range(2)]
-    x = PeerExchange.local(bufs, 0, n_q)
-    out = x.merge(2)
-    assert x.error()
+    n_kv, G = 2, 4
+    n_q = n_kv * G
+    k16, v16, halves = _half_pages(n_kv, 512, 6)
+    bufs = [PeerExchange.local_buffer(2, n_q, "cuda", groups=n_kv) for _ in range(2)]
+    xs = [PeerExchange.local(bufs, r, n_q, groups=n_kv) for r in range(2)]
+    out = xs[0].merge(n_kv)                                                     # nobody pushed: exchange 1 is lost on rank 0
+    assert xs[0].error()
     assert (out == 0).all()
     assert float(torch.ones(4, device="cuda").sum()) == 4.0
+    xs[1]._state[0] = 1                                                         # rank 1 gave up on exchange 1 as well
+    q16 = O.f32_to_bf16(np.random.default_rng(8).standard_normal((1, n_q, 128)).astype(np.float32))
+    q = to_bf16_cuda(q16)
+    _pages_call(q, halves[0][0], halves[0][1], 1, n_q, n_kv, SCALE, 2, exchange=xs[0].x)
+    o32 = torch.empty(n_q, 128, dtype=torch.float32, device="cuda")
+    _pages_call(q, halves[1][0], halves[1][1], 1, n_q, n_kv, SCALE, 2, out=torch.empty(n_q, 128, dtype=torch.bfloat16, device="cuda"), out_f32=o32,
+                exchange=xs[1].x, fused=True)
+    assert_attention_close(o32.cpu().numpy(), q16[0], k16.transpose(1, 0, 2), v16.transpose(1, 0, 2), SCALE)
+    assert not xs[1].error()
 
 
 def test_copy_wait_error_word_stays_clear():
@@ -203,27 +226,61 @@ def test_copy_wait_error_word_stays_clear():
     assert not workspace_error(q.device, 1, n_kv * G)
 
 
-@pytest.mark.parametrize("S", [65536, 131072])
-def test_attention_full_size_contexts(S):
-    """BASELINE config 1 (65536 tokens) and config 3 (131072 tokens) shapes: 32 query / 8 kv heads, synthetic KV of the benchmark
-    generator, default split count.  The codec is lossless, so the fp64 reference is computed on the GPU from the original BF16
-    tensors; the split merge is also checked against a single-split run (same result within the same tolerance)."""
+def _fp64_attention_on_gpu(q, k, v, n_kv, G, scale):
+    """(reference, sum_i p_i |v_i|) in float64 on the GPU: q [n_kv*G, 128], k / v [n_kv, L, 128] bf16."""
+    import torch
+    qd = q.double().view(n_kv, G, 128)
+    s = torch.einsum("hgd,htd->hgt", qd, k.double()) * scale
+    p = torch.softmax(s, -1)
+    vd = v.double()
+    return torch.einsum("hgt,htd->hgd", p, vd).reshape(n_kv * G, 128), torch.einsum("hgt,htd->hgd", p, vd.abs()).reshape(n_kv * G, 128)
+
+
+@pytest.mark.parametrize("S", [2048, 65536, 131072])
+@pytest.mark.parametrize("outliers", [False, True])
+def test_attention_full_size_contexts(S, outliers):
+    """32 query / 8 kv heads over 2048, 65536 and 131072 tokens of the benchmark generator, default split count.  The codec is
+    lossless, so the float64 reference is computed on the GPU from the original BF16 tensors.  Without the generator's forced
+    outliers (no element multiplied by 2^4 or 2^7) the fp32 result is held to a plain 2e-3 max-abs; with them to
+    2e-3 * max(1, sum_i p_i |v_i|) per element.  A single-split run must meet the same bound (split merge)."""
     import torch
     from gaac_b200 import attention, Codec, TileEncoder
     from gaac_b200.synth import synth_kv
     n_kv, G = 8, 4
-    k, v = synth_kv("k", n_kv, S, 41, "cuda"), synth_kv("v", n_kv, S, 41, "cuda")
+    fr = dict(raw_frac=0.002, four_frac=0.10) if outliers else dict(raw_frac=0.0, four_frac=0.0)
+    k, v = synth_kv("k", n_kv, S, 41, "cuda", **fr), synth_kv("v", n_kv, S, 41, "cuda", **fr)
     ck, cv = Codec(n_kv).calibrate(k[:, :2048]), Codec(n_kv).calibrate(v[:, :2048])
     kp, vp = TileEncoder("k").encode(ck, k), TileEncoder("v").encode(cv, v)
     q = torch.randn(1, n_kv * G, 128, generator=torch.Generator(device="cuda").manual_seed(5), device="cuda").to(torch.bfloat16)
     o32 = torch.empty(1, n_kv * G, 128, dtype=torch.float32, device="cuda")
     out = attention(q, kp, vp, SCALE, out_f32=o32)
-    qd = q[0].double().view(n_kv, G, 128)
-    s = torch.einsum("hgd,htd->hgt", qd, k.double()) * SCALE
-    ref = torch.einsum("hgt,htd->hgd", torch.softmax(s, -1), v.double()).reshape(n_kv * G, 128)
-    tol = 2e-3 * max(1.0, float(ref.abs().max()), float(v.float().abs().max()))
-    assert float((o32[0].double() - ref).abs().max()) <= tol
+    ref, ref_abs = _fp64_attention_on_gpu(q[0], k, v, n_kv, G, SCALE)
+    bound = 2e-3 * torch.clamp(ref_abs, min=1.0)
+    err = (o32[0].double() - ref).abs()
+    assert bool((err <= bound).all()), float((err / bound).max())
+    if not outliers:
+        assert float(err.max()) <= 2e-3, float(err.max())
     assert torch.equal(out[0], o32[0].to(torch.bfloat16))
     o1 = torch.empty_like(o32)
     attention(q, kp, vp, SCALE, nsplit=1, out_f32=o1)
-    assert float((o1[0].double() - ref).abs().max()) <= tol
+    err1 = (o1[0].double() - ref).abs()
+    assert bool((err1 <= bound).all()) and (outliers or float(err1.max()) <= 2e-3)
+
+
+def test_workspace_is_shared_by_calls_of_different_shapes():
+    """One stream, one cached workspace: a small call (1 row, 32 query heads, 8 splits) leaves its partials behind, then a call
+    with more (row, kv head) groups than the first one had counters runs on the same buffer.  The header of the workspace has a
+    fixed size, so the second call's counters never sit on the first call's partials."""
+    import torch
+    from gaac_b200 import attention, Codec, TileEncoder
+    from gaac_b200.kernel import workspace_error
+    rng = np.random.default_rng(12)
+    for B, n_kv, G, S, nsplit in ((1, 8, 4, 2048, 8), (16, 8, 1, 256, 2), (1, 8, 4, 2048, 3), (3, 2, 8, 700, 5)):
+        k16, v16 = O.synth_kv("k", B * n_kv, S, 50 + B), O.synth_kv("v", B * n_kv, S, 50 + B)
+        k, v = to_bf16_cuda(k16), to_bf16_cuda(v16)
+        kp, vp = TileEncoder("k").encode(Codec(n_kv).calibrate(k), k), TileEncoder("v").encode(Codec(n_kv).calibrate(v), v)
+        q16 = O.f32_to_bf16(rng.standard_normal((B, n_kv * G, 128)).astype(np.float32))
+        o32 = torch.full((B, n_kv * G, 128), float("nan"), dtype=torch.float32, device="cuda")
+        out = attention(to_bf16_cuda(q16), kp, vp, SCALE, nsplit=nsplit, out_f32=o32)
+        _check(out, o32, q16, k16, v16, B, n_kv, SCALE)
+    assert not workspace_error("cuda")

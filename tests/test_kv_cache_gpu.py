@@ -2,7 +2,7 @@
 parity with the fixtures produced by the reference.  Cases follow the reference's tests/test_kv_cache.py:32-86."""
 import numpy as np
 import pytest
-from common import golden, sha, to_bf16_cuda, bits, attn_tol
+from common import golden, sha, to_bf16_cuda, bits, assert_attention_close
 from oracle import gaac_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -30,8 +30,7 @@ def _check(cache, hist, slots_l, q16):
             assert out[b].abs().max().item() == 0
             continue
         k, v = hist[s]
-        ref = O.attention_ref(q16[b], k, v, SCALE)
-        assert np.abs(o32[b].cpu().numpy() - ref).max() <= attn_tol(ref, v)
+        ref, _ = assert_attention_close(o32[b].cpu().numpy(), q16[b], k, v, SCALE, (b, s))
         assert np.abs(out[b].float().cpu().numpy() - ref).max() <= 2e-2 * np.abs(ref).max() + 1e-3
         dk, dv = cache.decompress(s)
         assert np.array_equal(bits(dk), k) and np.array_equal(bits(dv), v)

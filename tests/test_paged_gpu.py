@@ -2,7 +2,7 @@
 Triton kernels, and the fused paged attention against the fp64 oracle (the reference has no tests for this layout)."""
 import numpy as np
 import pytest
-from common import golden, sha, to_bf16_cuda, bits, attn_tol
+from common import golden, sha, to_bf16_cuda, bits, assert_attention_close
 from oracle import gaac_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -59,13 +59,14 @@ def test_raw_pool_exhaustion_counts_errors():
     assert int(st.err) == 1 and int(st.top) == -1
 
 
-def _build_paged(seq_lens, n_kv, num_blocks, seed, adversarial_every=0):
-    """Store sequences of the given lengths through the paged store (whole prompt at once) -> (state, buf, bt, k16s, v16s)."""
+def _build_paged(seq_lens, n_kv, num_blocks, seed, adversarial_every=0, ovf_slot=128, **gen):
+    """Store sequences of the given lengths through the paged store (whole prompt at once) -> (state, buf, bt, k16s, v16s).
+    gen: raw_frac / four_frac of the synthetic generator."""
     import torch
     from gaac_b200.vllm.store import LayerState, OVF_OFF
     rng = np.random.default_rng(seed)
-    ovf_slot = 128; TS = OVF_OFF + ovf_slot
-    cal_k, cal_v = O.synth_kv("k", n_kv, 2048, seed), O.synth_kv("v", n_kv, 2048, seed)
+    TS = OVF_OFF + ovf_slot
+    cal_k, cal_v = O.synth_kv("k", n_kv, 2048, seed, **gen), O.synth_kv("v", n_kv, 2048, seed, **gen)
     k3, k4 = O.calibrate(cal_k, n_kv); v3, v4 = O.calibrate(cal_v, n_kv)
     bases = {n: torch.from_numpy(a) for n, a in (("k3", k3), ("k4", k4), ("v3", v3), ("v4", v4))}
     st = LayerState(num_blocks, n_kv, raw_tiles=len(seq_lens) * 2 * n_kv + 64, bases=bases, ovf_slot=ovf_slot, device="cuda")
@@ -76,7 +77,7 @@ def _build_paged(seq_lens, n_kv, num_blocks, seed, adversarial_every=0):
     ks, vs, used = [], [], 0
     for i, L in enumerate(seq_lens):
         # same generator, same per-channel scales as the calibration sample (seed selects the scales)
-        k16 = O.synth_kv("k", n_kv, 2048 + L, seed)[:, 2048:]; v16 = O.synth_kv("v", n_kv, 2048 + L, seed)[:, 2048:]
+        k16 = O.synth_kv("k", n_kv, 2048 + L, seed, **gen)[:, 2048:]; v16 = O.synth_kv("v", n_kv, 2048 + L, seed, **gen)[:, 2048:]
         k16 = np.ascontiguousarray(np.roll(k16, i * 7, axis=1)); v16 = np.ascontiguousarray(np.roll(v16, i * 11, axis=1))
         nb = (L + 15) // 16
         blocks = perm[used:used + nb]; used += nb
@@ -110,9 +111,8 @@ def test_paged_attention_matches_oracle(n_kv, G, adv):
         o32 = torch.empty(B, n_q, 128, dtype=torch.float32, device="cuda")
         paged_attention(to_bf16_cuda(q16), out, buf, st.raw, st.mt, bt, sl, st.bases, st.TS, n_q, n_kv, nsplit, out_f32=o32)
         for b in range(B):
-            ref = O.attention_ref(q16[b], ks[b], vs[b], 128 ** -0.5)
+            ref, _ = assert_attention_close(o32[b].cpu().numpy(), q16[b], ks[b], vs[b], 128 ** -0.5, (b, nsplit))
             mag = np.abs(ref).max()
-            assert np.abs(o32[b].cpu().numpy() - ref).max() <= attn_tol(ref, vs[b]), (b, nsplit)
             assert np.abs(out[b].view(n_q, 128).float().cpu().numpy() - ref).max() <= 2e-2 * mag + 1e-3
 
 
@@ -146,8 +146,7 @@ def test_paged_incremental_decode_steps():
         o32 = torch.empty(3, n_kv * G, 128, dtype=torch.float32, device="cuda")
         paged_attention(to_bf16_cuda(q16), out, buf, st.raw, st.mt, bt, torch.tensor(lens, dtype=torch.int32, device="cuda"), st.bases, st.TS, n_kv * G, n_kv, 2, out_f32=o32)
         for b in range(3):
-            ref = O.attention_ref(q16[b], ks[b], vs[b], 128 ** -0.5)
-            assert np.abs(o32[b].cpu().numpy() - ref).max() <= attn_tol(ref, vs[b]), (step, b)
+            assert_attention_close(o32[b].cpu().numpy(), q16[b], ks[b], vs[b], 128 ** -0.5, (step, b))
     assert int(st.err) == 0
     # raw tiles in use = one per (sequence, kv head, kind) with a filling block
     filling = sum(1 for L in lens if L % 16)

@@ -8,31 +8,34 @@ first failure has already run everything else."""
 import ctypes as C
 import numpy as np
 import pytest
-from common import to_bf16_cuda, attn_tol
+from common import to_bf16_cuda, assert_attention_close
 from oracle import gaac_oracle as O
 
 pytestmark = pytest.mark.gpu
 
 
+def _side(p, _lib):
+    return _lib.Side(p.sm.data_ptr(), p.codes.data_ptr(), p.flags.data_ptr(), p.tile_off.data_ptr(), p.ovf.data_ptr(),
+                     p.ovf_head_start.data_ptr(), p.ovf.numel(), p.base3.data_ptr(), p.base4.data_ptr(), None)
+
+
 def test_static_workspace_entry_matches_regular_entry_twice():
+    """Two calls in a row at one shape, then a third with more rows, kv heads and query heads on the same array."""
     import torch
     from gaac_b200 import Codec, TileEncoder, _lib
     L = _lib.lib()
-    assert hasattr(L, "gaac_decode_attn_static"), "library built without the allocation-free entry point"
     cap = L.gaac_static_workspace_bytes()
     assert cap == 8 << 20
-    B, n_kv, G, S, nsplit = 2, 2, 4, 1000, 5
-    n_q = n_kv * G
-    k16, v16 = O.synth_kv("k", B * n_kv, S, 11), O.synth_kv("v", B * n_kv, S, 11)
-    k, v = to_bf16_cuda(k16), to_bf16_cuda(v16)
-    kp = TileEncoder("k").encode(Codec(n_kv).calibrate(k), k); vp = TileEncoder("v").encode(Codec(n_kv).calibrate(v), v)
-    side = lambda p: _lib.Side(p.sm.data_ptr(), p.codes.data_ptr(), p.flags.data_ptr(), p.tile_off.data_ptr(), p.ovf.data_ptr(),
-                               p.ovf_head_start.data_ptr(), p.ovf.numel(), p.base3.data_ptr(), p.base4.data_ptr(), None)
-    K, V = side(kp), side(vp)
-    slots = torch.arange(B, dtype=torch.int32, device="cuda"); SL = torch.full((B * n_kv,), S, dtype=torch.int32, device="cuda")
     stream = torch.cuda.current_stream().cuda_stream
     rng = np.random.default_rng(0)
-    for call in range(2):
+    for call, (B, n_kv, G, S, nsplit) in enumerate(((2, 2, 4, 1000, 5), (2, 2, 4, 1000, 5), (5, 4, 8, 333, 3))):
+        n_q = n_kv * G
+        assert L.gaac_attn_workspace_bytes(B, n_q, nsplit) <= cap
+        k16, v16 = O.synth_kv("k", B * n_kv, S, 11), O.synth_kv("v", B * n_kv, S, 11)
+        k, v = to_bf16_cuda(k16), to_bf16_cuda(v16)
+        kp = TileEncoder("k").encode(Codec(n_kv).calibrate(k), k); vp = TileEncoder("v").encode(Codec(n_kv).calibrate(v), v)
+        K, V = _side(kp, _lib), _side(vp, _lib)
+        slots = torch.arange(B, dtype=torch.int32, device="cuda"); SL = torch.full((B * n_kv,), S, dtype=torch.int32, device="cuda")
         q16 = O.f32_to_bf16((rng.standard_normal((B, n_q, 128)) * (0.3 + call)).astype(np.float32))
         q = to_bf16_cuda(q16)
         out_s = torch.empty(B, n_q, 128, dtype=torch.bfloat16, device="cuda"); f32_s = torch.empty(B, n_q, 128, dtype=torch.float32, device="cuda")
@@ -47,11 +50,13 @@ def test_static_workspace_entry_matches_regular_entry_twice():
         torch.cuda.synchronize()
         for b in range(B):
             kb = k16[b * n_kv:(b + 1) * n_kv].transpose(1, 0, 2); vb = v16[b * n_kv:(b + 1) * n_kv].transpose(1, 0, 2)
-            ref = O.attention_ref(q16[b], kb, vb, 128 ** -0.5)
-            tol = attn_tol(ref, vb)
-            assert np.abs(f32_s[b].cpu().numpy() - f32_r[b].cpu().numpy()).max() <= tol, call
-            assert np.abs(f32_s[b].cpu().numpy() - ref).max() <= tol, call
+            ref, _ = assert_attention_close(f32_s[b].cpu().numpy(), q16[b], kb, vb, 128 ** -0.5, call)
+            # the two entry points run the same kernel; tiles reach the warps in a different order from run to run, so the
+            # results agree to fp32 accumulation noise, far inside the tolerance of the tests
+            assert np.abs(f32_s[b].cpu().numpy() - f32_r[b].cpu().numpy()).max() <= 1e-4 * max(1.0, np.abs(ref).max()), call
             assert np.abs(out_s[b].float().cpu().numpy() - out_r[b].float().cpu().numpy()).max() <= 2e-2 * np.abs(ref).max() + 1e-3, call
+    err = C.c_int32(-1)
+    assert L.gaac_static_workspace_error(C.byref(err), 0, stream) == 0 and err.value == 0      # no bounded wait ran out
 
 
 def test_static_workspace_entry_rejects_oversized_requests():
