@@ -48,6 +48,7 @@ _SIGNATURES = {
     "gaac_decode_page": (i32, [vp, vp, vp, vp, i64, vp, vp, vp, vp, vp, i32, i32, i64, i64, i64, vp, vp]),
     "gaac_exponent_hist": (i32, [vp, i64, i64, vp, vp]),
     "gaac_bases_from_hist": (i32, [vp, i64, vp, vp, vp]),
+    "gaac_set_launch_overlap": (None, [i32]),
     "gaac_attn_workspace_bytes": (sz, [i32, i32, i32]),
     "gaac_attn_workspace_header_bytes": (sz, [i32, i32]),
     "gaac_decode_attn_pages": (i32, [C.POINTER(Side), C.POINTER(Side), vp, i32, i32, i32, i64, i64, f32, i32, i32, vp, sz, vp, vp, vp, C.POINTER(Exchange), i32, vp]),

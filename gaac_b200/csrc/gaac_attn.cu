@@ -36,10 +36,35 @@ namespace gaac {
 #ifndef GAAC_LUTC
 #define GAAC_LUTC 0
 #endif
-constexpr int ATT_WARPS = 16;
+// Softmax weights enter the PV product as BF16 (tensor-core operand).  GAAC_SPLIT_P = 1: each weight goes in as the sum of two
+// BF16 numbers, its rounded value and the rounded remainder (two MMAs on the same V fragments), which brings the relative error
+// of a weight from 2^-8 down to 2^-16; = 0: the rounded value only, as the reference kernel does (gaac/kernel.py:178).
+#ifndef GAAC_SPLIT_P
+#define GAAC_SPLIT_P 1
+#endif
+// Build-time knobs of the experiments that shaped the kernel (the defaults are what ships):
+//   GAAC_WARPS    warps per CTA (one CTA per SM; the register budget per thread follows from it)
+//   GAAC_ESC_WIN  escape bytes staged per tile and kind
+//   GAAC_QSMEM    1: the query fragments live in a shared-memory table read once per K group instead of 16 registers per lane
+#ifndef GAAC_WARPS
+#define GAAC_WARPS 16
+#endif
+#ifndef GAAC_ESC_WIN
+#define GAAC_ESC_WIN 256
+#endif
+#ifndef GAAC_QSMEM
+#define GAAC_QSMEM 0
+#endif
+//   GAAC_ALU2FMA  bit mask of integer operations of the group decoder written as multiply-adds, which issue on the FMA pipe
+//                 instead of the half-rate ALU pipe: 1 = the >> 12 of the code word as a high multiply, 2 = the three-term
+//                 exponent sum as two multiply-adds by 1, 4 = the escape position advance as a multiply-add by 1
+#ifndef GAAC_ALU2FMA
+#define GAAC_ALU2FMA 0
+#endif
+constexpr int ATT_WARPS = GAAC_WARPS;
 constexpr int ATT_THREADS = ATT_WARPS * 32;
 constexpr int NSTAGE = 2;
-constexpr int ESC_WIN = 256;                         // escape bytes staged per tile and kind; longer tiles read theirs from global memory
+constexpr int ESC_WIN = GAAC_ESC_WIN;                       // escape bytes staged per tile and kind; longer tiles read theirs from global memory
 // ---- stage layout (bytes)
 // Stage = 16 bytes (mbarrier, then 8 bytes that stay zero) + a block per side:
 //   sign/mantissa (2048, storage order) | codes (768) | tag words (64) | escape window (ESC_WIN + 16: it starts at the
@@ -59,7 +84,8 @@ constexpr int META_TILES = 512;                      // tiles of a CTA's range w
 // CTA tables: escape-byte table (2 KiB), K / V base words, per-tile metadata, and the code table: four 3-bit codes -> four bytes
 // for all 4096 values of a 12-bit field (16 KiB).  The table turns four logic instructions per lookup into one shared-memory load.
 constexpr int TB_LUTX = 0, TB_KB = 2048, TB_VB = TB_KB + 256, TB_META = TB_VB + 256, TB_LUTC = TB_META + 2 * META_TILES * 4;
-constexpr int TABLE_BYTES = TB_LUTC + (GAAC_LUTC ? 4096 * 4 : 0);
+constexpr int TB_Q = TB_LUTC + (GAAC_LUTC ? 4096 * 4 : 0);          // query fragments: [4 K groups][32 lanes] x 16 bytes
+constexpr int TABLE_BYTES = TB_Q + (GAAC_QSMEM ? 4 * 32 * 16 : 0);
 constexpr int ATT_SMEM = TABLE_BYTES + ATT_WARPS * NSTAGE * STAGE_BYTES;
 static_assert(TABLE_BYTES % 16 == 0 && STAGE_BYTES % 16 == 0 && ST_KSM % 16 == 0 && ST_KCD % 16 == 0 && ST_KFL % 16 == 0 && ST_KESC % 16 == 0 &&
               ST_VSM % 16 == 0 && ST_VCD % 16 == 0 && ST_VFL % 16 == 0 && ST_VESC % 16 == 0 && ESC_COPY % 16 == 0 && ST_MBAR % 8 == 0 && SM_ROW % 16 == 0,
@@ -88,8 +114,16 @@ struct AttnParams {
   uint16_t* dump_k; uint16_t* dump_v; long dump_S;
 };
 
+#ifndef GAAC_MMA_VOLATILE
+#define GAAC_MMA_VOLATILE 1
+#endif
+#if GAAC_MMA_VOLATILE
+#define GAAC_MMA_ASM asm volatile
+#else
+#define GAAC_MMA_ASM asm
+#endif
 __device__ __forceinline__ void mma16816(float* c, const u32* a, u32 b0, u32 b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+  GAAC_MMA_ASM("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 // ---- bulk asynchronous copies (TMA engine, no tensor map): global -> shared, completion counted in bytes on an mbarrier.
@@ -139,8 +173,10 @@ struct WarpAcc {
 // Sums and accumulators are fp32 and P keeps its relative BF16 rounding, so the result is as exact as with the true
 // maximum, and the common tile needs no cross-lane reduction, no rescale factor and no accumulator multiply.
 constexpr float RESCALE_TAU = 16.f;
+// P^T B-fragments of one tile for the PV product: hi = the weights rounded to BF16, lo = the BF16-rounded remainders.
+struct PFrag { u32 hi0, hi1, lo0, lo1; };
 template <bool FULL_TILE>
-__device__ __forceinline__ void softmax_step(WarpAcc& A, const float* sc, float scale_log2, int nvalid, int lane, u32& pb0, u32& pb1) {
+__device__ __forceinline__ void softmax_step(WarpAcc& A, const float* sc, float scale_log2, int nvalid, int lane, PFrag& P) {
   const int j = lane & 3, r = lane >> 2;
   const bool v0 = FULL_TILE || r < nvalid, v8 = FULL_TILE || r + 8 < nvalid;     // a full tile needs no token masks
   const float s00 = v0 ? sc[0] * scale_log2 : -CUDART_INF_F, s01 = v0 ? sc[1] * scale_log2 : -CUDART_INF_F;
@@ -165,19 +201,62 @@ __device__ __forceinline__ void softmax_step(WarpAcc& A, const float* sc, float 
   const int srcA = 8 * j + (r >> 1), srcB = srcA + 4;
   const u32 a0 = __shfl_sync(FULLM, W0, srcA), a8 = __shfl_sync(FULLM, W8, srcA), b0w = __shfl_sync(FULLM, W0, srcB), b8w = __shfl_sync(FULLM, W8, srcB);
   const u32 sel = (r & 1) ? 0x7632u : 0x5410u;
-  pb0 = prmt(a0, b0w, sel); pb1 = prmt(a8, b8w, sel);
+  P.hi0 = prmt(a0, b0w, sel); P.hi1 = prmt(a8, b8w, sel);
+#if GAAC_SPLIT_P
+  // what the rounding dropped, exactly (p - bf16(p) is representable in fp32), rounded to BF16 in turn and routed the same way
+  __nv_bfloat162 xl = __floats2bfloat162_rn(p00 - __uint_as_float(W0 << 16), p01 - __uint_as_float(W0 & 0xFFFF0000u));
+  __nv_bfloat162 yl = __floats2bfloat162_rn(p80 - __uint_as_float(W8 << 16), p81 - __uint_as_float(W8 & 0xFFFF0000u));
+  const u32 L0 = *reinterpret_cast<u32*>(&xl), L8 = *reinterpret_cast<u32*>(&yl);
+  const u32 c0 = __shfl_sync(FULLM, L0, srcA), c8 = __shfl_sync(FULLM, L8, srcA), d0w = __shfl_sync(FULLM, L0, srcB), d8w = __shfl_sync(FULLM, L8, srcB);
+  P.lo0 = prmt(c0, d0w, sel); P.lo1 = prmt(c8, d8w, sel);
+#else
+  P.lo0 = P.lo1 = 0u;
+#endif
 }
 
 // PV for one pair of V words: tokens (2j, 2j+1, 2j+8, 2j+9) x elements (4w .. 4w+3).
-__device__ __forceinline__ void pv_words(WarpAcc& A, int w, const u32 (&u01)[4], const u32 (&u23)[4], u32 pb0, u32 pb1) {
+__device__ __forceinline__ void pv_words(WarpAcc& A, int w, const u32 (&u01)[4], const u32 (&u23)[4], const PFrag& P) {
+#if GAAC_SPLIT_P && defined(GAAC_PV_INTERLEAVE)
+  // the two MMAs into one accumulator depend on each other: issue the two independent ones in between
+  u32 a[4], c[4];
+  a[0] = prmt(u01[0], u01[1], 0x5410); a[2] = prmt(u01[2], u01[3], 0x5410);     // dim 8(4w)+r
+  a[1] = prmt(u01[0], u01[1], 0x7632); a[3] = prmt(u01[2], u01[3], 0x7632);     // dim 8(4w+1)+r
+  c[0] = prmt(u23[0], u23[1], 0x5410); c[2] = prmt(u23[2], u23[3], 0x5410);     // dim 8(4w+2)+r
+  c[1] = prmt(u23[0], u23[1], 0x7632); c[3] = prmt(u23[2], u23[3], 0x7632);     // dim 8(4w+3)+r
+  mma16816(A.acc[2 * w], a, P.hi0, P.hi1);
+  mma16816(A.acc[2 * w + 1], c, P.hi0, P.hi1);
+  mma16816(A.acc[2 * w], a, P.lo0, P.lo1);
+  mma16816(A.acc[2 * w + 1], c, P.lo0, P.lo1);
+#else
   u32 a[4];
   a[0] = prmt(u01[0], u01[1], 0x5410); a[2] = prmt(u01[2], u01[3], 0x5410);     // dim 8(4w)+r
   a[1] = prmt(u01[0], u01[1], 0x7632); a[3] = prmt(u01[2], u01[3], 0x7632);     // dim 8(4w+1)+r
-  mma16816(A.acc[2 * w], a, pb0, pb1);
+  mma16816(A.acc[2 * w], a, P.hi0, P.hi1);
+#if GAAC_SPLIT_P
+  mma16816(A.acc[2 * w], a, P.lo0, P.lo1);
+#endif
   a[0] = prmt(u23[0], u23[1], 0x5410); a[2] = prmt(u23[2], u23[3], 0x5410);     // dim 8(4w+2)+r
   a[1] = prmt(u23[0], u23[1], 0x7632); a[3] = prmt(u23[2], u23[3], 0x7632);     // dim 8(4w+3)+r
-  mma16816(A.acc[2 * w + 1], a, pb0, pb1);
+  mma16816(A.acc[2 * w + 1], a, P.hi0, P.hi1);
+#if GAAC_SPLIT_P
+  mma16816(A.acc[2 * w + 1], a, P.lo0, P.lo1);
+#endif
+#endif
 }
+
+// Q^T B-fragments of the score product.  Lane (j, r) holds, for k-step s, the words q[head r][16s + 2j, +1] and
+// q[head r][16s + 2j + 8, +9]; K group g of a lane uses k-steps 2g and 2g + 1.
+#if GAAC_QSMEM
+struct QFrag {
+  const uint4* tab;                                   // [4][32] in shared memory, built once per CTA
+  __device__ __forceinline__ void group(int g, int lane, u32 (&b)[4]) const { const uint4 v = tab[g * 32 + lane]; b[0] = v.x; b[1] = v.y; b[2] = v.z; b[3] = v.w; }
+};
+#else
+struct QFrag {
+  u32 qa[8][2];
+  __device__ __forceinline__ void group(int g, int, u32 (&b)[4]) const { b[0] = qa[2 * g][0]; b[1] = qa[2 * g][1]; b[2] = qa[2 * g + 1][0]; b[3] = qa[2 * g + 1][1]; }
+};
+#endif
 
 // Escape bytes of one tile as read by the group decoder.
 //   staged window (WIN): zp = shared-memory address of a zero byte below the tile's first escape byte; a group without an
@@ -227,8 +306,13 @@ __device__ __forceinline__ void decode_group_dev(u32 sm_lo, u32 sm_hi, u32 c24, 
   const u32 c_hi = mad_k<31u>(xh & 0x00380038u, xh);
 #else
   // four 3-bit codes -> four bytes in two steps; each step moves the upper fields with a multiply-add: (t & M) * (2^k - 1) + t
-  const u32 tl = c24 & 0xFFFu, th = (c24 >> 12) & 0xFFFu;
-  const u32 xl = mad_k<1023u>(c24 & 0xFC0u, tl), xh = mad_k<1023u>((c24 >> 12) & 0xFC0u, th);
+#if GAAC_ALU2FMA & 1
+  const u32 c12 = __umulhi(c24, 1u << 20);            // c24 >> 12
+#else
+  const u32 c12 = c24 >> 12;
+#endif
+  const u32 tl = c24 & 0xFFFu, th = c12 & 0xFFFu;
+  const u32 xl = mad_k<1023u>(c24 & 0xFC0u, tl), xh = mad_k<1023u>(c12 & 0xFC0u, th);
   const u32 c_lo = mad_k<31u>(xl & 0x00380038u, xl), c_hi = mad_k<31u>(xh & 0x00380038u, xh);
 #endif
   const u32 blo = bw.x + m1 * bw.z, bhi = bw.y + m1 * bw.w;
@@ -250,9 +334,18 @@ __device__ __forceinline__ void decode_group_dev(u32 sm_lo, u32 sm_hi, u32 c24, 
     x1 = spread_hi5_dev(funnel_r(lo, hi, 20) & 0xFFFFFu) - bhi;
     pos16 += 4;
   }
+#if GAAC_ALU2FMA & 4
+  pos16 = (int)mad_k<1u>(m1, (u32)pos16);
+#else
   pos16 += (int)m1;
+#endif
+#if GAAC_ALU2FMA & 2
+  bf16x4_dev(sm_lo, mad_k<1u>(c_lo, mad_k<1u>(blo, x0)), out[0], out[1]);
+  bf16x4_dev(sm_hi, mad_k<1u>(c_hi, mad_k<1u>(bhi, x1)), out[2], out[3]);
+#else
   bf16x4_dev(sm_lo, c_lo + blo + x0, out[0], out[1]);
   bf16x4_dev(sm_hi, c_hi + bhi + x1, out[2], out[3]);
+#endif
 }
 
 // Scores of one compressed K tile: sc += K . Q^T.  flrow / rowoff: tag word and escape offset of row (lane & 15) held by
@@ -261,7 +354,7 @@ __device__ __forceinline__ void decode_group_dev(u32 sm_lo, u32 sm_hi, u32 c24, 
 // fragment words it rebuilt at the (token, channel) pairs they stand for, rows >= nvalid are left alone.
 template <bool WIN, bool DUMP>
 __device__ __forceinline__ void k_scores(float* sc, const uint8_t* stage, const uint8_t* tables, const EscSrc<WIN>& es, u32 flrow, int rowoff,
-                                         int lane, const u32 (&qa)[8][2], uint16_t* dump = nullptr, int nvalid = T) {
+                                         int lane, const QFrag& Q, uint16_t* dump = nullptr, int nvalid = T) {
   const int j = lane & 3, r = lane >> 2;
   const u32x2* lutx = reinterpret_cast<const u32x2*>(tables + TB_LUTX);
   u32 t8[2]; int pos[2]; uint4 s0[2], s1[2]; u32 cd[2][3];
@@ -295,8 +388,10 @@ __device__ __forceinline__ void k_scores(float* sc, const uint8_t* stage, const 
           row[(32 * g + 16 + 2 * j) >> 1] = f[o][2]; row[(32 * g + 16 + 2 * j + 8) >> 1] = f[o][3];
         }
     }
-    { const u32 a[4] = {f[0][0], f[1][0], f[0][1], f[1][1]}; mma16816(sc, a, qa[2 * g][0], qa[2 * g][1]); }
-    { const u32 a[4] = {f[0][2], f[1][2], f[0][3], f[1][3]}; mma16816(s2, a, qa[2 * g + 1][0], qa[2 * g + 1][1]); }
+    u32 qb[4];
+    Q.group(g, lane, qb);
+    { const u32 a[4] = {f[0][0], f[1][0], f[0][1], f[1][1]}; mma16816(sc, a, qb[0], qb[1]); }
+    { const u32 a[4] = {f[0][2], f[1][2], f[0][3], f[1][3]}; mma16816(s2, a, qb[2], qb[3]); }
   }
   sc[0] += s2[0]; sc[1] += s2[1]; sc[2] += s2[2]; sc[3] += s2[3];
 }
@@ -304,7 +399,7 @@ __device__ __forceinline__ void k_scores(float* sc, const uint8_t* stage, const 
 // O^T += V^T . P^T for one compressed V tile.  flrow / rowoff of V row (lane & 15) are held by lanes 16-31.
 template <bool WIN, bool DUMP>
 __device__ __forceinline__ void v_accum(WarpAcc& A, const uint8_t* stage, const uint8_t* tables, const EscSrc<WIN>& es, u32 flrow, int rowoff,
-                                        int lane, u32 pb0, u32 pb1, uint16_t* dump = nullptr, int nvalid = T) {
+                                        int lane, const PFrag& P, uint16_t* dump = nullptr, int nvalid = T) {
   const int j = lane & 3, r = lane >> 2;
   const u32x2* lutx = reinterpret_cast<const u32x2*>(tables + TB_LUTX);
   u32 t4[4]; int pos[4]; uint4 sm[4]; u32 cd[6];
@@ -347,7 +442,7 @@ __device__ __forceinline__ void v_accum(WarpAcc& A, const uint8_t* stage, const 
     for (int h = 0; h < 2; h++) {
       const u32 u01[4] = {f[0][2 * h], f[1][2 * h], f[2][2 * h], f[3][2 * h]};
       const u32 u23[4] = {f[0][2 * h + 1], f[1][2 * h + 1], f[2][2 * h + 1], f[3][2 * h + 1]};
-      pv_words(A, 2 * g + h, u01, u23, pb0, pb1);
+      pv_words(A, 2 * g + h, u01, u23, P);
     }
   }
 }
@@ -368,11 +463,13 @@ __device__ __forceinline__ void scan_rows(const uint8_t* stage, bool rawk, bool 
 
 // Scores of a raw BF16 tile [16][128] in global memory (rows >= nvalid are not read).
 template <bool DUMP>
-__device__ __forceinline__ void raw_scores(float* sc, const uint16_t* kraw, int nvalid, int lane, const u32 (&qa)[8][2], uint16_t* dump = nullptr) {
+__device__ __forceinline__ void raw_scores(float* sc, const uint16_t* kraw, int nvalid, int lane, const QFrag& Q, uint16_t* dump = nullptr) {
   const int j = lane & 3, r = lane >> 2;
+  u32 qb[4];
 #pragma unroll
   for (int s = 0; s < 8; s++) {
     u32 a[4];
+    if ((s & 1) == 0) Q.group(s >> 1, lane, qb);
     const uint16_t* k0 = kraw + r * D + 16 * s + 2 * j;
     const uint16_t* k8 = k0 + 8 * D;
     a[0] = r < nvalid ? *reinterpret_cast<const u32*>(k0) : 0u; a[2] = r < nvalid ? *reinterpret_cast<const u32*>(k0 + 8) : 0u;
@@ -381,12 +478,12 @@ __device__ __forceinline__ void raw_scores(float* sc, const uint16_t* kraw, int 
       if (r < nvalid) { u32* row = reinterpret_cast<u32*>(dump + r * D); row[(16 * s + 2 * j) >> 1] = a[0]; row[(16 * s + 2 * j + 8) >> 1] = a[2]; }
       if (r + 8 < nvalid) { u32* row = reinterpret_cast<u32*>(dump + (r + 8) * D); row[(16 * s + 2 * j) >> 1] = a[1]; row[(16 * s + 2 * j + 8) >> 1] = a[3]; }
     }
-    mma16816(sc, a, qa[s][0], qa[s][1]);
+    mma16816(sc, a, qb[2 * (s & 1)], qb[2 * (s & 1) + 1]);
   }
 }
 // O^T += V^T . P^T for a raw BF16 tile.
 template <bool DUMP>
-__device__ __forceinline__ void raw_accum(WarpAcc& A, const uint16_t* vraw, int nvalid, int lane, u32 pb0, u32 pb1, uint16_t* dump = nullptr) {
+__device__ __forceinline__ void raw_accum(WarpAcc& A, const uint16_t* vraw, int nvalid, int lane, const PFrag& P, uint16_t* dump = nullptr) {
   const int j = lane & 3, r = lane >> 2;
 #pragma unroll
   for (int w = 0; w < 4; w++) {
@@ -403,7 +500,7 @@ __device__ __forceinline__ void raw_accum(WarpAcc& A, const uint16_t* vraw, int 
         o[0] = (uint16_t)e0; o[8] = (uint16_t)e1; o[16] = (uint16_t)e2; o[24] = (uint16_t)e3;
       }
     }
-    pv_words(A, w, u01, u23, pb0, pb1);
+    pv_words(A, w, u01, u23, P);
   }
 }
 
@@ -561,16 +658,28 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
   const int nstaged = min(thi - tlo, META_TILES);
   TileMeta m_first{0, 0};
   if (tid < nstaged) m_first = global_meta(tlo + tid);
-  u32 qa[8][2];
+  QFrag Q;
+#if GAAC_QSMEM
+  Q.tab = reinterpret_cast<const uint4*>(smem + TB_Q);
+  uint4 q_mine = make_uint4(0u, 0u, 0u, 0u);            // threads 0..127 load one table entry each: K group tid >> 5 of lane tid & 31
+  if (tid < 128) {
+    const int gg = tid >> 5, jj = tid & 3, rr = (tid & 31) >> 2;
+    if (rr < G) {
+      const uint16_t* qp = p.q + ((long)b * p.n_q + kvh * G + rr) * D + 32 * gg + 2 * jj;
+      q_mine = make_uint4(*reinterpret_cast<const u32*>(qp), *reinterpret_cast<const u32*>(qp + 8), *reinterpret_cast<const u32*>(qp + 16), *reinterpret_cast<const u32*>(qp + 24));
+    }
+  }
+#else
   {
     const bool ok = r < G;
     const uint16_t* qp = p.q + ((long)b * p.n_q + kvh * G + (ok ? r : 0)) * D;
 #pragma unroll
     for (int s = 0; s < 8; s++) {
-      qa[s][0] = ok ? *reinterpret_cast<const u32*>(qp + 16 * s + 2 * j) : 0u;
-      qa[s][1] = ok ? *reinterpret_cast<const u32*>(qp + 16 * s + 2 * j + 8) : 0u;
+      Q.qa[s][0] = ok ? *reinterpret_cast<const u32*>(qp + 16 * s + 2 * j) : 0u;
+      Q.qa[s][1] = ok ? *reinterpret_cast<const u32*>(qp + 16 * s + 2 * j + 8) : 0u;
     }
   }
+#endif
   // ---- CTA tables: escape-byte table, code table, per-lane-class base words {b3lo, b3hi, b4lo-b3lo, b4hi-b3hi} per group,
   // zero pads, per-tile metadata of the range (escape offsets or mode-table entries, so that the main loop never waits on a
   // dependent global load)
@@ -588,6 +697,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       *reinterpret_cast<u32x4*>(smem + TB_VB + 16 * t) = u32x4{w3[2 * gg], w3[2 * gg + 1], w4[2 * gg] - w3[2 * gg], w4[2 * gg + 1] - w3[2 * gg + 1]};
     }
     if (tid < 256) fill_lutx(reinterpret_cast<u32x2*>(smem + TB_LUTX), tid);
+#if GAAC_QSMEM
+    if (tid < 128) reinterpret_cast<uint4*>(smem + TB_Q)[tid] = q_mine;
+#endif
 #if GAAC_LUTC
     for (int i = tid; i < 4096; i += ATT_THREADS) reinterpret_cast<u32*>(smem + TB_LUTC)[i] = spread_codes4((u32)i);
 #endif
@@ -636,11 +748,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       int off, avail;
       staged_escapes(false, cur.mk, off, avail);
       if (__shfl_sync(FULLM, total, 15) + 8 <= avail)                                         // +8: a raw payload is read as two aligned words
-        k_scores<true, DUMP>(sc, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off}, flrow, rowoff, lane, qa, dump_k + (long)tile * T * D, nvalid);
+        k_scores<true, DUMP>(sc, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off}, flrow, rowoff, lane, Q, dump_k + (long)tile * T * D, nvalid);
       else
-        k_scores<false, DUMP>(sc, stage, smem, EscSrc<false>{nullptr, global_escapes(false, cur.mk), 0}, flrow, rowoff, lane, qa, dump_k + (long)tile * T * D, nvalid);
+        k_scores<false, DUMP>(sc, stage, smem, EscSrc<false>{nullptr, global_escapes(false, cur.mk), 0}, flrow, rowoff, lane, Q, dump_k + (long)tile * T * D, nvalid);
     } else {
-      raw_scores<DUMP>(sc, p.raw + (long)(~cur.mk) * (T * D), nvalid, lane, qa, dump_k + (long)tile * T * D);
+      raw_scores<DUMP>(sc, p.raw + (long)(~cur.mk) * (T * D), nvalid, lane, Q, dump_k + (long)tile * T * D);
     }
     t1 = __shfl_sync(FULLM, t1, 0);
     TileMeta nxt{0, 0};
@@ -649,18 +761,18 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       const u32 st = ring_s + (stg ^ 1) * STAGE_BYTES;
       if (lane == 0) bulk_issue(st, t1, nxt);
     }
-    u32 pb0, pb1;
-    if (nvalid == T) softmax_step<true>(A, sc, p.scale_log2, nvalid, lane, pb0, pb1);
-    else softmax_step<false>(A, sc, p.scale_log2, nvalid, lane, pb0, pb1);
+    PFrag P;
+    if (nvalid == T) softmax_step<true>(A, sc, p.scale_log2, nvalid, lane, P);
+    else softmax_step<false>(A, sc, p.scale_log2, nvalid, lane, P);
     if (!rawv) {
       int off, avail;
       staged_escapes(true, cur.mv, off, avail);
       if (__shfl_sync(FULLM, total, 31) + 8 <= avail)
-        v_accum<true, DUMP>(A, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off}, flrow, rowoff, lane, pb0, pb1, dump_v + (long)tile * T * D, nvalid);
+        v_accum<true, DUMP>(A, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off}, flrow, rowoff, lane, P, dump_v + (long)tile * T * D, nvalid);
       else
-        v_accum<false, DUMP>(A, stage, smem, EscSrc<false>{nullptr, global_escapes(true, cur.mv), 0}, flrow, rowoff, lane, pb0, pb1, dump_v + (long)tile * T * D, nvalid);
+        v_accum<false, DUMP>(A, stage, smem, EscSrc<false>{nullptr, global_escapes(true, cur.mv), 0}, flrow, rowoff, lane, P, dump_v + (long)tile * T * D, nvalid);
     } else {
-      raw_accum<DUMP>(A, p.raw + (long)(~cur.mv) * (T * D), nvalid, lane, pb0, pb1, dump_v + (long)tile * T * D);
+      raw_accum<DUMP>(A, p.raw + (long)(~cur.mv) * (T * D), nvalid, lane, P, dump_v + (long)tile * T * D);
     }
     cur = nxt; stg ^= 1; tile = t1;
   }
@@ -671,10 +783,10 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     for (int t0 = 0; t0 < TL; t0 += T) {
       const int nvalid = min(T, TL - t0);
       float sc[4] = {0.f, 0.f, 0.f, 0.f};
-      raw_scores<DUMP>(sc, kraw, nvalid, lane, qa, dump_k + ((long)S + t0) * D);
-      u32 pb0, pb1;
-      softmax_step<false>(A, sc, p.scale_log2, nvalid, lane, pb0, pb1);
-      raw_accum<DUMP>(A, vraw, nvalid, lane, pb0, pb1, dump_v + ((long)S + t0) * D);
+      raw_scores<DUMP>(sc, kraw, nvalid, lane, Q, dump_k + ((long)S + t0) * D);
+      PFrag P;
+      softmax_step<false>(A, sc, p.scale_log2, nvalid, lane, P);
+      raw_accum<DUMP>(A, vraw, nvalid, lane, P, dump_v + ((long)S + t0) * D);
       kraw += T * D; vraw += T * D;
     }
   }
@@ -919,6 +1031,9 @@ static int carve_workspace(void* ws, size_t ws_bytes, int B, int n_q, int nsplit
   return GAAC_OK;
 }
 
+// Programmatic dependent launch of the attention and merge kernels (see gaac_set_launch_overlap); on unless switched off.
+static int g_launch_overlap = 1;
+
 template <bool PAGED, bool DUMP>
 static int launch_attn(const AttnParams& p, cudaStream_t st) {
   cudaFuncSetAttribute(decode_attn_kernel<PAGED, DUMP>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT_SMEM);
@@ -926,7 +1041,7 @@ static int launch_attn(const AttnParams& p, cudaStream_t st) {
   cfg.gridDim = dim3((unsigned)(p.B * p.n_kv), (unsigned)p.nsplit); cfg.blockDim = dim3(ATT_THREADS);
   cfg.dynamicSmemBytes = ATT_SMEM; cfg.stream = st;
   cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = g_launch_overlap;
   cfg.attrs = at; cfg.numAttrs = 1;
   if (cudaLaunchKernelEx(&cfg, decode_attn_kernel<PAGED, DUMP>, p) != cudaSuccess) { cudaGetLastError(); return GAAC_E_LAUNCH; }
   return launch_status();
@@ -1013,6 +1128,8 @@ static int paged_attn(const gaac_paged* st, const int32_t* bt, int64_t bt_stride
 
 using namespace gaac;
 
+extern "C" void gaac_set_launch_overlap(int enabled) { g_launch_overlap = enabled ? 1 : 0; }
+
 extern "C" size_t gaac_attn_workspace_bytes(int B, int n_q, int nsplit) {
   if (B <= 0 || n_q <= 0 || nsplit <= 0) return 0;
   return ws_bytes_needed(B, n_q, nsplit);
@@ -1076,7 +1193,7 @@ extern "C" int gaac_exchange_merge(const gaac_exchange* x, int64_t n_heads, int 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)n_heads); cfg.blockDim = dim3(128); cfg.stream = (cudaStream_t)stream;
   cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = 1;
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = g_launch_overlap;
   cfg.attrs = at; cfg.numAttrs = 1;
   if (cudaLaunchKernelEx(&cfg, exchange_merge_kernel, x->recv, x->flags, x->epoch, x->ticket, x->err, x->rank, x->world, (int)(n_heads / groups),
                          (long)x->rows_cap, (uint16_t*)out_bf16, out_f32) != cudaSuccess) { cudaGetLastError(); return GAAC_E_LAUNCH; }

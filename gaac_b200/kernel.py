@@ -123,9 +123,11 @@ def _ext():
     return _mod
 
 
-def attention(q, kp, vp, scale=None, nsplit=None, out_f32=None):
+def attention(q, kp, vp, scale=None, nsplit=None, out_f32=None, out=None):
     """Decode attention over two Pages (kinds 'k' / 'v', H = B*n_kv heads of equal length).
     q: [B, n_q, D] bf16 (one query token per sequence) -> [B, n_q, D] bf16.  (gaac/kernel.py:345-359)
+    out (contiguous bf16 tensor of B*n_q*D elements) receives the result instead of a new tensor; out_f32 (fp32, same shape)
+    additionally receives the result before its rounding to BF16.
     nsplit=None picks the B200 heuristic; an explicit nsplit is honoured as given.  The two gaac_side descriptors are built
     once and kept on the Page objects, so a decode loop pays one library call per layer."""
     B, n_q, Dq = q.shape
@@ -139,7 +141,10 @@ def attention(q, kp, vp, scale=None, nsplit=None, out_f32=None):
         raise RuntimeError("GQA group size must be 1..8")
     dev = q.device
     if nsplit is None: nsplit = choose_nsplit_sm100(B, n_kv, kp.S)
-    out = torch.empty(B * n_q, Dq, dtype=q.dtype, device=dev)
+    if out is None:
+        out = torch.empty(B * n_q, Dq, dtype=q.dtype, device=dev)
+    elif not (out.is_contiguous() and out.dtype == q.dtype and out.numel() == B * n_q * Dq):
+        raise RuntimeError("out must be a contiguous bf16 tensor with B*n_q*128 elements")
     _pages_call(q, kp, vp, B, n_q, n_kv, scale, nsplit, out=out, out_f32=out_f32)
     return out.view(B, n_q, Dq)
 

@@ -102,6 +102,14 @@ typedef struct {
   const void* tail;           /* [heads, tail_cap, 128] bf16 raw tail, or NULL */
 } gaac_side;
 
+/* The attention and exchange-merge kernels are launched with programmatic stream serialisation allowed and begin with
+ * griddepcontrol.wait: behind a kernel that signals early (these do) their CTAs become resident while that kernel is still
+ * finishing, so consecutive attention layers overlap by a few microseconds; nothing is read or written before the wait returns.
+ * enabled = 0 switches this off for later launches of the process (every launch then starts after its predecessor has finished
+ * entirely, which is what a measurement of one launch's own duration wants); 1, the default, switches it back on.  Not
+ * thread-safe against concurrent launches.  No counterpart in the reference. */
+void gaac_set_launch_overlap(int enabled);
+
 /* Bytes of workspace gaac_decode_attn / gaac_paged_decode_attn need for (B, n_q, nsplit), and the size of the header at its
  * start.  Workspace = header | split partials.  Header: an int32 error word at byte 0, the int32 split counters (one per row
  * and kv head) from byte 256.  The header must be zero on the first use; every call leaves the counters zero, so a workspace

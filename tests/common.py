@@ -41,7 +41,7 @@ def assert_pages_equal(got: dict, ref: dict):
 
 
 def assert_attention_close(o32: np.ndarray, q16: np.ndarray, k16: np.ndarray, v16: np.ndarray, scale: float, what=""):
-    """fp32 attention result against the float64 oracle, element by element: |o32 - ref| <= 2e-3 * max(1, sum_i p_i |v_i|)
+    """fp32 attention result against the float64 oracle, element by element: |o32 - ref| <= max(2e-3, 2^-12 * sum_i p_i |v_i|)
     (oracle.attention_bound).  q16 [n_q, D], k16 / v16 [L, n_kv, D] BF16 bit patterns.  Returns (ref, worst error / bound)."""
     from oracle import gaac_oracle as O
     ref, ref_abs = O.attention_ref(q16, k16, v16, scale, with_abs=True)

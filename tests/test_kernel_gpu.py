@@ -20,7 +20,7 @@ def _check(out, out32, q16, k16, v16, B, n_kv, scale):
     o16, o32 = bits(out), out32.cpu().numpy()
     for b in range(B):
         kb = k16[b * n_kv:(b + 1) * n_kv].transpose(1, 0, 2); vb = v16[b * n_kv:(b + 1) * n_kv].transpose(1, 0, 2)
-        ref, _ = assert_attention_close(o32[b], q16[b], kb, vb, scale, b)          # fp32 result: 2e-3 x max(1, sum p|v|) per element
+        ref, _ = assert_attention_close(o32[b], q16[b], kb, vb, scale, b)          # fp32 result: max(2e-3, 2^-12 sum p|v|) per element
         mag = np.abs(ref).max()
         assert np.array_equal(o16[b], O.f32_to_bf16(o32[b]))                      # the bf16 output is the rounded fp32 result
         err16 = np.abs(O.bf16_to_f64(o16[b]) - ref).max()
@@ -242,7 +242,7 @@ def test_attention_full_size_contexts(S, outliers):
     """32 query / 8 kv heads over 2048, 65536 and 131072 tokens of the benchmark generator, default split count.  The codec is
     lossless, so the float64 reference is computed on the GPU from the original BF16 tensors.  Without the generator's forced
     outliers (no element multiplied by 2^4 or 2^7) the fp32 result is held to a plain 2e-3 max-abs; with them to
-    2e-3 * max(1, sum_i p_i |v_i|) per element.  A single-split run must meet the same bound (split merge)."""
+    max(2e-3, 2^-12 * sum_i p_i |v_i|) per element.  A single-split run must meet the same bound (split merge)."""
     import torch
     from gaac_b200 import attention, Codec, TileEncoder
     from gaac_b200.synth import synth_kv
@@ -255,7 +255,7 @@ def test_attention_full_size_contexts(S, outliers):
     o32 = torch.empty(1, n_kv * G, 128, dtype=torch.float32, device="cuda")
     out = attention(q, kp, vp, SCALE, out_f32=o32)
     ref, ref_abs = _fp64_attention_on_gpu(q[0], k, v, n_kv, G, SCALE)
-    bound = 2e-3 * torch.clamp(ref_abs, min=1.0)
+    bound = torch.clamp(ref_abs * 2.0 ** -12, min=2e-3)
     err = (o32[0].double() - ref).abs()
     assert bool((err <= bound).all()), float((err / bound).max())
     if not outliers:

@@ -59,7 +59,7 @@ def test_raw_pool_exhaustion_counts_errors():
     assert int(st.err) == 1 and int(st.top) == -1
 
 
-def _build_paged(seq_lens, n_kv, num_blocks, seed, adversarial_every=0, ovf_slot=128, **gen):
+def _build_paged(seq_lens, n_kv, num_blocks, seed, adversarial_every=0, ovf_slot=128, raw_tiles=None, **gen):
     """Store sequences of the given lengths through the paged store (whole prompt at once) -> (state, buf, bt, k16s, v16s).
     gen: raw_frac / four_frac of the synthetic generator."""
     import torch
@@ -69,7 +69,7 @@ def _build_paged(seq_lens, n_kv, num_blocks, seed, adversarial_every=0, ovf_slot
     cal_k, cal_v = O.synth_kv("k", n_kv, 2048, seed, **gen), O.synth_kv("v", n_kv, 2048, seed, **gen)
     k3, k4 = O.calibrate(cal_k, n_kv); v3, v4 = O.calibrate(cal_v, n_kv)
     bases = {n: torch.from_numpy(a) for n, a in (("k3", k3), ("k4", k4), ("v3", v3), ("v4", v4))}
-    st = LayerState(num_blocks, n_kv, raw_tiles=len(seq_lens) * 2 * n_kv + 64, bases=bases, ovf_slot=ovf_slot, device="cuda")
+    st = LayerState(num_blocks, n_kv, raw_tiles=raw_tiles or len(seq_lens) * 2 * n_kv + 64, bases=bases, ovf_slot=ovf_slot, device="cuda")
     buf = torch.zeros(num_blocks * 2 * n_kv * TS, dtype=torch.uint8, device="cuda")
     perm = rng.permutation(num_blocks)
     max_blocks = (max(seq_lens) + 15) // 16

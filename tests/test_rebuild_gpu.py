@@ -10,7 +10,7 @@ paged layout small and large escape slots, finalized tiles that stayed raw, and 
 """
 import numpy as np
 import pytest
-from common import to_bf16_cuda, bits
+from common import to_bf16_cuda, bits, assert_attention_close
 from oracle import gaac_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -53,7 +53,7 @@ def _assert_rebuilt(got, want16, S, what):
 @pytest.mark.parametrize("B,n_kv,G,S,nsplit", [(1, 2, 4, 1000, 3), (2, 2, 8, 333, 1), (1, 8, 4, 4096, 6), (3, 1, 1, 16, 1)])
 def test_rebuild_inside_attention_is_bit_exact_all_tiers(B, n_kv, G, S, nsplit):
     import torch
-    from gaac_b200 import Codec, TileEncoder, attention
+    from gaac_b200 import Codec, TileEncoder
     rng = np.random.default_rng(S + G)
     k16, v16 = O.synth_kv("k", B * n_kv, S, 3, raw_frac=0.01, four_frac=0.2), O.synth_kv("v", B * n_kv, S, 4, raw_frac=0.01, four_frac=0.2)
     if S >= 333:                                           # two stretches of random bit patterns: their tiles overflow the staged window
@@ -65,9 +65,8 @@ def test_rebuild_inside_attention_is_bit_exact_all_tiers(B, n_kv, G, S, nsplit):
     q16 = O.f32_to_bf16((rng.standard_normal((B, n_kv * G, 128)) * 0.05).astype(np.float32))
     kr, vr, o32 = _rebuild_pages(kp, vp, q16, B, n_kv, G, nsplit)
     _assert_rebuilt(kr, k16, S, "K"); _assert_rebuilt(vr, v16, S, "V")
-    ref32 = torch.empty_like(o32)
-    attention(to_bf16_cuda(q16), kp, vp, SCALE, nsplit=nsplit, out_f32=ref32)
-    assert float((o32 - ref32).abs().max()) <= 1e-4 * max(1.0, float(ref32.abs().max()))      # the same kernel, the same result
+    for b in range(B):                                     # the debug instantiation computes the same attention
+        assert_attention_close(o32[b].cpu().numpy(), q16[b], k16[b * n_kv:(b + 1) * n_kv].transpose(1, 0, 2), v16[b * n_kv:(b + 1) * n_kv].transpose(1, 0, 2), SCALE, b)
 
 
 def test_rebuild_at_every_phase_of_the_escape_stream():
@@ -141,7 +140,8 @@ def test_rebuild_paged_layout(ovf_slot, adv, gen):
     from test_paged_gpu import _build_paged
     n_kv, G = 2, 4
     seq_lens = [16, 37, 333, 1000, 5]
-    st, buf, bt, ks, vs = _build_paged(seq_lens, n_kv, 256, seed=21 + ovf_slot, adversarial_every=adv, ovf_slot=ovf_slot, **gen)
+    st, buf, bt, ks, vs = _build_paged(seq_lens, n_kv, 256, seed=21 + ovf_slot, adversarial_every=adv, ovf_slot=ovf_slot, raw_tiles=512, **gen)
+    assert int(st.err) == 0                                           # the raw pool was large enough for every tile that stayed raw
     mt = st.mt.cpu().numpy()
     full_tiles = sum(L // 16 for L in seq_lens) * 2 * n_kv
     n_raw_final = int((mt < 0).sum()) - sum(1 for L in seq_lens if L % 16) * 2 * n_kv
