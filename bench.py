@@ -663,7 +663,7 @@ def run_paged16(args):
     freeq = torch.empty(max(B, 1) * 2 * n_kv, dtype=torch.int32, device=dev)
     q = torch.randn(max(B, 1), n_q, 128, device=dev).to(torch.bfloat16)
     out = torch.empty(max(B, 1), n_q * 128, dtype=torch.bfloat16, device=dev)
-    ns = choose_nsplit_sm100(max(B, 1), n_kv, max_blocks * 16, ragged=True)
+    ns = choose_nsplit_sm100(max(B, 1), n_kv, max(lens0 + [16]), ragged=True, total_tokens=sum(lens0))
 
     def attend(s):
         paged_attention(q, out, buf, st.raw, st.mt, btd, sl_d[s], st.bases, TS, n_q, n_kv, ns)

@@ -44,7 +44,7 @@ _SIGNATURES = {
     "gaac_compact": (i32, [vp, vp, i64, i64, vp, vp, vp, i64, vp, vp, i64, i64, vp, vp]),
     "gaac_head_prefix": (i32, [vp, i64, vp, vp]),
     "gaac_encode_begin": (i32, [vp, i64, i64, i64, i64, vp, vp, vp, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp]),
-    "gaac_compact_copy": (i32, [vp, vp, i64, i64, vp, vp, vp, i64, vp, i64, i64, vp, i32, vp]),
+    "gaac_compact_copy": (i32, [vp, vp, i64, i64, vp, vp, vp, i64, vp, i64, i64, vp, i32, i64, i64, vp, vp]),
     "gaac_decode_page": (i32, [vp, vp, vp, vp, i64, vp, vp, vp, vp, vp, i32, i32, i64, i64, i64, vp, vp]),
     "gaac_exponent_hist": (i32, [vp, i64, i64, vp, vp]),
     "gaac_bases_from_hist": (i32, [vp, i64, vp, vp, vp]),

@@ -111,7 +111,8 @@ __global__ void __launch_bounds__(256) head_prefix_kernel(const int* __restrict_
 __global__ void __launch_bounds__(128) compact_copy_kernel(const uint8_t* __restrict__ slots, const int* __restrict__ tile_bytes, int ntiles,
                                                             const int* __restrict__ tile_off, long tile_off_stride,
                                                             const int* __restrict__ head_start, uint8_t* __restrict__ ovf, long n_items,
-                                                            const int* __restrict__ flags, long S, long S_pad, int* __restrict__ ovf_off, int zero_pad) {
+                                                            const int* __restrict__ flags, long S, long S_pad, int* __restrict__ ovf_off, int zero_pad,
+                                                            long ovf_cap, long head_cap, int* __restrict__ status) {
   const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (item >= n_items) return;
   const int lane = threadIdx.x & 31;
@@ -119,9 +120,17 @@ __global__ void __launch_bounds__(128) compact_copy_kernel(const uint8_t* __rest
   const int n = tile_bytes[item];
   const int toff = tile_off[h * tile_off_stride + t];
   const uint8_t* src = slots + item * (long)TILE_MAX_ESC;
-  uint8_t* dst = ovf + (long)head_start[h] + toff;
-  for (int i = lane; i < n; i += 32) dst[i] = src[i];
-  if (zero_pad && item == 0 && lane < zero_pad) ovf[(long)head_start[n_items / ntiles] + lane] = 0;     // over-read padding behind the last head
+  // bounds: the whole stream must fit ovf_cap bytes (ovf_cap > 0), a head's part head_cap bytes (head_cap > 0), read padding
+  // included; a tile that does not fit is not written and bit 0 of *status is set
+  const long at = (long)head_start[h] + toff;
+  const bool fits = (ovf_cap <= 0 || at + n + zero_pad <= ovf_cap) && (head_cap <= 0 || (long)toff + n + zero_pad <= head_cap);
+  if (fits) { uint8_t* dst = ovf + at; for (int i = lane; i < n; i += 32) dst[i] = src[i]; }
+  else if (lane == 0 && status) atomicOr(status, 1);
+  if (zero_pad && head_cap <= 0 && item == 0 && lane < zero_pad) {                                    // over-read padding behind the last head (packed stream)
+    const long end = (long)head_start[n_items / ntiles];
+    if (ovf_cap <= 0 || end + zero_pad <= ovf_cap) ovf[end + lane] = 0;
+    else if (lane == 0 && status) atomicOr(status, 1);
+  }
   if (ovf_off) {
     const long row = t * T + (lane & 15);
     const int sz = (lane < T && row < S) ? row_esc_bytes((u32)flags[h * S_pad + row]) : 0;
@@ -245,7 +254,7 @@ extern "C" int gaac_compact(const uint8_t* slots, const int32_t* tile_bytes, int
   if (head_start) {
     const long n_items = H * ntiles;
     compact_copy_kernel<<<(unsigned)((n_items + 3) / 4), 128, 0, st>>>(slots, tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_start, ovf, n_items,
-                                                                    flags, S, S_pad, ovf_off, 0);
+                                                                    flags, S, S_pad, ovf_off, 0, 0, 0, nullptr);
   }
   return launch_status();
 }
@@ -263,12 +272,13 @@ extern "C" int gaac_encode_begin(const void* x_bf16, int64_t H, int64_t S, int64
 
 extern "C" int gaac_compact_copy(const uint8_t* slots, const int32_t* tile_bytes, int64_t H, int64_t ntiles, const int32_t* head_start, uint8_t* ovf,
                                  const int32_t* tile_off, int64_t tile_off_stride, const int32_t* flags, int64_t S, int64_t S_pad, int32_t* ovf_off,
-                                 int zero_pad, void* stream) {
+                                 int zero_pad, int64_t ovf_cap, int64_t head_cap, int32_t* status, void* stream) {
   if (!slots || !tile_bytes || !head_start || !ovf || !tile_off || H <= 0 || ntiles <= 0 || tile_off_stride < ntiles || zero_pad < 0 || zero_pad > 32) return GAAC_E_ARG;
+  if (ovf_cap < 0 || head_cap < 0) return GAAC_E_ARG;
   if (ovf_off && (!flags || S <= 0 || S_pad < S)) return GAAC_E_ARG;
   const long n_items = H * ntiles;
   compact_copy_kernel<<<(unsigned)((n_items + 3) / 4), 128, 0, (cudaStream_t)stream>>>(slots, tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_start, ovf,
-                                                                                       n_items, flags, S, S_pad, ovf_off, zero_pad);
+                                                                                       n_items, flags, S, S_pad, ovf_off, zero_pad, ovf_cap, head_cap, status);
   return launch_status();
 }
 

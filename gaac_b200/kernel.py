@@ -39,21 +39,26 @@ def choose_nsplit(B: int, n_kv: int, S: int, target_ctas: int = 96, min_tok: int
     return min(max(1, target_ctas // (B * n_kv)), max(1, S // min_tok), cap)
 
 
-def choose_nsplit_sm100(B: int, n_kv: int, S: int, sm_count: int = SM_COUNT_B200, min_tiles_per_warp: int = 2, ragged: bool = False) -> int:
+def choose_nsplit_sm100(B: int, n_kv: int, S: int, sm_count: int = SM_COUNT_B200, min_tiles_per_warp: int = 2, ragged: bool = False,
+                        total_tokens: int | None = None) -> int:
     """Splits per (row, kv head) for a B200.  The kernel runs one 16-warp CTA per SM.
 
-    Few rows (B*n_kv up to half the SMs): fill the SMs in one wave, while every warp of a CTA keeps at least
-    min_tiles_per_warp 16-token tiles so the per-CTA prologue and merge stay amortised.
-    Many rows: the grid runs in several waves.  With equal lengths (S is every row's length) the split count minimises
-    waves x (tiles per CTA / 16 warps x tile time + per-CTA fixed cost); with ragged lengths (S is the longest row,
-    ragged=True) CTAs of about 512 tiles at the longest row let the block scheduler even out the rows."""
+    Equal lengths (S is every row's length), few rows (B*n_kv up to half the SMs): fill the SMs in one wave, while every warp of
+    a CTA keeps at least min_tiles_per_warp 16-token tiles so the per-CTA prologue and merge stay amortised.
+    Equal lengths, many rows: the grid runs in several waves; the split count minimises
+    waves x (tiles per CTA / 16 warps x tile time + per-CTA fixed cost).
+    Ragged lengths (ragged=True, S is the longest row, total_tokens the sum over the batch rows when known, else rows are taken
+    to average 55 % of the longest): every row gets the same split count, so the longest row's chunks must be small against an
+    SM's share of the whole batch for the block scheduler to even the SMs out: a third of that share, and at most 512 tiles."""
     rows = max(1, B * n_kv)
     ntiles = max(1, (S + 15) // 16)
     most = max(1, ntiles // (ATT_WARPS * min_tiles_per_warp))
+    if ragged:
+        mean_tiles = (total_tokens / max(1, B) / 16.0) if total_tokens else 0.55 * ntiles
+        per_sm = max(1.0, rows * mean_tiles / sm_count)
+        return max(1, min(most, max(-(-ntiles // 512), int(-(-3 * ntiles // per_sm)))))
     if 2 * rows <= sm_count:
         return max(1, min(sm_count // rows, most))
-    if ragged:
-        return max(1, min(-(-ntiles // 512), most))
     tile_us, fixed_us, best, best_t = 4.4, 10.0, 1, None              # measured: time of one tile pair in a full CTA, prologue + merges
     for ns in range(1, min(most, 32) + 1):
         waves = -(-rows * ns // sm_count)

@@ -118,23 +118,30 @@ class CompressedKVCache:
                 st.base3[hs], st.base4[hs] = own.base3, own.base4
             st.ovf_used[hs] = 0
             if n_full:
-                self._store_tiles(st, hs, per_head[:, :n_full], n_full)
+                self._store_tiles(st, hs, per_head, n_full)
             if L > n_full:
                 st.tail[hs, :L - n_full] = per_head[:, n_full:]
         self.S[hs] = n_full
         self.tail_len[hs] = L - n_full
 
     def _store_tiles(self, st: _Store, hs: slice, x: torch.Tensor, n_tok: int):
-        """Compress x [n_kv, n_tok, 128] (n_tok a multiple of 16) into the heads hs of st, escape streams from offset 0."""
-        rows = torch.arange(hs.start, hs.stop, device=x.device, dtype=torch.int32) % st.base3.shape[0]     # base row of each head
-        tile_bytes = st.enc.encode_tiles(x, st.base3, st.base4, st.sm[hs], st.codes[hs], st.flags[hs], n_tok, self.cap, self.n_kv, bidx=rows.contiguous())
-        _, head_bytes = st.enc.tile_offsets(tile_bytes)
+        """Compress the first n_tok tokens (a multiple of 16) of x [n_kv, >= n_tok, 128] into the heads hs of st, escape streams
+        from offset 0.  Encode, offsets and the copy into the heads' streams are launched back to back; the copy never writes
+        past a head's share, so the one host read (largest head, status word) can come afterwards.  Only when a head's stream was
+        too small are the streams enlarged and the copy (not the encode) repeated."""
+        rows = (torch.arange(hs.start, hs.stop, device=x.device, dtype=torch.int32) % st.base3.shape[0]).contiguous()     # base row of each head
+        tile_off = torch.empty(self.n_kv, n_tok // T, dtype=torch.int32, device=x.device)
+        status, retry = st.enc.encode_into(x, st.base3, st.base4, self.n_kv, st.sm[hs], st.codes[hs], st.flags[hs], tile_off, st.ovf, S=n_tok, S_pad=self.cap,
+                                           head_base=st.head_start[hs], head_cap=st.ovf_cap, head_bytes=st.ovf_used[hs], bidx=rows, zero_pad=_OVER_READ)
+        st.tile_off[hs, :n_tok // T] = tile_off
+        biggest, too_small = (int(v) for v in torch.stack([st.ovf_used[hs].max(), status[0]]).tolist())
         # room for these tiles and for one more worst-case tile, which an append may add before the next check_capacity
-        wanted = int(head_bytes.max()) + TILE_MAX_ESC + _OVER_READ
+        wanted = biggest + TILE_MAX_ESC + _OVER_READ
         if wanted > st.ovf_cap:
             self._grow(wanted)
-        st.tile_off[hs, :n_tok // T] = st.enc.compact(tile_bytes, st.head_start[hs.start:hs.stop + 1], st.ovf)
-        st.ovf_used[hs] = head_bytes
+        if too_small:
+            status.zero_()
+            retry(st.ovf, head_base=st.head_start[hs], head_cap=st.ovf_cap)
 
     # ------------------------------------------------------------------ decode step
     def append(self, slots: torch.Tensor, k: torch.Tensor, v: torch.Tensor):

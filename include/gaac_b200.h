@@ -63,10 +63,15 @@ int gaac_encode_begin(const void* x_bf16, int64_t H, int64_t S, int64_t S_in, in
 
 /* The copy half of gaac_compact with tile offsets that are already known: scratch slots -> ovf + head_start[h] + tile_off[h, t],
  * optionally the per-row offsets ovf_off [H, S], and zero_pad (0..32) zero bytes written behind the last head (the reference
- * allocates its stream with 8 bytes of over-read padding, gaac/encoder.py:121).  Replaces _compact (gaac/encoder.py:69-76). */
+ * allocates its stream with 8 bytes of over-read padding, gaac/encoder.py:121).  The copy is bounded, which lets a caller
+ * allocate the stream before its size is known and so keep the whole encode free of host round trips: with ovf_cap > 0 nothing
+ * is written at or beyond ovf + ovf_cap, with head_cap > 0 nothing of head h beyond head_start[h] + head_cap (zero_pad bytes of
+ * read padding included in both); a tile that does not fit is skipped and bit 0 of *status (device int32, may be NULL) is set.  The
+ * sizes in head_start / head_bytes are exact all the same, so the caller enlarges the buffer and repeats only this call (the
+ * scratch slots are still valid).  Replaces _compact (gaac/encoder.py:69-76). */
 int gaac_compact_copy(const uint8_t* slots, const int32_t* tile_bytes, int64_t H, int64_t ntiles, const int32_t* head_start, uint8_t* ovf,
                       const int32_t* tile_off, int64_t tile_off_stride, const int32_t* flags, int64_t S, int64_t S_pad, int32_t* ovf_off,
-                      int zero_pad, void* stream);
+                      int zero_pad, int64_t ovf_cap, int64_t head_cap, int32_t* status, void* stream);
 
 /* head_start[0..H] = exclusive prefix of head_bytes[0..H-1] (int32).  Replaces the head-level cumsum of
  * TileEncoder.encode (gaac/encoder.py:119-120). */

@@ -151,3 +151,53 @@ def test_paged_incremental_decode_steps():
     # raw tiles in use = one per (sequence, kv head, kind) with a filling block
     filling = sum(1 for L in lens if L % 16)
     assert int((st.mt < 0).sum()) == filling * 2 * n_kv
+
+
+def test_step_metadata_feeds_store_and_attention():
+    """The host-side step metadata (build_entries, EntryUploader: gaac/vllm/backend.py:205-224 restated) drives the GPU store over a
+    chunked prefill, a whole-prompt prefill and decode steps; afterwards every block decodes to what was written and paged
+    attention over the result matches the oracle."""
+    import torch
+    from gaac_b200.vllm import metadata as M
+    from gaac_b200.vllm.store import LayerState, OVF_OFF
+    from gaac_b200.vllm.paged_kernel import paged_attention
+    n_kv, G, num_blocks, ovf_slot = 2, 4, 64, 128
+    TS = OVF_OFF + ovf_slot
+    cal_k, cal_v = O.synth_kv("k", n_kv, 512, 3), O.synth_kv("v", n_kv, 512, 3)
+    k3, k4 = O.calibrate(cal_k, n_kv); v3, v4 = O.calibrate(cal_v, n_kv)
+    st = LayerState(num_blocks, n_kv, raw_tiles=32, bases={n: torch.from_numpy(a) for n, a in (("k3", k3), ("k4", k4), ("v3", v3), ("v4", v4))}, ovf_slot=ovf_slot, device="cuda")
+    buf = torch.zeros(num_blocks * 2 * n_kv * TS, dtype=torch.uint8, device="cuda")
+    up = M.EntryUploader(max_entries=8, n_kv=n_kv, device="cuda")
+    rng = np.random.default_rng(1)
+    blocks = rng.permutation(num_blocks)
+    table = {0: blocks[0:8], 1: blocks[8:16], 2: blocks[16:24]}
+    cached = {0: 0, 1: 0, 2: 0}
+    hist = {r: (np.zeros((0, n_kv, 128), np.uint16), np.zeros((0, n_kv, 128), np.uint16)) for r in table}
+    stream = {r: (np.roll(O.synth_kv("k", n_kv, 512 + 120, 3)[:, 512:].transpose(1, 0, 2), r, axis=0), np.roll(O.synth_kv("v", n_kv, 512 + 120, 3)[:, 512:].transpose(1, 0, 2), r, axis=0)) for r in table}
+    for step in [{0: 20, 1: 37}, {0: 13, 2: 16}] + [{0: 1, 1: 1, 2: 1}] * 30:
+        reqs = sorted(step)
+        qsl = np.concatenate([[0], np.cumsum([step[r] for r in reqs])])
+        key = np.concatenate([stream[r][0][cached[r]:cached[r] + step[r]] for r in reqs]); val = np.concatenate([stream[r][1][cached[r]:cached[r] + step[r]] for r in reqs])
+        slot_mapping = np.concatenate([table[r][(cached[r] + np.arange(step[r])) // 16] * 16 + (cached[r] + np.arange(step[r])) % 16 for r in reqs])
+        ent, freeq = up.upload(M.build_entries(qsl, [cached[r] for r in reqs]), torch.from_numpy(slot_mapping).cuda())
+        st.store(to_bf16_cuda(key), to_bf16_cuda(val), buf, ent, freeq)
+        for i, r in enumerate(reqs):
+            hist[r] = (np.concatenate([hist[r][0], key[qsl[i]:qsl[i + 1]]]), np.concatenate([hist[r][1], val[qsl[i]:qsl[i + 1]]]))
+            cached[r] += step[r]
+    assert int(st.err) == 0
+    # every block decodes to what was written
+    L = [cached[r] for r in sorted(table)]
+    rows0 = np.concatenate([[0], np.cumsum([(l + 15) // 16 * 16 for l in L])])
+    pairs = [[int(table[r][b]), int(rows0[i] + 16 * b), min(16, L[i] - 16 * b)] for i, r in enumerate(sorted(table)) for b in range((L[i] + 15) // 16)]
+    sk = torch.zeros(int(rows0[-1]), n_kv, 128, dtype=torch.bfloat16, device="cuda"); sv = torch.zeros_like(sk)
+    st.decode_blocks(buf, torch.tensor(pairs, dtype=torch.int32, device="cuda"), sk, sv)
+    for i, r in enumerate(sorted(table)):
+        assert np.array_equal(bits(sk)[rows0[i]:rows0[i] + L[i]], hist[r][0]) and np.array_equal(bits(sv)[rows0[i]:rows0[i] + L[i]], hist[r][1])
+    # and attention over the stored blocks
+    n_q = n_kv * G
+    bt = torch.tensor(np.stack([table[r] for r in sorted(table)]).astype(np.int32), device="cuda")
+    q16 = O.f32_to_bf16((rng.standard_normal((3, n_q, 128)) * 0.3).astype(np.float32))
+    out = torch.empty(3, n_q * 128, dtype=torch.bfloat16, device="cuda"); o32 = torch.empty(3, n_q, 128, dtype=torch.float32, device="cuda")
+    paged_attention(to_bf16_cuda(q16), out, buf, st.raw, st.mt, bt, torch.tensor(L, dtype=torch.int32, device="cuda"), st.bases, st.TS, n_q, n_kv, out_f32=o32)
+    for i, r in enumerate(sorted(table)):
+        assert_attention_close(o32[i].cpu().numpy(), q16[i], hist[r][0], hist[r][1], 128 ** -0.5, r)
