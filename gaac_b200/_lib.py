@@ -66,6 +66,7 @@ _SIGNATURES = {
     "gaac_paged_release": (i32, [C.POINTER(Paged), vp, i32, vp]),
     "gaac_paged_decode_blocks": (i32, [C.POINTER(Paged), vp, i32, vp, vp, i64, vp]),
     "gaac_paged_decode_attn": (i32, [C.POINTER(Paged), vp, i64, vp, vp, i32, i32, f32, i32, vp, sz, vp, vp, vp]),
+    "gaac_paged_decode_attn256": (i32, [C.POINTER(Paged), vp, i64, vp, vp, i32, i32, f32, i32, vp, sz, vp, vp, vp]),
     "gaac_decode_attn_static": (i32, [C.POINTER(Side), C.POINTER(Side), vp, vp, i32, i32, i32, vp, i64, f32, i32, vp, i32, i32, vp, vp, vp]),
     "gaac_static_workspace_bytes": (sz, []),
     "gaac_static_workspace_error": (i32, [vp, i32, vp]),

@@ -948,6 +948,178 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
   }
 }
 
+// ------------------------------------------------------------------------------------------------ head_dim 256, paged layout
+// A 256-dim head is stored as two 128-dim half-heads in neighbouring tile slots, each with its own bases
+// (gaac/vllm/paged_kernel256.py:1-4): block = 2*n_kv half-heads x {K, V}, half-head hh = 2*kvh + half.  Two warps form a pair that
+// streams the same tiles: each warp owns one half - it stages and rebuilds its half's K tile, which yields a partial score, and
+// its half's V tile, which yields its 128 output dimensions.  The two partial scores meet in shared memory once per tile (one
+// 64-thread named barrier; the exchange slots alternate with the tile's parity so one barrier per tile is enough), after which
+// both warps run the same softmax step on the same numbers.  Tiles are handed to PAIRS from the CTA's counter; the even warp
+// takes the number and passes it through the exchange slot.  A warp whose bounded wait on its copies runs out says so in
+// the same slot, so that both warps of the pair leave the loop together and nobody is left at the barrier.
+// Output: un-normalised partials of "virtual heads" vq = 2 * query head + half, i.e. exactly the layout gaac_combine turns into
+// out [B, n_q, 256].
+static_assert(GAAC_LUTC == 0 && ATT_WARPS % 2 == 0, "the 256-dim kernel uses the arithmetic code spreading and warp pairs");
+constexpr int T256_HALF = 2048 + 256 + 256;                       // per half: escape-byte table, K base words, V base words (same offsets as the CTA tables above)
+constexpr int XCH_PAR_BYTES = 2 * 32 * 16 + 16;                    // one parity: two halves x 32 lanes x float4, then {next tile, fail flag of half 0, of half 1, -}
+constexpr int T256_XCH = 2 * T256_HALF;
+constexpr int TABLE256_BYTES = T256_XCH + (ATT_WARPS / 2) * 2 * XCH_PAR_BYTES;
+constexpr int ATT256_SMEM = TABLE256_BYTES + ATT_WARPS * NSTAGE * STAGE_BYTES;
+static_assert(TB_KB == 2048 && TB_VB == 2048 + 256 && TABLE256_BYTES % 16 == 0 && ATT256_SMEM + 64 <= 232448, "table layout shared with the 128-dim kernel; one CTA per SM");
+
+__global__ void __launch_bounds__(ATT_THREADS, 1) paged256_attn_kernel(const __grid_constant__ AttnParams p) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  __shared__ int s_next;
+  const int bh = blockIdx.x, split = blockIdx.y, tid = threadIdx.x, lane = tid & 31, j = lane & 3, r = lane >> 2;
+  const int warp = __shfl_sync(FULLM, tid >> 5, 0);
+  const int hf = warp & 1, pair = warp >> 1;
+  const int b = bh / p.n_kv, kvh = bh % p.n_kv, G = p.G, hh = 2 * kvh + hf, NT = 4 * p.n_kv;    // p.n_kv = 256-dim kv heads; NT tile slots per block
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::);
+  const int S = __shfl_sync(FULLM, p.seq_len[b], 0);
+  const int ntiles = (S + 15) >> 4, chunk = (ntiles + p.nsplit - 1) / p.nsplit;
+  const int tlo = min(split * chunk, ntiles), thi = min(tlo + chunk, ntiles);
+  uint8_t* ring = smem + TABLE256_BYTES + warp * (NSTAGE * STAGE_BYTES);
+  const u32 ring_s = (u32)__cvta_generic_to_shared(ring);
+  const uint8_t* tables = smem + hf * T256_HALF;
+  uint8_t* xch = smem + T256_XCH + pair * (2 * XCH_PAR_BYTES);
+  auto meta = [&](int tile) -> TileMeta { const int pc = p.bt[(long)b * p.bt_stride + tile] * NT + 2 * hh; return TileMeta{p.mt[pc], p.mt[pc + 1]}; };
+  auto issue = [&](u32 st, const TileMeta& m) {                                // executed by lane 0
+    const u32 mb = st + ST_MBAR, n = (u32)min(p.TS, SLOT_OVF_OFF + ESC_COPY);
+    mbar_expect_tx(mb, (m.mk >= 0 ? n : 0u) + (m.mv >= 0 ? n : 0u));
+    if (m.mk >= 0) bulk_g2s(st + ST_KSM, p.buf + (long)m.mk * p.TS, n, mb);
+    if (m.mv >= 0) bulk_g2s(st + ST_VSM, p.buf + (long)m.mv * p.TS, n, mb);
+  };
+  if (lane == 0) {
+    mbar_init(ring_s + ST_MBAR, 1); mbar_init(ring_s + STAGE_BYTES + ST_MBAR, 1);
+    *reinterpret_cast<unsigned long long*>(ring + ST_ZERO) = 0ull; *reinterpret_cast<unsigned long long*>(ring + STAGE_BYTES + ST_ZERO) = 0ull;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncwarp();
+  int tile = tlo + pair;
+  TileMeta cur{0, 0};
+  if (tile < thi) { cur = meta(tile); if (lane == 0) issue(ring_s, cur); }
+  QFrag Q;
+#if GAAC_QSMEM
+#error "the 256-dim kernel keeps the query fragments in registers"
+#else
+  {
+    const bool ok = r < G;
+    const uint16_t* qp = p.q + ((long)b * p.n_q + kvh * G + (ok ? r : 0)) * (2 * D) + hf * D;
+#pragma unroll
+    for (int s = 0; s < 8; s++) {
+      Q.qa[s][0] = ok ? *reinterpret_cast<const u32*>(qp + 16 * s + 2 * j) : 0u;
+      Q.qa[s][1] = ok ? *reinterpret_cast<const u32*>(qp + 16 * s + 2 * j + 8) : 0u;
+    }
+  }
+#endif
+  {   // tables of both halves; exchange slots start out zero
+    if (tid < 256) { fill_lutx(reinterpret_cast<u32x2*>(smem + TB_LUTX), tid); fill_lutx(reinterpret_cast<u32x2*>(smem + T256_HALF + TB_LUTX), tid); }
+    if (tid >= 256 && tid < 288) {                    // K: half, lane class jj, group gg
+      const int t = tid - 256, h2 = t >> 4, jj = (t >> 2) & 3, gg = t & 3; u32 w3[8], w4[8];
+      const int row = 2 * kvh + h2;
+      k_base_words(p.b3k + row * D, jj, w3); k_base_words(p.b4k + row * D, jj, w4);
+      *reinterpret_cast<u32x4*>(smem + h2 * T256_HALF + TB_KB + 16 * (t & 15)) = u32x4{w3[2 * gg], w3[2 * gg + 1], w4[2 * gg] - w3[2 * gg], w4[2 * gg + 1] - w3[2 * gg + 1]};
+    } else if (tid >= 288 && tid < 320) {             // V: half, lane class rr, group gg
+      const int t = tid - 288, h2 = t >> 4, rr = (t >> 1) & 7, gg = t & 1; u32 w3[4], w4[4];
+      const int row = 2 * kvh + h2;
+      v_base_words(p.b3v + row * D, rr, w3); v_base_words(p.b4v + row * D, rr, w4);
+      *reinterpret_cast<u32x4*>(smem + h2 * T256_HALF + TB_VB + 16 * (t & 15)) = u32x4{w3[2 * gg], w3[2 * gg + 1], w4[2 * gg] - w3[2 * gg], w4[2 * gg + 1] - w3[2 * gg + 1]};
+    }
+    for (int i = tid; i < (ATT_WARPS / 2) * 2 * XCH_PAR_BYTES / 4; i += ATT_THREADS) reinterpret_cast<u32*>(smem + T256_XCH)[i] = 0u;
+    if (tid == 0) s_next = tlo + ATT_WARPS / 2;       // tiles tlo .. tlo + pairs - 1 go to the pairs in order, the rest is handed out on demand
+  }
+  WarpAcc A;
+#pragma unroll
+  for (int n = 0; n < 8; n++) A.acc[n][0] = A.acc[n][1] = A.acc[n][2] = A.acc[n][3] = 0.f;
+  A.m0 = A.m1 = -CUDART_INF_F; A.l0 = A.l1 = 0.f;
+  __syncthreads();
+
+  int stg = 0, par = 0;
+  u32 phase = 0;
+  const int esc_off = ST_KESC - ST_ZERO, esc_off_v = ST_VESC - ST_ZERO;
+  const int esc_avail = min(p.ovf_slot, min(p.TS, SLOT_OVF_OFF + ESC_COPY) - SLOT_OVF_OFF);
+  while (tile < thi) {
+    int t1 = 0;
+    if (hf == 0 && lane == 0) t1 = atomicAdd(&s_next, 1);
+    const bool ok = __all_sync(FULLM, mbar_wait(ring_s + stg * STAGE_BYTES + ST_MBAR, (phase >> stg) & 1u));
+    phase ^= 1u << stg;
+    const uint8_t* stage = ring + stg * STAGE_BYTES;
+    const int nvalid = min(T, S - tile * T);
+    const bool rawk = cur.mk < 0, rawv = cur.mv < 0;
+    u32 flrow = 0; int rowoff = 0, total = 0;
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (ok) {
+      scan_rows(stage, rawk, rawv, lane, flrow, rowoff, total);
+      if (!rawk) {
+        if (__shfl_sync(FULLM, total, 15) + 8 <= esc_avail)
+          k_scores<true, false>(sc, stage, tables, EscSrc<true>{stage + ST_ZERO, nullptr, esc_off}, flrow, rowoff, lane, Q);
+        else
+          k_scores<false, false>(sc, stage, tables, EscSrc<false>{nullptr, p.buf + (long)cur.mk * p.TS + SLOT_OVF_OFF, 0}, flrow, rowoff, lane, Q);
+      } else raw_scores<false>(sc, p.raw + (long)(~cur.mk) * (T * D), nvalid, lane, Q);
+    }
+    // ---- the two halves' partial scores meet; the next tile's number and a failed wait travel with them
+    uint8_t* slot = xch + par * XCH_PAR_BYTES;
+    reinterpret_cast<float4*>(slot + hf * 512)[lane] = make_float4(sc[0], sc[1], sc[2], sc[3]);
+    int* ctl = reinterpret_cast<int*>(slot + 1024);
+    if (lane == 0) { if (hf == 0) ctl[0] = t1; if (!ok) ctl[1 + hf] = 1; }
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");
+    const float4 other = reinterpret_cast<const float4*>(slot + (hf ^ 1) * 512)[lane];
+    sc[0] += other.x; sc[1] += other.y; sc[2] += other.z; sc[3] += other.w;
+    t1 = ctl[0];
+    const bool failed = (ctl[1] | ctl[2]) != 0;
+    par ^= 1;
+    if (failed) { if (lane == 0) atomicExch(p.err, 1); break; }                 // both warps of the pair see the same flags and leave together
+    TileMeta nxt{0, 0};
+    if (t1 < thi) { nxt = meta(t1); if (lane == 0) issue(ring_s + (stg ^ 1) * STAGE_BYTES, nxt); }
+    PFrag P;
+    if (nvalid == T) softmax_step<true>(A, sc, p.scale_log2, nvalid, lane, P);
+    else softmax_step<false>(A, sc, p.scale_log2, nvalid, lane, P);
+    if (!rawv) {
+      if (__shfl_sync(FULLM, total, 31) + 8 <= esc_avail)
+        v_accum<true, false>(A, stage, tables, EscSrc<true>{stage + ST_ZERO, nullptr, esc_off_v}, flrow, rowoff, lane, P);
+      else
+        v_accum<false, false>(A, stage, tables, EscSrc<false>{nullptr, p.buf + (long)cur.mv * p.TS + SLOT_OVF_OFF, 0}, flrow, rowoff, lane, P);
+    } else raw_accum<false>(A, p.raw + (long)(~cur.mv) * (T * D), nvalid, lane, P);
+    cur = nxt; stg ^= 1; tile = t1;
+  }
+  // ---- merge the warps of the CTA, half by half, and write one partial per virtual head (2 * query head + half)
+  __syncthreads();
+  constexpr int ACC_LD = D + 4;
+  float* sh_m = reinterpret_cast<float*>(smem + TABLE256_BYTES);
+  float* sh_l = sh_m + ATT_WARPS * 8;
+  float* sh_acc = sh_l + ATT_WARPS * 8;
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) { A.l0 += __shfl_xor_sync(FULLM, A.l0, o); A.l1 += __shfl_xor_sync(FULLM, A.l1, o); }
+  if (r == 0) { sh_m[warp * 8 + 2 * j] = A.m0; sh_l[warp * 8 + 2 * j] = A.l0; sh_m[warp * 8 + 2 * j + 1] = A.m1; sh_l[warp * 8 + 2 * j + 1] = A.l1; }
+  if (2 * j < G) {
+#pragma unroll
+    for (int n = 0; n < 8; n++) {
+      float* a0 = sh_acc + ((warp * 8 + 2 * j) * ACC_LD) + 16 * n + r;
+      a0[0] = A.acc[n][0]; a0[ACC_LD] = A.acc[n][1]; a0[8] = A.acc[n][2]; a0[ACC_LD + 8] = A.acc[n][3];
+    }
+  }
+  __syncthreads();
+  const int d = tid & 127;
+  for (int vg = tid >> 7; vg < 2 * G; vg += ATT_THREADS / 128) {
+    const int g = vg >> 1, h2 = vg & 1;
+    float M = -CUDART_INF_F;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS / 2; w++) M = fmaxf(M, sh_m[(2 * w + h2) * 8 + g]);
+    float Lc = 0.f, Ac = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS / 2; w++) {
+      const int ww = 2 * w + h2;
+      const float mw = sh_m[ww * 8 + g];
+      const float f = (mw == -CUDART_INF_F) ? 0.f : fast_exp2(mw - M);
+      Lc += sh_l[ww * 8 + g] * f; Ac += sh_acc[(ww * 8 + g) * ACC_LD + d] * f;
+    }
+    const long vq = ((long)b * p.n_q + kvh * G + g) * 2 + h2, pidx = vq * p.nsplit + split;
+    if (d == 0) { p.pm[pidx] = M * LN2; p.pl[pidx] = Lc; }                      // m in natural-log units, as gaac_combine expects
+    p.pa[pidx * D + d] = Ac;
+  }
+}
+
 // Second half of the cross-GPU exchange as a launch of its own (the attention kernel was launched push-only): wait until
 // every rank's rows of this exchange have arrived in this GPU's receive buffer, merge them, and advance the exchange number.
 // One CTA per query head; heads_per_group consecutive query heads share the flags of one (row, kv head) group.  After
@@ -1210,6 +1382,33 @@ extern "C" int gaac_paged_decode_attn(const gaac_paged* st, const int32_t* bt, i
                                       int B, int n_q, float scale, int nsplit, void* workspace, size_t workspace_bytes,
                                       void* out_bf16, float* out_f32, void* stream) {
   return paged_attn(st, bt, bt_stride, seq_lens, q_bf16, B, n_q, scale, nsplit, workspace, workspace_bytes, out_bf16, out_f32, nullptr, nullptr, 0, stream);
+}
+
+extern "C" int gaac_paged_decode_attn256(const gaac_paged* st, const int32_t* bt, int64_t bt_stride, const int32_t* seq_lens, const void* q_bf16,
+                                         int B, int n_q, float scale, int nsplit, void* workspace, size_t workspace_bytes,
+                                         void* out_bf16, float* out_f32, void* stream) {
+  if (!st || !bt || !seq_lens || !q_bf16 || !out_bf16 || !st->buf || !st->raw || !st->mt || !st->b3k || !st->b4k || !st->b3v || !st->b4v) return GAAC_E_ARG;
+  if (B <= 0 || n_q <= 0 || st->n_kv <= 0 || nsplit <= 0 || nsplit > 1024 || bt_stride <= 0) return GAAC_E_ARG;
+  if (st->n_kv % 2) return GAAC_E_UNSUPPORTED;                                // half-heads come in pairs
+  const int n_kv = st->n_kv / 2;                                              // 256-dim kv heads
+  if (n_q % n_kv || n_q / n_kv < 1 || n_q / n_kv > 8 || st->TS % 16 || st->TS != SLOT_OVF_OFF + st->ovf_slot) return GAAC_E_UNSUPPORTED;
+  if (!aligned16(st->buf) || (reinterpret_cast<uintptr_t>(st->raw) & 3) || (reinterpret_cast<uintptr_t>(q_bf16) & 3)) return GAAC_E_ALIGN;
+  AttnParams p{};
+  p.buf = st->buf; p.raw = (const uint16_t*)st->raw; p.mt = st->mt; p.bt = bt; p.bt_stride = bt_stride; p.TS = st->TS; p.ovf_slot = st->ovf_slot;
+  p.b3k = st->b3k; p.b4k = st->b4k; p.b3v = st->b3v; p.b4v = st->b4v; p.seq_len = seq_lens;
+  p.q = (const uint16_t*)q_bf16; p.B = B; p.n_q = n_q; p.n_kv = n_kv; p.G = n_q / n_kv; p.scale_log2 = scale * LOG2E; p.nsplit = nsplit;
+  if (int e = carve_workspace(workspace, workspace_bytes, B, 2 * n_q, nsplit, p)) return e;     // one partial per (query head, half)
+  cudaFuncSetAttribute(paged256_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATT256_SMEM);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(B * n_kv), (unsigned)nsplit); cfg.blockDim = dim3(ATT_THREADS);
+  cfg.dynamicSmemBytes = ATT256_SMEM; cfg.stream = (cudaStream_t)stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = g_launch_overlap;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, paged256_attn_kernel, p) != cudaSuccess) { cudaGetLastError(); return GAAC_E_LAUNCH; }
+  // the halves' partials are laid out as 2 * B * n_q heads of 128 dims, which is out [B, n_q, 256] after the merge
+  combine_kernel<<<(unsigned)(2 * B * n_q), 128, 0, (cudaStream_t)stream>>>(p.pm, p.pl, p.pa, nsplit, (uint16_t*)out_bf16, out_f32);
+  return launch_status();
 }
 
 // ---- test hooks: the same kernels, instantiated so that every rebuilt BF16 fragment is also written to memory

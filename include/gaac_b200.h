@@ -283,6 +283,16 @@ int gaac_paged_decode_attn(const gaac_paged* st, const int32_t* bt, int64_t bt_s
                            int B, int n_q, float scale, int nsplit, void* workspace, size_t workspace_bytes,
                            void* out_bf16, float* out_f32, void* stream);
 
+/* The same for head_dim 256: a 256-dim head is stored as two 128-dim half-heads in neighbouring tile slots, each with its own
+ * bases, so the store, the block decoder and the bases all see 2 * (256-dim kv heads) half-heads: st->n_kv is that number of
+ * HALF-heads (even), as for gaac_paged_store; the base tables have st->n_kv rows.  q [B, n_q, 256] bf16, out [B, n_q*256] bf16
+ * (out_f32 optional), n_q a multiple of st->n_kv / 2 with group size 1..8.  workspace: gaac_attn_workspace_bytes(B, 2 * n_q,
+ * nsplit) bytes.  Two launches (attention over warp pairs, then the split merge).  Replaces gaac_vpaged256_launch =
+ * gaac_vpaged256<G> + gaac_combine2 (gaac/vllm/paged_kernel256.py:40-283, 299-305). */
+int gaac_paged_decode_attn256(const gaac_paged* st, const int32_t* bt, int64_t bt_stride, const int32_t* seq_lens, const void* q_bf16,
+                              int B, int n_q, float scale, int nsplit, void* workspace, size_t workspace_bytes,
+                              void* out_bf16, float* out_f32, void* stream);
+
 /* ---------------------------------------------------------------------------------------------- test hooks */
 
 /* gaac_decode_attn / gaac_paged_decode_attn compiled so that every BF16 fragment word the kernel rebuilds on its way to the

@@ -65,6 +65,11 @@ def test_bad_arguments_are_rejected_before_any_launch(lib):
     assert lib.gaac_debug_decode_attn_rebuild(side, side, fake, None, 1, 8, 2, None, 16, 16, 0.1, 1, None, 0, 2, fake, 1 << 20, fake, None, None, fake, 32, None) == 1
     pg = _lib.Paged(0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 2, 3000, 120)
     assert lib.gaac_paged_decode_attn(pg, fake, 4, fake, fake, 1, 8, 0.1, 1, fake, 1 << 20, fake, None, None) == 2     # TS % 16
+    odd = _lib.Paged(0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 3, 3008, 128)
+    assert lib.gaac_paged_decode_attn256(odd, fake, 4, fake, fake, 1, 8, 0.1, 1, fake, 1 << 22, fake, None, None) == 2   # half-heads come in pairs
+    two = _lib.Paged(0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 2, 3008, 128)
+    assert lib.gaac_paged_decode_attn256(two, fake, 4, fake, fake, 1, 9, 0.1, 1, fake, 1 << 22, fake, None, None) == 2   # group of 9
+    assert lib.gaac_paged_decode_attn256(two, fake, 4, fake, fake, 1, 4, 0.1, 2, fake, 1024, fake, None, None) == 5      # workspace for 2 * n_q heads
 
 
 def test_missing_library_fails_loudly(monkeypatch):
