@@ -61,6 +61,24 @@ namespace gaac {
 #ifndef GAAC_ALU2FMA
 #define GAAC_ALU2FMA 0
 #endif
+//   GAAC_ABLATE   timing-only builds that compute WRONG results, to see where the time goes: 1 = no rebuild at all (fragments
+//                 taken from the staged bytes as they are), 2 = every group decoded as tier 0 (no tags, no escape bytes),
+//                 3 = raw tier compiled out
+#ifndef GAAC_ABLATE
+#define GAAC_ABLATE 0
+#endif
+//   GAAC_RAWPATCH 1: raw-tier groups are resolved by a short pass per tile that turns each of them into a table entry, after
+//                 which the group decoder has no branch at all; 0: the decoder branches on the raw tag of every group
+#ifndef GAAC_RAWPATCH
+#define GAAC_RAWPATCH 1
+#endif
+//   GAAC_DEEP     1: a warp's copies run a whole tile ahead: the stage it has just consumed is refilled at once with the tile after
+//                 the next one; 0: the next tile's copies are issued in the middle of the current tile (half a tile ahead).
+//                 Measured 2 % SLOWER at 1 (with and without the rebuild): the copies already arrive in time, the kernel waits
+//                 for instruction issue, not for memory
+#ifndef GAAC_DEEP
+#define GAAC_DEEP 0
+#endif
 constexpr int ATT_WARPS = GAAC_WARPS;
 constexpr int ATT_THREADS = ATT_WARPS * 32;
 constexpr int NSTAGE = 2;
@@ -86,7 +104,12 @@ constexpr int META_TILES = 512;                      // tiles of a CTA's range w
 constexpr int TB_LUTX = 0, TB_KB = 2048, TB_VB = TB_KB + 256, TB_META = TB_VB + 256, TB_LUTC = TB_META + 2 * META_TILES * 4;
 constexpr int TB_Q = TB_LUTC + (GAAC_LUTC ? 4096 * 4 : 0);          // query fragments: [4 K groups][32 lanes] x 16 bytes
 constexpr int TABLE_BYTES = TB_Q + (GAAC_QSMEM ? 4 * 32 * 16 : 0);
-constexpr int ATT_SMEM = TABLE_BYTES + ATT_WARPS * NSTAGE * STAGE_BYTES;
+// Raw-tier patch table of a warp: per side PATCH_MAX entries of 8 bytes = the two exponent addends of a raw group with the
+// 4-bit-window base already taken off (the decoder adds that base to every promoted group).  Tiles with more raw groups on a
+// side (random bit patterns) take the decoder that branches.
+constexpr int PATCH_MAX = 32, PATCH_BYTES = 2 * PATCH_MAX * 8;
+constexpr int WARP_SMEM = NSTAGE * STAGE_BYTES + PATCH_BYTES;
+constexpr int ATT_SMEM = TABLE_BYTES + ATT_WARPS * WARP_SMEM;
 static_assert(TABLE_BYTES % 16 == 0 && STAGE_BYTES % 16 == 0 && ST_KSM % 16 == 0 && ST_KCD % 16 == 0 && ST_KFL % 16 == 0 && ST_KESC % 16 == 0 &&
               ST_VSM % 16 == 0 && ST_VCD % 16 == 0 && ST_VFL % 16 == 0 && ST_VESC % 16 == 0 && ESC_COPY % 16 == 0 && ST_MBAR % 8 == 0 && SM_ROW % 16 == 0,
               "bulk copies need 16-byte aligned shared-memory destinations and sizes");
@@ -244,6 +267,10 @@ __device__ __forceinline__ void pv_words(WarpAcc& A, int w, const u32 (&u01)[4],
 #endif
 }
 
+// rowoff / total as scan_rows leaves them: escape bytes (low half) and raw groups (high half) before the row, or of the tile
+__device__ __forceinline__ int esc_part(int v) { return v & 0xFFFF; }
+__device__ __forceinline__ int raw_part(int v) { return v >> 16; }
+
 // Q^T B-fragments of the score product.  Lane (j, r) holds, for k-step s, the words q[head r][16s + 2j, +1] and
 // q[head r][16s + 2j + 8, +9]; K group g of a lane uses k-steps 2g and 2g + 1.
 #if GAAC_QSMEM
@@ -286,15 +313,28 @@ __device__ __forceinline__ u32 spread_hi5_dev(u32 u) {
 
 // Rebuild one group (two sign/mantissa words) into four bf16x2 words.  Same results as decode_group_lut (gaac_tile.h);
 // pos16 = es.off + escape position of the group, advanced past it on return; lutc = the 4096-entry code table.
-template <bool WIN>
+// RT (only with WIN): raw groups were turned into patch-table entries by build_raw_patches, which also left each entry's number in
+// the first payload byte of its group: the addends of EVERY group then come from one load, out of the escape-byte table
+// (byte = the 4-bit-window escape byte, or the zero byte) or out of the patch table (byte = entry number), chosen by address
+// arithmetic, and the decoder has no branch.  patch_rel = patch table address - escape-byte table address (shared memory).
+template <bool WIN, bool RT>
 __device__ __forceinline__ void decode_group_dev(u32 sm_lo, u32 sm_hi, u32 c24, u32 tg, int& pos16, const EscSrc<WIN>& es,
-                                                 const u32x2* lutx, const uint8_t* lutc, const u32x4& bw, u32 out[4]) {
+                                                 const u32x2* lutx, const uint8_t* lutc, const u32x4& bw, u32 out[4], u32 patch_rel = 0u) {
+  static_assert(WIN || !RT, "the patch table goes with the staged escape window");
   const u32 m1 = tg & 1u;                             // promoted (tags are 0, 1 or 3)
   u32 xe;
   if (WIN) xe = es.zp[m1 * (u32)pos16];               // raw groups read a payload byte here; their addends are replaced below
   else xe = m1 ? es.glob[pos16 - es.off] : 0u;
-  const u32x2 x = lutx[xe];
-  u32 x0 = x.x, x1 = x.y;
+  u32 x0, x1;
+  if (RT) {
+    const u32 r2 = tg & 2u;                           // 2 for a raw group
+    const u32x2 x = *reinterpret_cast<const u32x2*>(reinterpret_cast<const uint8_t*>(lutx) + (8u * xe + r2 * (patch_rel >> 1)));
+    x0 = x.x; x1 = x.y;
+    pos16 += (int)(2u * r2);                          // a raw payload is five bytes: four here, one below with every promoted group
+  } else {
+    const u32x2 x = lutx[xe];
+    x0 = x.x; x1 = x.y;
+  }
 #if GAAC_LUTC == 1
   const u32 c_lo = *reinterpret_cast<const u32*>(lutc + ((c24 << 2) & 0x3FFCu));
   const u32 c_hi = *reinterpret_cast<const u32*>(lutc + ((c24 >> 10) & 0x3FFCu));
@@ -316,7 +356,11 @@ __device__ __forceinline__ void decode_group_dev(u32 sm_lo, u32 sm_hi, u32 c24, 
   const u32 c_lo = mad_k<31u>(xl & 0x00380038u, xl), c_hi = mad_k<31u>(xh & 0x00380038u, xh);
 #endif
   const u32 blo = bw.x + m1 * bw.z, bhi = bw.y + m1 * bw.w;
-  if (tg & 2u) {                                      // raw exponents: e = code | hi5 << 3 (the base must not contribute)
+#if GAAC_ABLATE == 3
+  if (false) {
+#else
+  if (!RT && (tg & 2u)) {                             // raw exponents: e = code | hi5 << 3 (the base must not contribute)
+#endif
     u32 w0, w1; int sh;
     if (WIN) {
       const u32 a = (u32)__cvta_generic_to_shared(es.zp) + (u32)pos16;
@@ -352,9 +396,9 @@ __device__ __forceinline__ void decode_group_dev(u32 sm_lo, u32 sm_hi, u32 c24, 
 // lanes 0-15.
 // dump (debug instantiation only): where token 0 of this tile goes in the [token][128] dump of the head; every lane writes the
 // fragment words it rebuilt at the (token, channel) pairs they stand for, rows >= nvalid are left alone.
-template <bool WIN, bool DUMP>
+template <bool WIN, bool DUMP, bool RT = false>
 __device__ __forceinline__ void k_scores(float* sc, const uint8_t* stage, const uint8_t* tables, const EscSrc<WIN>& es, u32 flrow, int rowoff,
-                                         int lane, const QFrag& Q, uint16_t* dump = nullptr, int nvalid = T) {
+                                         int lane, const QFrag& Q, uint16_t* dump = nullptr, int nvalid = T, u32 patch_rel = 0u) {
   const int j = lane & 3, r = lane >> 2;
   const u32x2* lutx = reinterpret_cast<const u32x2*>(tables + TB_LUTX);
   u32 t8[2]; int pos[2]; uint4 s0[2], s1[2]; u32 cd[2][3];
@@ -362,7 +406,7 @@ __device__ __forceinline__ void k_scores(float* sc, const uint8_t* stage, const 
 #pragma unroll
   for (int o = 0; o < 2; o++) {
     const u32 fl = __shfl_sync(FULLM, flrow, 8 * o + r);
-    pos[o] = __shfl_sync(FULLM, rowoff, 8 * o + r) + esc_prefix(fl, 8 * j) + es.off;
+    pos[o] = esc_part(__shfl_sync(FULLM, rowoff, 8 * o + r)) + esc_prefix(fl, 8 * j) + es.off;
     t8[o] = fl >> (8 * j);
     s0[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + (8 * o + (lane >> 2)) * SM_ROW + 32 * (lane & 3));   // storage order, skewed rows
     s1[o] = *reinterpret_cast<const uint4*>(stage + ST_KSM + (8 * o + (lane >> 2)) * SM_ROW + 32 * (lane & 3) + 16);
@@ -377,7 +421,13 @@ __device__ __forceinline__ void k_scores(float* sc, const uint8_t* stage, const 
     for (int o = 0; o < 2; o++) {
       const u32 smlo = g == 0 ? s0[o].x : g == 1 ? s0[o].z : g == 2 ? s1[o].x : s1[o].z;
       const u32 smhi = g == 0 ? s0[o].y : g == 1 ? s0[o].w : g == 2 ? s1[o].y : s1[o].w;
-      decode_group_dev<WIN>(smlo, smhi, k_group_codes(cd[o], g), t8[o] >> (2 * g), pos[o], es, lutx, tables + TB_LUTC, bw, f[o]);
+#if GAAC_ABLATE == 1
+      f[o][0] = smlo; f[o][1] = smhi; f[o][2] = smlo ^ cd[o][0]; f[o][3] = smhi ^ cd[o][g % 3];
+#elif GAAC_ABLATE == 2
+      decode_group_dev<WIN, RT>(smlo, smhi, k_group_codes(cd[o], g), 0u, pos[o], es, lutx, tables + TB_LUTC, bw, f[o], patch_rel);
+#else
+      decode_group_dev<WIN, RT>(smlo, smhi, k_group_codes(cd[o], g), t8[o] >> (2 * g), pos[o], es, lutx, tables + TB_LUTC, bw, f[o], patch_rel);
+#endif
     }
     if (DUMP) {
 #pragma unroll
@@ -397,9 +447,9 @@ __device__ __forceinline__ void k_scores(float* sc, const uint8_t* stage, const 
 }
 
 // O^T += V^T . P^T for one compressed V tile.  flrow / rowoff of V row (lane & 15) are held by lanes 16-31.
-template <bool WIN, bool DUMP>
+template <bool WIN, bool DUMP, bool RT = false>
 __device__ __forceinline__ void v_accum(WarpAcc& A, const uint8_t* stage, const uint8_t* tables, const EscSrc<WIN>& es, u32 flrow, int rowoff,
-                                        int lane, const PFrag& P, uint16_t* dump = nullptr, int nvalid = T) {
+                                        int lane, const PFrag& P, uint16_t* dump = nullptr, int nvalid = T, u32 patch_rel = 0u) {
   const int j = lane & 3, r = lane >> 2;
   const u32x2* lutx = reinterpret_cast<const u32x2*>(tables + TB_LUTX);
   u32 t4[4]; int pos[4]; uint4 sm[4]; u32 cd[6];
@@ -407,7 +457,7 @@ __device__ __forceinline__ void v_accum(WarpAcc& A, const uint8_t* stage, const 
   for (int t = 0; t < 4; t++) {
     const int tok = 2 * j + (t & 1) + 8 * (t >> 1);
     const u32 fl = __shfl_sync(FULLM, flrow, 16 + tok);
-    pos[t] = __shfl_sync(FULLM, rowoff, 16 + tok) + esc_prefix(fl, 4 * r) + es.off;
+    pos[t] = esc_part(__shfl_sync(FULLM, rowoff, 16 + tok)) + esc_prefix(fl, 4 * r) + es.off;
     t4[t] = fl >> (4 * r);
     sm[t] = *reinterpret_cast<const uint4*>(stage + ST_VSM + (lane >> 1) * SM_ROW + 64 * (lane & 1) + 16 * t);
   }
@@ -423,7 +473,13 @@ __device__ __forceinline__ void v_accum(WarpAcc& A, const uint8_t* stage, const 
 #pragma unroll
     for (int t = 0; t < 4; t++) {
       const u32 smlo = g == 0 ? sm[t].x : sm[t].z, smhi = g == 0 ? sm[t].y : sm[t].w;
-      decode_group_dev<WIN>(smlo, smhi, v_group_codes(cd, t, g), t4[t] >> (2 * g), pos[t], es, lutx, tables + TB_LUTC, bw, f[t]);
+#if GAAC_ABLATE == 1
+      f[t][0] = smlo; f[t][1] = smhi; f[t][2] = smlo ^ cd[g]; f[t][3] = smhi ^ cd[g + 3];
+#elif GAAC_ABLATE == 2
+      decode_group_dev<WIN, RT>(smlo, smhi, v_group_codes(cd, t, g), 0u, pos[t], es, lutx, tables + TB_LUTC, bw, f[t], patch_rel + PATCH_MAX * 8);
+#else
+      decode_group_dev<WIN, RT>(smlo, smhi, v_group_codes(cd, t, g), t4[t] >> (2 * g), pos[t], es, lutx, tables + TB_LUTC, bw, f[t], patch_rel + PATCH_MAX * 8);
+#endif
     }
     if (DUMP) {
 #pragma unroll
@@ -454,11 +510,45 @@ __device__ __forceinline__ void scan_rows(const uint8_t* stage, bool rawk, bool 
   const int row = lane & 15;
   const bool isv = lane >= 16;
   flrow = (isv ? rawv : rawk) ? 0u : *reinterpret_cast<const u32*>(stage + (isv ? ST_VFL : ST_KFL) + 4 * row);
-  const int sz = row_esc_bytes(flrow);
+  // one scan for two prefixes: escape bytes in the low half, raw groups in the high half (a tile has at most 1280 and 256 of them)
+  const int sz = row_esc_bytes(flrow) + (popc(flrow & 0xAAAAAAAAu) << 16);
   int inc = sz;
 #pragma unroll
   for (int d = 1; d < 16; d <<= 1) { int v = __shfl_up_sync(FULLM, inc, d, 16); if (row >= d) inc += v; }
   rowoff = inc - sz; total = inc;
+}
+
+// Turn the raw-tier groups of a staged tile into patch-table entries, so that the group decoder needs no branch.  Lanes 0-15
+// own the K rows, lanes 16-31 the V rows (as in scan_rows); a lane walks the raw groups of its row.  For each one: read the
+// five payload bytes from the staged escape window, spread the 5-bit fields to byte positions, take off the 4-bit-window base
+// words (the decoder adds them to every promoted group), store the two words as entry k of the side's patch table, and write k
+// over the first payload byte, which is where the decoder looks for a promoted group's escape byte.  k = number of raw
+// groups before this one on the tile side (rows in order, groups ascending).  side_on[0/1]: whether the K / V side takes part.
+__device__ __forceinline__ void build_raw_patches(uint8_t* stage, const uint8_t* tables, uint8_t* patch, int off_k, int off_v, bool on_k, bool on_v,
+                                                  u32 flrow, int rowoff, int lane) {
+  const bool isv = lane >= 16;
+  u32 rb = (isv ? on_v : on_k) ? (flrow & 0xAAAAAAAAu) : 0u;
+  uint8_t* win = stage + ST_ZERO + (isv ? off_v : off_k);           // the tile side's first escape byte
+  const uint8_t* bws = tables + (isv ? TB_VB : TB_KB);
+  u32x2* ptab = reinterpret_cast<u32x2*>(patch + (isv ? PATCH_MAX * 8 : 0));
+  while (__any_sync(FULLM, rb != 0u)) {
+    if (rb) {
+      const int bit = __ffs(rb) - 1, g = bit >> 1;                  // raw bit of group g is bit 2g + 1
+      rb &= rb - 1u;
+      const u32 below = flrow & ((1u << (bit - 1)) - 1u);            // tag bits of the groups before g
+      const int pos = esc_part(rowoff) + popc(below & 0x55555555u) + 4 * popc(below & 0xAAAAAAAAu);
+      const int k = raw_part(rowoff) + popc(below & 0xAAAAAAAAu);
+      uint8_t* pl = win + pos;
+      const u32 a = (u32)__cvta_generic_to_shared(pl);
+      const int sh = 8 * (int)(a & 3u);
+      const u32 w0 = *reinterpret_cast<const u32*>(pl - (a & 3u)), w1 = *reinterpret_cast<const u32*>(pl - (a & 3u) + 4);
+      const u32 lo = funnel_r(w0, w1, sh), hi = w1 >> sh;            // bytes 0-3 and byte 4 of the payload
+      const u32x4 bw = *reinterpret_cast<const u32x4*>(bws + 16 * g);
+      ptab[k] = u32x2{spread_hi5_dev(lo & 0xFFFFFu) - (bw.x + bw.z), spread_hi5_dev(funnel_r(lo, hi, 20) & 0xFFFFFu) - (bw.y + bw.w)};
+      *pl = (uint8_t)k;
+    }
+  }
+  __syncwarp();
 }
 
 // Scores of a raw BF16 tile [16][128] in global memory (rows >= nvalid are not read).
@@ -570,7 +660,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
 
   // ---- addressing of this lane, and the copies of the warp's first tile: they are put in flight before the CTA builds its
   // tables so that the first tile arrives while the tables are written
-  uint8_t* ring = smem + TABLE_BYTES + warp * (NSTAGE * STAGE_BYTES);
+  uint8_t* ring = smem + TABLE_BYTES + warp * WARP_SMEM;
   const u32 ring_s = (u32)__cvta_generic_to_shared(ring);
   LaneAddr L;
   L.ohk = ohk; L.ohv = ohv;
@@ -596,6 +686,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
   };
   auto bulk_issue = [&](u32 st, int tile, const TileMeta& m) {                  // executed by lane 0
     const u32 mb = st + ST_MBAR;
+    // the stage may have been written through ordinary stores (patch numbers in its escape window): order those before the
+    // copy engine's writes to the same bytes
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     if (PAGED) {
       const u32 n = (u32)min(p.TS, SLOT_OVF_OFF + ESC_COPY);                    // a slot is one contiguous piece, escapes included
       mbar_expect_tx(mb, (m.mk >= 0 ? n : 0u) + (m.mv >= 0 ? n : 0u));
@@ -730,6 +823,17 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
   // of the shared-memory atomic; the copies of the next tile are issued between the K half and the V half.
   int stg = 0;
   u32 phase = 0;                                       // bit s: parity of the phase of stage s that is waited for next
+#if GAAC_DEEP
+  // the warp's second tile goes into the other stage right away; from then on the stage a tile leaves is refilled, as soon as the
+  // tile is done, with the tile after the next one, so the copies of a tile have a whole tile's time to arrive
+  int tile_b = thi; TileMeta meta_b{0, 0};
+  if (tile < thi) {
+    int t = 0;
+    if (lane == 0) t = atomicAdd(&s_next, 1);
+    tile_b = __shfl_sync(FULLM, t, 0);
+    if (tile_b < thi) { meta_b = meta_of(tile_b); if (lane == 0) bulk_issue(ring_s + STAGE_BYTES, tile_b, meta_b); }
+  }
+#endif
   while (tile < thi) {
     int t1 = 0;
     if (lane == 0) t1 = atomicAdd(&s_next, 1);
@@ -743,12 +847,24 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     const bool rawk = PAGED && cur.mk < 0, rawv = PAGED && cur.mv < 0;
     u32 flrow; int rowoff, total;
     scan_rows(stage, rawk, rawv, lane, flrow, rowoff, total);
+    // which decoder each side takes: the staged window (branch-free, raw groups through the patch table) when the side's escape
+    // bytes all fit the window and it has at most PATCH_MAX raw groups; else the one that reads escapes from global memory
+    int off_k = 0, off_v = 0, avail_k = 0, avail_v = 0;
+    if (!rawk) staged_escapes(false, cur.mk, off_k, avail_k);
+    if (!rawv) staged_escapes(true, cur.mv, off_v, avail_v);
+    const int tot_k = __shfl_sync(FULLM, total, 15), tot_v = __shfl_sync(FULLM, total, 31);
+    const bool win_k = !rawk && esc_part(tot_k) + 8 <= avail_k && (!GAAC_RAWPATCH || raw_part(tot_k) <= PATCH_MAX);     // +8: a raw payload is read as two aligned words
+    const bool win_v = !rawv && esc_part(tot_v) + 8 <= avail_v && (!GAAC_RAWPATCH || raw_part(tot_v) <= PATCH_MAX);
+    uint8_t* const patch = ring + NSTAGE * STAGE_BYTES;
+    const u32 patch_rel = (u32)(patch - (smem + TB_LUTX));
+#if GAAC_RAWPATCH
+    if ((win_k && raw_part(tot_k) > 0) || (win_v && raw_part(tot_v) > 0))
+      build_raw_patches(ring + stg * STAGE_BYTES, smem, patch, off_k, off_v, win_k, win_v, flrow, rowoff, lane);
+#endif
     float sc[4] = {0.f, 0.f, 0.f, 0.f};
     if (!rawk) {
-      int off, avail;
-      staged_escapes(false, cur.mk, off, avail);
-      if (__shfl_sync(FULLM, total, 15) + 8 <= avail)                                         // +8: a raw payload is read as two aligned words
-        k_scores<true, DUMP>(sc, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off}, flrow, rowoff, lane, Q, dump_k + (long)tile * T * D, nvalid);
+      if (win_k)
+        k_scores<true, DUMP, GAAC_RAWPATCH != 0>(sc, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off_k}, flrow, rowoff, lane, Q, dump_k + (long)tile * T * D, nvalid, patch_rel);
       else
         k_scores<false, DUMP>(sc, stage, smem, EscSrc<false>{nullptr, global_escapes(false, cur.mk), 0}, flrow, rowoff, lane, Q, dump_k + (long)tile * T * D, nvalid);
     } else {
@@ -756,25 +872,31 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     }
     t1 = __shfl_sync(FULLM, t1, 0);
     TileMeta nxt{0, 0};
+#if !GAAC_DEEP
     if (t1 < thi) {
       nxt = meta_of(t1);
       const u32 st = ring_s + (stg ^ 1) * STAGE_BYTES;
       if (lane == 0) bulk_issue(st, t1, nxt);
     }
+#endif
     PFrag P;
     if (nvalid == T) softmax_step<true>(A, sc, p.scale_log2, nvalid, lane, P);
     else softmax_step<false>(A, sc, p.scale_log2, nvalid, lane, P);
     if (!rawv) {
-      int off, avail;
-      staged_escapes(true, cur.mv, off, avail);
-      if (__shfl_sync(FULLM, total, 31) + 8 <= avail)
-        v_accum<true, DUMP>(A, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off}, flrow, rowoff, lane, P, dump_v + (long)tile * T * D, nvalid);
+      if (win_v)
+        v_accum<true, DUMP, GAAC_RAWPATCH != 0>(A, stage, smem, EscSrc<true>{stage + ST_ZERO, nullptr, off_v}, flrow, rowoff, lane, P, dump_v + (long)tile * T * D, nvalid, patch_rel);
       else
         v_accum<false, DUMP>(A, stage, smem, EscSrc<false>{nullptr, global_escapes(true, cur.mv), 0}, flrow, rowoff, lane, P, dump_v + (long)tile * T * D, nvalid);
     } else {
       raw_accum<DUMP>(A, p.raw + (long)(~cur.mv) * (T * D), nvalid, lane, P, dump_v + (long)tile * T * D);
     }
+#if GAAC_DEEP
+    __syncwarp();                                      // every lane has read what it needs of this stage
+    if (t1 < thi) { nxt = meta_of(t1); if (lane == 0) bulk_issue(ring_s + stg * STAGE_BYTES, t1, nxt); }
+    cur = meta_b; tile = tile_b; meta_b = nxt; tile_b = t1; stg ^= 1;
+#else
     cur = nxt; stg ^= 1; tile = t1;
+#endif
   }
   // ---- slot layout: the raw BF16 tail belongs to the last split's warp 0
   if (!PAGED && TL > 0 && split == p.nsplit - 1 && warp == 0) {
@@ -964,7 +1086,7 @@ constexpr int T256_HALF = 2048 + 256 + 256;                       // per half: e
 constexpr int XCH_PAR_BYTES = 2 * 32 * 16 + 16;                    // one parity: two halves x 32 lanes x float4, then {next tile, fail flag of half 0, of half 1, -}
 constexpr int T256_XCH = 2 * T256_HALF;
 constexpr int TABLE256_BYTES = T256_XCH + (ATT_WARPS / 2) * 2 * XCH_PAR_BYTES;
-constexpr int ATT256_SMEM = TABLE256_BYTES + ATT_WARPS * NSTAGE * STAGE_BYTES;
+constexpr int ATT256_SMEM = TABLE256_BYTES + ATT_WARPS * WARP_SMEM;
 static_assert(TB_KB == 2048 && TB_VB == 2048 + 256 && TABLE256_BYTES % 16 == 0 && ATT256_SMEM + 64 <= 232448, "table layout shared with the 128-dim kernel; one CTA per SM");
 
 __global__ void __launch_bounds__(ATT_THREADS, 1) paged256_attn_kernel(const __grid_constant__ AttnParams p) {
@@ -979,7 +1101,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) paged256_attn_kernel(const __g
   const int S = __shfl_sync(FULLM, p.seq_len[b], 0);
   const int ntiles = (S + 15) >> 4, chunk = (ntiles + p.nsplit - 1) / p.nsplit;
   const int tlo = min(split * chunk, ntiles), thi = min(tlo + chunk, ntiles);
-  uint8_t* ring = smem + TABLE256_BYTES + warp * (NSTAGE * STAGE_BYTES);
+  uint8_t* ring = smem + TABLE256_BYTES + warp * WARP_SMEM;
   const u32 ring_s = (u32)__cvta_generic_to_shared(ring);
   const uint8_t* tables = smem + hf * T256_HALF;
   uint8_t* xch = smem + T256_XCH + pair * (2 * XCH_PAR_BYTES);
@@ -1052,7 +1174,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) paged256_attn_kernel(const __g
     if (ok) {
       scan_rows(stage, rawk, rawv, lane, flrow, rowoff, total);
       if (!rawk) {
-        if (__shfl_sync(FULLM, total, 15) + 8 <= esc_avail)
+        if (esc_part(__shfl_sync(FULLM, total, 15)) + 8 <= esc_avail)
           k_scores<true, false>(sc, stage, tables, EscSrc<true>{stage + ST_ZERO, nullptr, esc_off}, flrow, rowoff, lane, Q);
         else
           k_scores<false, false>(sc, stage, tables, EscSrc<false>{nullptr, p.buf + (long)cur.mk * p.TS + SLOT_OVF_OFF, 0}, flrow, rowoff, lane, Q);
@@ -1076,7 +1198,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) paged256_attn_kernel(const __g
     if (nvalid == T) softmax_step<true>(A, sc, p.scale_log2, nvalid, lane, P);
     else softmax_step<false>(A, sc, p.scale_log2, nvalid, lane, P);
     if (!rawv) {
-      if (__shfl_sync(FULLM, total, 31) + 8 <= esc_avail)
+      if (esc_part(__shfl_sync(FULLM, total, 31)) + 8 <= esc_avail)
         v_accum<true, false>(A, stage, tables, EscSrc<true>{stage + ST_ZERO, nullptr, esc_off_v}, flrow, rowoff, lane, P);
       else
         v_accum<false, false>(A, stage, tables, EscSrc<false>{nullptr, p.buf + (long)cur.mv * p.TS + SLOT_OVF_OFF, 0}, flrow, rowoff, lane, P);
