@@ -1,4 +1,4 @@
-"""Time the UNMODIFIED reference package on this GPU, beside gaac_b200, on bench.py's workload (config 1).
+"""Time the UNMODIFIED reference package on this GPU, beside gaac_b200, on the headline workload of bench.py (batch 1, 32 q / 8 kv heads, 65536 tokens).
 
 The reference is installed, as it is, under baseline/_ref (`pip install --no-deps --target baseline/_ref <reference checkout>`)
 and its JIT extension `gaac_attn_v1` is prebuilt for sm_100a under baseline/_ref/_torch_ext by build_reference.py, so

@@ -14,6 +14,7 @@ __global__ void __launch_bounds__(ENC_WARPS * 32) encode_tiles_kernel(
     const int* __restrict__ bidx, int n_kv, uint8_t* __restrict__ sm, uint8_t* __restrict__ codes, int* __restrict__ flags,
     uint8_t* __restrict__ slots, int* __restrict__ tile_bytes, int ntiles) {
   __shared__ __align__(16) WarpScratch scratch[ENC_WARPS];
+  __shared__ __align__(16) uint8_t esc_stage[ENC_WARPS][TILE_MAX_ESC];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long h = blockIdx.y;
   WarpScratch& ws = scratch[warp];
@@ -32,7 +33,15 @@ __global__ void __launch_bounds__(ENC_WARPS * 32) encode_tiles_kernel(
     const long trow = h * S_pad + row0;
     store_tile_payload<KIND_V>(lt, sm + trow * D, codes + trow * CB, lane);
     if (lane < T) flags[trow + lane] = (int)ws.fl[lane];
-    store_tile_escapes<KIND_V>(ws, lt, slots + (h * ntiles + tile) * (long)TILE_MAX_ESC, lane);
+    // escape bytes: gathered in shared memory with byte stores (every lane at its own positions), then written to the tile's
+    // scratch slot as whole words by neighbouring lanes, so the slot costs one or two coalesced stores instead of ~50 byte stores
+    store_tile_escapes<KIND_V>(ws, lt, esc_stage[warp], lane);
+    __syncwarp();
+    {
+      u32* dst = reinterpret_cast<u32*>(slots + (h * ntiles + tile) * (long)TILE_MAX_ESC);
+      const u32* src = reinterpret_cast<const u32*>(esc_stage[warp]);
+      for (int k = lane; 4 * k < total; k += 32) dst[k] = src[k];
+    }
     if (lane == 0) tile_bytes[h * ntiles + tile] = total;
   }
 }

@@ -143,3 +143,39 @@ def test_capacity_and_growth_rules():
     cache.growable = False
     with pytest.raises(RuntimeError, match="escape stream"):
         cache.check_capacity(used=cache.k.ovf_cap)
+
+
+def test_append_never_writes_outside_a_heads_escape_share():
+    """A cache whose escape streams are far too small for the data (random bit patterns: 1280 escape bytes per tile against 8 reserved)
+    and a caller that never runs check_capacity: the appends that complete a tile must refuse it instead of writing into the next
+    head's share.  The refused tiles are counted, the head's counters stay where they were, and a neighbouring slot filled with
+    ordinary data still decompresses bit for bit."""
+    import torch
+    from gaac_b200 import CompressedKVCache
+    cache = CompressedKVCache(n_slots=3, n_kv=2, capacity=256, bases=_bases2(), ovf_bytes_per_tile=8)
+    good_k, good_v = _tok(O.kv_like(2, 37, 5)), _tok(O.kv_like(2, 37, 6))
+    for s in (0, 2):
+        cache.prefill(s, to_bf16_cuda(good_k), to_bf16_cuda(good_v))                  # may grow the streams: that is prefill's job
+    cap_before = cache.k.ovf_cap
+    cache.growable = False
+    rng = np.random.default_rng(3)
+    slots = torch.tensor([1], dtype=torch.int32, device="cuda")
+    for step in range(160):                                                       # ten tiles' worth of junk into slot 1: 12.8 KB of escapes per head
+        junk = rng.integers(0, 65536, (1, 2, 128)).astype(np.uint16)
+        junk = np.where(((junk >> 7) & 0xFF) >= 0x86, junk & ~np.uint16(0x4000), junk)
+        cache.append(slots, to_bf16_cuda(junk), to_bf16_cuda(junk))
+    torch.cuda.synchronize()
+    stored_tiles = int(cache.S[2]) // 16                                          # head 2 = first head of slot 1
+    assert int(cache.append_errors) > 0 and 0 < stored_tiles < 10                 # the stream filled up; the tiles after that were refused
+    assert cache.k.ovf_cap == cap_before
+    assert int(cache.k.ovf_used.max()) + 8 <= cache.k.ovf_cap and int(cache.v.ovf_used.max()) + 8 <= cache.v.ovf_cap
+    for s in (0, 2):
+        dk, dv = cache.decompress(s)
+        assert np.array_equal(bits(dk), good_k) and np.array_equal(bits(dv), good_v)
+
+
+def _bases2():
+    import torch
+    k, v = _tok(O.kv_like(2, 2048, 11)), _tok(O.kv_like(2, 2048, 12))
+    k3, k4 = O.bases_from_hist(O.exponent_hist_fast(k, 2), 2); v3, v4 = O.bases_from_hist(O.exponent_hist_fast(v, 2), 2)
+    return {n: torch.from_numpy(a) for n, a in (("k3", k3), ("k4", k4), ("v3", v3), ("v4", v4))}
