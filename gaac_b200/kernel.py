@@ -6,6 +6,7 @@ reference (its slot cache) work unchanged.  One kernel launch does split-K flash
 tail and the merge of the splits.
 """
 from __future__ import annotations
+import functools
 import torch
 from . import _lib
 
@@ -39,14 +40,17 @@ def choose_nsplit(B: int, n_kv: int, S: int, target_ctas: int = 96, min_tok: int
     return min(max(1, target_ctas // (B * n_kv)), max(1, S // min_tok), cap)
 
 
+@functools.lru_cache(maxsize=4096)
 def choose_nsplit_sm100(B: int, n_kv: int, S: int, sm_count: int = SM_COUNT_B200, min_tiles_per_warp: int = 2, ragged: bool = False,
                         total_tokens: int | None = None) -> int:
-    """Splits per (row, kv head) for a B200.  The kernel runs one 16-warp CTA per SM.
+    """Splits per (row, kv head) for a B200.  The kernel runs one 16-warp CTA per SM; a CTA keeps the metadata of the first
+    META_TILES (512) tiles of its range in shared memory and fetches the rest from global memory inside the loop.
 
-    Equal lengths (S is every row's length), few rows (B*n_kv up to half the SMs): fill the SMs in one wave, while every warp of
-    a CTA keeps at least min_tiles_per_warp 16-token tiles so the per-CTA prologue and merge stay amortised.
-    Equal lengths, many rows: the grid runs in several waves; the split count minimises
-    waves x (tiles per CTA / 16 warps x tile time + per-CTA fixed cost).
+    Equal lengths (S is every row's length): the split count minimises a cost model fitted to measurements,
+        waves x ((tiles per warp + 0.5) x tile time + per-CTA fixed cost),   waves = ceil(rows x splits / SMs),
+    over the counts that leave every warp at least min_tiles_per_warp 16-token tiles.  Tile time: 4.5 us for a tile whose
+    metadata is staged, 5.2 us beyond; fixed cost (prologue, warp merge, split merge): 10 us.  Few rows end up with one wave that
+    fills the SMs, many rows with ranges of at most 512 tiles in several waves.
     Ragged lengths (ragged=True, S is the longest row, total_tokens the sum over the batch rows when known, else rows are taken
     to average 55 % of the longest): every row gets the same split count, so the longest row's chunks must be small against an
     SM's share of the whole batch for the block scheduler to even the SMs out: a third of that share, and at most 512 tiles."""
@@ -57,13 +61,14 @@ def choose_nsplit_sm100(B: int, n_kv: int, S: int, sm_count: int = SM_COUNT_B200
         mean_tiles = (total_tokens / max(1, B) / 16.0) if total_tokens else 0.55 * ntiles
         per_sm = max(1.0, rows * mean_tiles / sm_count)
         return max(1, min(most, max(-(-ntiles // 512), int(-(-3 * ntiles // per_sm)))))
-    if 2 * rows <= sm_count:
-        return max(1, min(sm_count // rows, most))
-    tile_us, fixed_us, best, best_t = 4.4, 10.0, 1, None              # measured: time of one tile pair in a full CTA, prologue + merges
-    for ns in range(1, min(most, 32) + 1):
+    tile_us, tile_far_us, fixed_us, staged = 4.5, 5.2, 10.0, 512
+    best, best_t = 1, None
+    for ns in range(1, min(most, 2 * sm_count) + 1):
+        chunk = -(-ntiles // ns)
         waves = -(-rows * ns // sm_count)
-        t = waves * (-(-ntiles // ns) / ATT_WARPS * tile_us + fixed_us)
-        if best_t is None or t < best_t * 0.97:                        # prefer fewer splits unless clearly better
+        near, far = min(chunk, staged), max(0, chunk - staged)
+        t = waves * (near / ATT_WARPS * tile_us + far / ATT_WARPS * tile_far_us + 0.5 * tile_us + fixed_us)   # tiles are handed out on demand: warps end half a tile apart
+        if best_t is None or t < best_t * 0.985:                       # prefer fewer splits unless clearly better
             best, best_t = ns, t
     return best
 

@@ -99,6 +99,8 @@ def test_split_count_heuristics():
     assert choose_nsplit_sm100(1, 8, 65536) == 18           # 144 CTAs
     assert choose_nsplit_sm100(1, 8, 8192) == 16            # at least two tiles per warp
     assert choose_nsplit_sm100(1, 1, 100) == 1
-    assert choose_nsplit_sm100(64, 1, 32768) == 2           # one wave of 128 CTAs
+    assert choose_nsplit_sm100(64, 1, 32768) == 9           # four full waves of ranges whose metadata fits the staged table
+    assert choose_nsplit_sm100(64, 2, 32768) == 8           # 1024 CTAs = 6.9 waves of 256-tile ranges (measured best of 1, 2, 4, 8, 15)
+    assert choose_nsplit_sm100(1, 1, 65536) == 128          # two tiles per warp
     assert choose_nsplit_sm100(16, 8, 65536, ragged=True) == 8
     assert choose_nsplit_sm100(256, 8, 4096) == 1
