@@ -898,7 +898,7 @@ def run_batch64(args):
                                    "ms_for_64_layers_scaled": prefill_ms / args.prefill_layers * n_layers_model, "scale_factor": n_layers_model / args.prefill_layers,
                                    "gbs_in_plus_out": (in_bytes + out_bytes) * args.prefill_layers / (prefill_ms * 1e-3) / 1e9,
                                    "blocks_per_s": tiles_layer * args.prefill_layers / (prefill_ms * 1e-3), "host_wall_ms_per_layer": prefill_wall * 1e3 / args.prefill_layers,
-                                   "how": "CompressedKVCache.prefill, one call per sequence and layer (64 calls per layer, each with one host read of the escape sizes); per rank"},
+                                   "how": "CompressedKVCache.prefill, one call per sequence and layer (64 calls per layer, each one library call and one host read of its status words); per rank"},
                 "encode_whole_layer": enc,
                 "e2e": {"value": e2e_us, "unit": "us/layer", "h2d_bytes_per_step": int(hk.numel() * 2 * 2 + hq.numel() * 2), "d2h_bytes_per_step": int(ho.numel() * 2)},
                 "gpu_launches": 2 * args.steps, "clocks": clk.summary(c_from, c_to)}

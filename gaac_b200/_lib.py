@@ -62,6 +62,8 @@ _SIGNATURES = {
     "gaac_decode_attn_push": (i32, [C.POINTER(Side), C.POINTER(Side), vp, vp, i32, i32, i32, vp, i64, f32, i32, vp, i32, i32, vp, sz, C.POINTER(Exchange), vp]),
     "gaac_exchange_merge": (i32, [C.POINTER(Exchange), i64, i32, vp, vp, vp]),
     "gaac_append_kv": (i32, [C.POINTER(Store), C.POINTER(Store), vp, vp, vp, i32, i32, vp, vp, i64, i64, i32, vp, vp]),
+    "gaac_cache_prefill_scratch_bytes": (C.c_size_t, [i64, i32]),
+    "gaac_cache_prefill": (i32, [C.POINTER(Store), C.POINTER(Store), vp, vp, i64, i64, i32, i32, vp, vp, i64, i64, i32, vp, C.c_size_t, vp, i32, vp]),
     "gaac_paged_store": (i32, [C.POINTER(Paged), vp, vp, i64, i64, vp, i32, vp, vp]),
     "gaac_paged_release": (i32, [C.POINTER(Paged), vp, i32, vp]),
     "gaac_paged_decode_blocks": (i32, [C.POINTER(Paged), vp, i32, vp, vp, i64, vp]),
@@ -72,7 +74,7 @@ _SIGNATURES = {
     "gaac_static_workspace_error": (i32, [vp, i32, vp]),
 }
 EXPORTS = tuple(_SIGNATURES)
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 
 def lib():

@@ -7,12 +7,13 @@ namespace gaac {
 constexpr int ENC_WARPS = 4;          // warps per CTA
 constexpr int ENC_TILES_PER_WARP = 4; // consecutive work items of one warp share the head's base words
 
-// One warp per (head, tile).  grid = (ceil(ntiles / (ENC_WARPS*ENC_TILES_PER_WARP)), H).
+// One warp per (head, tile).  grid = (ceil(ntiles / (ENC_WARPS*ENC_TILES_PER_WARP)), H).  Token t of head h is read at
+// x + h * x_head_stride + t * x_row_stride (bf16 elements): head-major [H, S_in, 128] or token-major [L, n_kv, 128] input.
 template <int KIND_V>
 __global__ void __launch_bounds__(ENC_WARPS * 32) encode_tiles_kernel(
-    const uint16_t* __restrict__ x, long S, long S_in, long S_pad, const uint8_t* __restrict__ base3, const uint8_t* __restrict__ base4,
-    const int* __restrict__ bidx, int n_kv, uint8_t* __restrict__ sm, uint8_t* __restrict__ codes, int* __restrict__ flags,
-    uint8_t* __restrict__ slots, int* __restrict__ tile_bytes, int ntiles) {
+    const uint16_t* __restrict__ x, long S, long x_head_stride, long x_row_stride, long S_pad, const uint8_t* __restrict__ base3,
+    const uint8_t* __restrict__ base4, const int* __restrict__ bidx, int n_kv, uint8_t* __restrict__ sm, uint8_t* __restrict__ codes,
+    int* __restrict__ flags, uint8_t* __restrict__ slots, int* __restrict__ tile_bytes, int ntiles) {
   __shared__ __align__(16) WarpScratch scratch[ENC_WARPS];
   __shared__ __align__(16) uint8_t esc_stage[ENC_WARPS][TILE_MAX_ESC];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -27,7 +28,7 @@ __global__ void __launch_bounds__(ENC_WARPS * 32) encode_tiles_kernel(
     if (tile >= ntiles) break;                       // warp-uniform
     const long row0 = (long)tile * T;
     const int nvalid = (int)min((long)T, S - row0);
-    stage_rows(ws, x + (h * S_in + row0) * D, D, nvalid, lane);
+    stage_rows(ws, x + h * x_head_stride + row0 * x_row_stride, x_row_stride, nvalid, lane);
     LaneTile lt;
     const int total = encode_tile_warp<KIND_V>(ws, nvalid, b3w, b4w, lane, lt);
     const long trow = h * S_pad + row0;
@@ -119,7 +120,7 @@ __global__ void __launch_bounds__(256) head_prefix_kernel(const int* __restrict_
 // ovf_off[h, row] = tile_off[h, tile] + (escape bytes of the tile's earlier rows), recomputed from the tag words.
 __global__ void __launch_bounds__(128) compact_copy_kernel(const uint8_t* __restrict__ slots, const int* __restrict__ tile_bytes, int ntiles,
                                                             const int* __restrict__ tile_off, long tile_off_stride,
-                                                            const int* __restrict__ head_start, uint8_t* __restrict__ ovf, long n_items,
+                                                            const int* __restrict__ head_start, long head_stride, uint8_t* __restrict__ ovf, long n_items,
                                                             const int* __restrict__ flags, long S, long S_pad, int* __restrict__ ovf_off, int zero_pad,
                                                             long ovf_cap, long head_cap, int* __restrict__ status) {
   const long item = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
@@ -131,11 +132,11 @@ __global__ void __launch_bounds__(128) compact_copy_kernel(const uint8_t* __rest
   const uint8_t* src = slots + item * (long)TILE_MAX_ESC;
   // bounds: the whole stream must fit ovf_cap bytes (ovf_cap > 0), a head's part head_cap bytes (head_cap > 0), read padding
   // included; a tile that does not fit is not written and bit 0 of *status is set
-  const long at = (long)head_start[h] + toff;
+  const long at = (head_start ? (long)head_start[h] : h * head_stride) + toff;        // no table: head h's stream starts at h * head_stride
   const bool fits = (ovf_cap <= 0 || at + n + zero_pad <= ovf_cap) && (head_cap <= 0 || (long)toff + n + zero_pad <= head_cap);
   if (fits) { uint8_t* dst = ovf + at; for (int i = lane; i < n; i += 32) dst[i] = src[i]; }
   else if (lane == 0 && status) atomicOr(status, 1);
-  if (zero_pad && head_cap <= 0 && item == 0 && lane < zero_pad) {                                    // over-read padding behind the last head (packed stream)
+  if (zero_pad && head_cap <= 0 && head_start && item == 0 && lane < zero_pad) {                                    // over-read padding behind the last head (packed stream)
     const long end = (long)head_start[n_items / ntiles];
     if (ovf_cap <= 0 || end + zero_pad <= ovf_cap) ovf[end + lane] = 0;
     else if (lane == 0 && status) atomicOr(status, 1);
@@ -232,6 +233,35 @@ __global__ void __launch_bounds__(128) bases_from_hist_kernel(const long long* _
   }
 }
 
+// Last step of a slot's prefill (one CTA): the prompt's remainder (L mod 16 rows) goes into the raw tails of the slot's heads,
+// the heads' token counters are set, and the largest escape stream of the slot per kind is reported for the host's capacity
+// check.  k_tok / v_tok: token-major rows, head h of token t at t * row_stride + h * 128 (bf16 elements).
+__global__ void __launch_bounds__(256) prefill_finish_kernel(const uint16_t* __restrict__ k_tok, const uint16_t* __restrict__ v_tok, long row_stride, long L,
+                                                              int n_kv, long h0, uint16_t* __restrict__ ktail, uint16_t* __restrict__ vtail,
+                                                              int* __restrict__ seq_len, int* __restrict__ tail_len, int* __restrict__ used_k,
+                                                              int* __restrict__ used_v, int* __restrict__ status) {
+  const long n_full = L / T * T;
+  const int rem = (int)(L - n_full), tid = threadIdx.x;
+  const int per_kind = rem * n_kv * 16;                              // 16-byte pieces
+  for (int i = tid; i < 2 * per_kind; i += blockDim.x) {
+    const int kind = i >= per_kind, j = i - kind * per_kind;
+    const int r = j / (n_kv * 16), h = (j >> 4) % n_kv, c = j & 15;
+    const uint16_t* src = (kind ? v_tok : k_tok) + (n_full + r) * row_stride + h * D + c * 8;
+    uint16_t* dst = (kind ? vtail : ktail) + ((h0 + h) * T + r) * D + c * 8;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+  }
+  if (tid < n_kv) {
+    seq_len[h0 + tid] = (int)n_full; tail_len[h0 + tid] = rem;
+    if (n_full == 0) { used_k[h0 + tid] = 0; used_v[h0 + tid] = 0; }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int mk = 0, mv = 0;
+    for (int h = 0; h < n_kv; h++) { mk = max(mk, used_k[h0 + h]); mv = max(mv, used_v[h0 + h]); }
+    status[1] = mk; status[3] = mv;
+  }
+}
+
 }  // namespace gaac
 
 using namespace gaac;
@@ -246,9 +276,9 @@ extern "C" int gaac_encode_tiles(const void* x_bf16, int64_t H, int64_t S, int64
   dim3 grid((ntiles + ENC_WARPS * ENC_TILES_PER_WARP - 1) / (ENC_WARPS * ENC_TILES_PER_WARP), (unsigned)H);
   cudaStream_t st = (cudaStream_t)stream;
   if (kind == GAAC_KIND_K)
-    encode_tiles_kernel<0><<<grid, ENC_WARPS * 32, 0, st>>>((const uint16_t*)x_bf16, S, S_in, S_pad, base3, base4, bidx, n_kv, sm, codes, flags, slots, tile_bytes, ntiles);
+    encode_tiles_kernel<0><<<grid, ENC_WARPS * 32, 0, st>>>((const uint16_t*)x_bf16, S, S_in * D, D, S_pad, base3, base4, bidx, n_kv, sm, codes, flags, slots, tile_bytes, ntiles);
   else
-    encode_tiles_kernel<1><<<grid, ENC_WARPS * 32, 0, st>>>((const uint16_t*)x_bf16, S, S_in, S_pad, base3, base4, bidx, n_kv, sm, codes, flags, slots, tile_bytes, ntiles);
+    encode_tiles_kernel<1><<<grid, ENC_WARPS * 32, 0, st>>>((const uint16_t*)x_bf16, S, S_in * D, D, S_pad, base3, base4, bidx, n_kv, sm, codes, flags, slots, tile_bytes, ntiles);
   return launch_status();
 }
 
@@ -262,7 +292,7 @@ extern "C" int gaac_compact(const uint8_t* slots, const int32_t* tile_bytes, int
   tile_scan_kernel<<<(unsigned)H, SCAN_THREADS, 0, st>>>(tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_bytes);
   if (head_start) {
     const long n_items = H * ntiles;
-    compact_copy_kernel<<<(unsigned)((n_items + 3) / 4), 128, 0, st>>>(slots, tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_start, ovf, n_items,
+    compact_copy_kernel<<<(unsigned)((n_items + 3) / 4), 128, 0, st>>>(slots, tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_start, 0, ovf, n_items,
                                                                     flags, S, S_pad, ovf_off, 0, 0, 0, nullptr);
   }
   return launch_status();
@@ -286,7 +316,7 @@ extern "C" int gaac_compact_copy(const uint8_t* slots, const int32_t* tile_bytes
   if (ovf_cap < 0 || head_cap < 0) return GAAC_E_ARG;
   if (ovf_off && (!flags || S <= 0 || S_pad < S)) return GAAC_E_ARG;
   const long n_items = H * ntiles;
-  compact_copy_kernel<<<(unsigned)((n_items + 3) / 4), 128, 0, (cudaStream_t)stream>>>(slots, tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_start, ovf,
+  compact_copy_kernel<<<(unsigned)((n_items + 3) / 4), 128, 0, (cudaStream_t)stream>>>(slots, tile_bytes, (int)ntiles, tile_off, tile_off_stride, head_start, 0, ovf,
                                                                                        n_items, flags, S, S_pad, ovf_off, zero_pad, ovf_cap, head_cap, status);
   return launch_status();
 }
@@ -324,5 +354,60 @@ extern "C" int gaac_exponent_hist(const void* x_bf16, int64_t N, int64_t n_ch, l
 extern "C" int gaac_bases_from_hist(const long long* hist, int64_t n_rows, uint8_t* base3, uint8_t* base4, void* stream) {
   if (!hist || !base3 || !base4 || n_rows <= 0) return GAAC_E_ARG;
   bases_from_hist_kernel<<<(unsigned)((n_rows + 3) / 4), 128, 0, (cudaStream_t)stream>>>(hist, n_rows, base3, base4);
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------- slot cache: whole-prompt prefill
+constexpr int CACHE_READ_PAD = 8;      // bytes kept free behind a head's escape bytes (the readers may touch them)
+
+extern "C" size_t gaac_cache_prefill_scratch_bytes(int64_t L, int n_kv) {
+  const size_t items = (size_t)(L > 0 ? L / T : 0) * (size_t)(n_kv > 0 ? n_kv : 0);
+  return 2 * items * (TILE_MAX_ESC + sizeof(int32_t)) + 256;
+}
+
+extern "C" int gaac_cache_prefill(const gaac_store* K, const gaac_store* V, const void* k_tok, const void* v_tok, int64_t L, int64_t row_stride, int slot,
+                                  int n_kv, int32_t* tail_len, int32_t* seq_len, int64_t S_cap, int64_t ovf_cap, int n_base_rows, uint8_t* scratch,
+                                  size_t scratch_bytes, int32_t* status, int copy_only, void* stream) {
+  if (!K || !V || !tail_len || !seq_len || !scratch || !status || (L > 0 && (!k_tok || !v_tok))) return GAAC_E_ARG;
+  if (L < 0 || L > S_cap || S_cap % T || row_stride < (int64_t)n_kv * D || slot < 0 || n_kv <= 0 || n_kv > 256 || ovf_cap <= CACHE_READ_PAD ||
+      n_base_rows <= 0 || n_base_rows % n_kv)
+    return GAAC_E_ARG;
+  for (const gaac_store* s : {K, V}) {
+    if (!s->sm || !s->codes || !s->flags || !s->tile_off || !s->ovf || !s->ovf_used || !s->tail || !s->base3 || !s->base4) return GAAC_E_ARG;
+    if (!aligned16(s->sm) || !aligned16(s->codes) || !aligned16(s->tail)) return GAAC_E_ALIGN;
+  }
+  if (!aligned16(k_tok) || !aligned16(v_tok) || (row_stride * 2) % 16) return GAAC_E_ALIGN;
+  if (scratch_bytes < gaac_cache_prefill_scratch_bytes(L, n_kv)) return GAAC_E_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long h0 = (long)slot * n_kv;
+  const int ntiles = (int)(L / T);
+  const long S = (long)ntiles * T, tiles_cap = S_cap / T, n_items = (long)n_kv * ntiles;
+  // scratch: escape slots of K, of V, then the tile sizes of K, of V
+  uint8_t* slots[2] = {scratch, scratch + n_items * TILE_MAX_ESC};
+  int32_t* tbytes[2] = {reinterpret_cast<int32_t*>(scratch + 2 * n_items * TILE_MAX_ESC), reinterpret_cast<int32_t*>(scratch + 2 * n_items * TILE_MAX_ESC) + n_items};
+  if (copy_only) { cudaMemsetAsync(status, 0, 4, st); cudaMemsetAsync(status + 2, 0, 4, st); }
+  else cudaMemsetAsync(status, 0, 16, st);
+  const gaac_store* side[2] = {K, V};
+  const void* tok[2] = {k_tok, v_tok};
+  for (int kind = 0; kind < 2 && ntiles > 0; kind++) {
+    const gaac_store* s = side[kind];
+    int32_t* toff = s->tile_off + h0 * tiles_cap;
+    if (!copy_only) {
+      const uint8_t* b3 = s->base3 + (h0 % n_base_rows) * D; const uint8_t* b4 = s->base4 + (h0 % n_base_rows) * D;      // consecutive heads, consecutive rows
+      dim3 grid((ntiles + ENC_WARPS * ENC_TILES_PER_WARP - 1) / (ENC_WARPS * ENC_TILES_PER_WARP), (unsigned)n_kv);
+      if (kind == 0)
+        encode_tiles_kernel<0><<<grid, ENC_WARPS * 32, 0, st>>>((const uint16_t*)tok[kind], S, D, row_stride, S_cap, b3, b4, nullptr, n_kv, s->sm + h0 * S_cap * D,
+                                                               s->codes + h0 * S_cap * CB, s->flags + h0 * S_cap, slots[kind], tbytes[kind], ntiles);
+      else
+        encode_tiles_kernel<1><<<grid, ENC_WARPS * 32, 0, st>>>((const uint16_t*)tok[kind], S, D, row_stride, S_cap, b3, b4, nullptr, n_kv, s->sm + h0 * S_cap * D,
+                                                               s->codes + h0 * S_cap * CB, s->flags + h0 * S_cap, slots[kind], tbytes[kind], ntiles);
+      tile_scan_kernel<<<(unsigned)n_kv, SCAN_THREADS, 0, st>>>(tbytes[kind], ntiles, toff, tiles_cap, s->ovf_used + h0);
+    }
+    compact_copy_kernel<<<(unsigned)((n_items + 3) / 4), 128, 0, st>>>(slots[kind], tbytes[kind], ntiles, toff, tiles_cap, nullptr, ovf_cap, s->ovf + h0 * ovf_cap, n_items,
+                                                                    nullptr, 0, 0, nullptr, 0, 0, ovf_cap - CACHE_READ_PAD, status + 2 * kind);
+  }
+  if (!copy_only)
+    prefill_finish_kernel<<<1, 256, 0, st>>>((const uint16_t*)k_tok, (const uint16_t*)v_tok, row_stride, L, n_kv, h0, (uint16_t*)K->tail, (uint16_t*)V->tail,
+                                             seq_len, tail_len, K->ovf_used, V->ovf_used, status);
   return launch_status();
 }

@@ -15,7 +15,7 @@ read them; the device work goes through libgaac_b200.so.
 from __future__ import annotations
 import torch
 from . import _lib
-from .codec import Codec, Page, D, T, CB
+from .codec import Codec, Page, D, T, CB, bases_from_hist, exponent_hist
 from .encoder import TileEncoder
 from .kernel import _ext, choose_nsplit, choose_nsplit_sm100
 
@@ -85,6 +85,8 @@ class CompressedKVCache:
         self.S = torch.zeros(self.H, dtype=torch.int32, device=device)                           # tokens in compressed tiles, per head
         self.tail_len = torch.zeros(self.H, dtype=torch.int32, device=device)                    # tokens in the raw tail, per head
         self.append_errors = torch.zeros(1, dtype=torch.int32, device=device)                    # tiles an append refused for lack of escape room
+        self._scratch = None                                                                     # escape slots of the prefill in flight (grown on demand)
+        self._prefill_status = torch.zeros(4, dtype=torch.int32, device=device)
         self.growable = True                                                                     # False: the buffers may not move (their addresses are baked into CUDA graphs)
 
     @staticmethod
@@ -106,42 +108,50 @@ class CompressedKVCache:
     # ------------------------------------------------------------------ prefill
     def prefill(self, slot: int, k: torch.Tensor, v: torch.Tensor):
         """Put a prompt's K and V ([L, n_kv, 128] bf16, one row per token as the model produces them) into `slot`: whole tiles
-        compressed, the remainder into the tail.  Replaces whatever the slot held.  (gaac/kv_cache.py:149-169)"""
+        compressed, the remainder into the tail.  Replaces whatever the slot held.  (gaac/kv_cache.py:149-169)
+        One library call (encode of both kinds straight from the token-major rows, offsets, the copy into the heads' escape
+        streams, tails, counters) and ONE host read afterwards (the status words): the copy never writes past a head's share, so
+        the check can follow it.  Only when a head's stream was too small are the streams enlarged and the copy (not the
+        encode) repeated."""
         L = k.shape[0]
         assert L <= self.cap, f"sequence of {L} tokens exceeds the cache capacity {self.cap}"
+        assert 0 <= slot < self.n_slots
         hs = self._heads(slot)
-        n_full = L // T * T
-        for st, x in ((self.k, k), (self.v, v)):
-            per_head = x.transpose(0, 1).contiguous()                                         # [n_kv, L, 128]
-            if self.per_sequence_bases:
-                own = Codec(self.n_kv, x.device).calibrate(per_head)
-                st.base3[hs], st.base4[hs] = own.base3, own.base4
-            st.ovf_used[hs] = 0
-            if n_full:
-                self._store_tiles(st, hs, per_head, n_full)
-            if L > n_full:
-                st.tail[hs, :L - n_full] = per_head[:, n_full:]
-        self.S[hs] = n_full
-        self.tail_len[hs] = L - n_full
+        k, v = self._token_rows(k), self._token_rows(v)
+        if self.per_sequence_bases and L:
+            for st, x in ((self.k, k), (self.v, v)):
+                rows = x if x.is_contiguous() else x.contiguous()                                 # the histogram reads [L, n_kv * 128] rows
+                st.base3[hs], st.base4[hs] = bases_from_hist(exponent_hist(rows, self.n_kv), self.n_kv)
+        L_ = _lib.lib()
+        need = L_.gaac_cache_prefill_scratch_bytes(L, self.n_kv)
+        if self._scratch is None or self._scratch.numel() < need:
+            self._scratch = torch.empty(need, dtype=torch.uint8, device=k.device)
 
-    def _store_tiles(self, st: _Store, hs: slice, x: torch.Tensor, n_tok: int):
-        """Compress the first n_tok tokens (a multiple of 16) of x [n_kv, >= n_tok, 128] into the heads hs of st, escape streams
-        from offset 0.  Encode, offsets and the copy into the heads' streams are launched back to back; the copy never writes
-        past a head's share, so the one host read (largest head, status word) can come afterwards.  Only when a head's stream was
-        too small are the streams enlarged and the copy (not the encode) repeated."""
-        rows = (torch.arange(hs.start, hs.stop, device=x.device, dtype=torch.int32) % st.base3.shape[0]).contiguous()     # base row of each head
-        tile_off = torch.empty(self.n_kv, n_tok // T, dtype=torch.int32, device=x.device)
-        status, retry = st.enc.encode_into(x, st.base3, st.base4, self.n_kv, st.sm[hs], st.codes[hs], st.flags[hs], tile_off, st.ovf, S=n_tok, S_pad=self.cap,
-                                           head_base=st.head_start[hs], head_cap=st.ovf_cap, head_bytes=st.ovf_used[hs], bidx=rows, zero_pad=_OVER_READ)
-        st.tile_off[hs, :n_tok // T] = tile_off
-        biggest, too_small = (int(v) for v in torch.stack([st.ovf_used[hs].max(), status[0]]).tolist())
+        def launch(copy_only: int):
+            _lib.check(L_.gaac_cache_prefill(self.k.c_store(), self.v.c_store(), k.data_ptr(), v.data_ptr(), L, k.stride(0), slot, self.n_kv,
+                                             self.tail_len.data_ptr(), self.S.data_ptr(), self.cap, self.k.ovf_cap, self.k.base3.shape[0],
+                                             self._scratch.data_ptr(), self._scratch.numel(), self._prefill_status.data_ptr(), copy_only,
+                                             _lib.stream_ptr(k.device)), "gaac_cache_prefill")
+        launch(0)
+        short_k, used_k, short_v, used_v = self._prefill_status.tolist()                           # the one host synchronisation
         # room for these tiles and for one more worst-case tile, which an append may add before the next check_capacity
-        wanted = biggest + TILE_MAX_ESC + _OVER_READ
-        if wanted > st.ovf_cap:
+        wanted = max(used_k, used_v) + TILE_MAX_ESC + _OVER_READ
+        if wanted > self.k.ovf_cap:
             self._grow(wanted)
-        if too_small:
-            status.zero_()
-            retry(st.ovf, head_base=st.head_start[hs], head_cap=st.ovf_cap)
+        if short_k or short_v:
+            launch(1)
+
+    @staticmethod
+    def _token_rows(x: torch.Tensor) -> torch.Tensor:
+        """x [L, n_kv, 128] as the library reads it: unit stride over channels, heads 128 elements apart, 16-byte aligned rows; a
+        slice of a larger token-major tensor passes as it is, anything else is copied."""
+        if not x.is_cuda:
+            raise RuntimeError("CompressedKVCache needs CUDA tensors: gaac_b200 has no CPU path")
+        ok = x.dtype == torch.bfloat16 and x.dim() == 3 and x.shape[2] == D and x.stride(2) == 1 and (x.shape[1] == 1 or x.stride(1) == D) and \
+            (x.shape[0] <= 1 or (x.stride(0) >= x.shape[1] * D and x.stride(0) % 8 == 0)) and x.data_ptr() % 16 == 0
+        if ok and x.shape[0] <= 1:
+            return x.contiguous()
+        return x if ok else x.to(torch.bfloat16).contiguous()
 
     # ------------------------------------------------------------------ decode step
     def append(self, slots: torch.Tensor, k: torch.Tensor, v: torch.Tensor):

@@ -249,6 +249,26 @@ typedef struct {
 int gaac_append_kv(const gaac_store* K, const gaac_store* V, const void* k_new, const void* v_new, const int32_t* slot, int B, int n_kv,
                    int32_t* tail_len, int32_t* seq_len, int64_t S_cap, int64_t ovf_cap, int n_base_rows, int32_t* err, void* stream);
 
+/* A whole prompt into one slot: k_tok / v_tok = the prompt's K and V as the model produces them, token-major: head h of token t
+ * at x + t*row_stride + h*128 (bf16 elements; row_stride >= n_kv*128, rows 16-byte aligned), L tokens (L <= S_cap).  The
+ * floor(L/16) whole tiles of every head of the slot are compressed straight into the store (tile 0 upward, the head's escape
+ * bytes from offset 0 of its share), the L mod 16 remaining rows go into the raw tails, seq_len / tail_len / ovf_used of the
+ * slot's heads are set: seven launches, no host synchronisation, no transposed copy of the input.
+ * Replaces CompressedKVCache.prefill's device work (gaac/kv_cache.py:149-169: Triton encode per kind, torch prefix sums, the
+ * scatter of the escape bytes, tail copy, counter updates).
+ *   scratch: gaac_cache_prefill_scratch_bytes(L, n_kv) bytes of device memory, kept by the caller until a copy_only repeat is
+ *     no longer needed.
+ *   status: device int32[4], written by the call: [0] bit 0 set when some K head's escape bytes (+ 8 bytes of read padding) did
+ *     not fit ovf_cap: the escape bytes of the tiles that did not fit were NOT written (nothing is written outside a head's
+ *     share); tile_off and ovf_used are exact all the same; [1] = largest ovf_used among the slot's K heads; [2], [3]: same for V.
+ *   copy_only != 0: after the caller has enlarged the escape streams (new K->ovf / V->ovf, new ovf_cap), repeat only the copy of
+ *     the escape bytes from the scratch of the previous call with the same L and slot; status[0] and status[2] are rewritten.
+ * Base row of head slot*n_kv + h: (slot*n_kv + h) % n_base_rows, as in gaac_append_kv. */
+size_t gaac_cache_prefill_scratch_bytes(int64_t L, int n_kv);
+int gaac_cache_prefill(const gaac_store* K, const gaac_store* V, const void* k_tok, const void* v_tok, int64_t L, int64_t row_stride, int slot,
+                       int n_kv, int32_t* tail_len, int32_t* seq_len, int64_t S_cap, int64_t ovf_cap, int n_base_rows, uint8_t* scratch,
+                       size_t scratch_bytes, int32_t* status, int copy_only, void* stream);
+
 /* ---------------------------------------------------------------------------------------------- paged layout (layout B) */
 
 /* Paged store state of one layer (gaac/vllm/store.py:177-203).  Tile slot p = block*(2*n_kv) + 2*kvh + kind lives at

@@ -25,7 +25,7 @@ def test_status_strings(lib):
     assert lib.gaac_status_string(0) == b"ok"
     for s in range(1, 6):
         assert len(lib.gaac_status_string(s)) > 4
-    assert lib.gaac_abi_version() == 2
+    assert lib.gaac_abi_version() == 3
 
 
 def test_bad_arguments_are_rejected_before_any_launch(lib):

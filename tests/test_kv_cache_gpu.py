@@ -179,3 +179,39 @@ def _bases2():
     k, v = _tok(O.kv_like(2, 2048, 11)), _tok(O.kv_like(2, 2048, 12))
     k3, k4 = O.bases_from_hist(O.exponent_hist_fast(k, 2), 2); v3, v4 = O.bases_from_hist(O.exponent_hist_fast(v, 2), 2)
     return {n: torch.from_numpy(a) for n, a in (("k3", k3), ("k4", k4), ("v3", v3), ("v4", v4))}
+
+
+@pytest.mark.parametrize("static_bases", [True, False])
+def test_prefill_reads_token_major_rows_in_place(static_bases):
+    """prefill takes the prompt as the model produces it: a span of a larger token-major tensor (row stride n_kv*128, no copy),
+    a QKV-style buffer whose rows are wider than n_kv*128, a transposed view (copied by the wrapper); lengths 0, 5, 16, 33 and
+    one that fills the capacity.  Every slot decompresses to exactly what went in and attends correctly."""
+    from gaac_b200 import CompressedKVCache
+    import torch
+    cap = 256
+    cache = CompressedKVCache(n_slots=6, n_kv=N_KV, capacity=cap, bases=_bases(11) if static_bases else None)
+    lens = [5, 16, 33, cap]
+    total = sum(lens)
+    k_all, v_all = _tok(O.kv_like(N_KV, total, 71)), _tok(O.kv_like(N_KV, total, 72))
+    kd, vd = to_bf16_cuda(k_all), to_bf16_cuda(v_all)
+    hist, at = {}, 0
+    for s, L in enumerate(lens):                                             # spans of one flat batch tensor, as a prefill step has them
+        cache.prefill(s, kd[at:at + L], vd[at:at + L]); hist[s] = (k_all[at:at + L], v_all[at:at + L]); at += L
+    # rows inside a wider buffer: [L, 3 * n_kv, 128], the K heads in the middle third
+    L = 40
+    wide = torch.zeros(L, 3 * N_KV, 128, dtype=torch.bfloat16, device="cuda")
+    k5, v5 = _tok(O.kv_like(N_KV, L, 73)), _tok(O.kv_like(N_KV, L, 74))
+    wide[:, N_KV:2 * N_KV] = to_bf16_cuda(k5); wide[:, 2 * N_KV:] = to_bf16_cuda(v5)
+    cache.prefill(4, wide[:, N_KV:2 * N_KV], wide[:, 2 * N_KV:]); hist[4] = (k5, v5)
+    # a head-major tensor viewed token-major (strides the library does not read directly)
+    k6, v6 = O.kv_like(N_KV, 21, 75), O.kv_like(N_KV, 21, 76)
+    cache.prefill(5, to_bf16_cuda(k6).transpose(0, 1), to_bf16_cuda(v6).transpose(0, 1)); hist[5] = (_tok(k6), _tok(v6))
+    for s, (k, v) in hist.items():
+        dk, dv = cache.decompress(s)
+        assert np.array_equal(bits(dk), k) and np.array_equal(bits(dv), v), s
+    rng = np.random.default_rng(3)
+    q16 = O.f32_to_bf16((rng.standard_normal((6, N_KV * G, 128)) * 0.1).astype(np.float32))
+    _check(cache, hist, [0, 1, 2, 3, 4, 5], q16)
+    # an empty prompt empties the slot
+    cache.prefill(2, kd[:0], vd[:0])
+    assert int(cache.S[2 * N_KV]) == 0 and int(cache.tail_len[2 * N_KV]) == 0 and int(cache.k.ovf_used[2 * N_KV]) == 0
