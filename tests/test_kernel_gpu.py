@@ -267,6 +267,32 @@ def test_attention_full_size_contexts(S, outliers):
     assert bool((err1 <= bound).all()) and (outliers or float(err1.max()) <= 2e-3)
 
 
+@pytest.mark.parametrize("B,n_kv,G,S,nsplit", [(1, 1, 4, 65536, None), (1, 1, 8, 65536, 296), (1, 2, 4, 40000, 74), (64, 2, 2, 4096, 4), (5, 8, 1, 9000, 33)])
+def test_attention_many_splits_and_many_rows(B, n_kv, G, S, nsplit):
+    """Split counts far beyond the usual 18 (one kv head over 128 CTAs, the most the cost model picks, 296 = two CTAs per SM's
+    worth; more splits than tiles per warp would allow evenly) and many-row batches that run in several waves, against the
+    float64 reference computed on the GPU; ranges that leave whole CTAs without a tile must not disturb the merge."""
+    import torch
+    from gaac_b200 import attention, Codec, TileEncoder
+    from gaac_b200.synth import synth_kv
+    from gaac_b200.kernel import choose_nsplit_sm100, workspace_error
+    k, v = synth_kv("k", B * n_kv, S, 43, "cuda"), synth_kv("v", B * n_kv, S, 43, "cuda")
+    ck, cv = Codec(n_kv).calibrate(k[:n_kv, :2048]), Codec(n_kv).calibrate(v[:n_kv, :2048])
+    kp, vp = TileEncoder("k").encode(ck, k), TileEncoder("v").encode(cv, v)
+    q = torch.randn(B, n_kv * G, 128, generator=torch.Generator(device="cuda").manual_seed(6), device="cuda").to(torch.bfloat16)
+    o32 = torch.empty(B, n_kv * G, 128, dtype=torch.float32, device="cuda")
+    if nsplit is None:
+        assert choose_nsplit_sm100(B, n_kv, S) == 128
+    out = attention(q, kp, vp, SCALE, nsplit=nsplit, out_f32=o32)
+    for b in range(B):
+        ref, ref_abs = _fp64_attention_on_gpu(q[b], k[b * n_kv:(b + 1) * n_kv], v[b * n_kv:(b + 1) * n_kv], n_kv, G, SCALE)
+        bound = torch.clamp(ref_abs * 2.0 ** -12, min=2e-3)
+        err = (o32[b].double() - ref).abs()
+        assert bool((err <= bound).all()), (b, float((err / bound).max()))
+    assert torch.equal(out, o32.to(torch.bfloat16))
+    assert not workspace_error("cuda")
+
+
 def test_workspace_is_shared_by_calls_of_different_shapes():
     """One stream, one cached workspace: a small call (1 row, 32 query heads, 8 splits) leaves its partials behind, then a call
     with more (row, kv head) groups than the first one had counters runs on the same buffer.  The header of the workspace has a
