@@ -14,21 +14,30 @@ __global__ void __launch_bounds__(ENC_WARPS * 32) encode_tiles_kernel(
     const uint16_t* __restrict__ x, long S, long x_head_stride, long x_row_stride, long S_pad, const uint8_t* __restrict__ base3,
     const uint8_t* __restrict__ base4, const int* __restrict__ bidx, int n_kv, uint8_t* __restrict__ sm, uint8_t* __restrict__ codes,
     int* __restrict__ flags, uint8_t* __restrict__ slots, int* __restrict__ tile_bytes, int ntiles) {
-  __shared__ __align__(16) WarpScratch scratch[ENC_WARPS];
+  __shared__ __align__(16) WarpScratch scratch[2][ENC_WARPS];       // two per warp: the next tile's rows arrive while this one is encoded
   __shared__ __align__(16) uint8_t esc_stage[ENC_WARPS][TILE_MAX_ESC];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long h = blockIdx.y;
-  WarpScratch& ws = scratch[warp];
   const int brow = bidx ? bidx[h] : (int)(h % n_kv);
   u32 b3w[8], b4w[8];
   load_base_words<KIND_V>(base3 + (long)brow * D, base4 + (long)brow * D, lane, b3w, b4w);
-  const int tile0 = blockIdx.x * (ENC_WARPS * ENC_TILES_PER_WARP);
+  const int tile0 = blockIdx.x * (ENC_WARPS * ENC_TILES_PER_WARP) + warp;
+  const uint16_t* xh = x + h * x_head_stride;
+  auto fetch = [&](int i) {                           // rows of the warp's i-th tile into scratch[i & 1]
+    const long row0 = (long)(tile0 + i * ENC_WARPS) * T;
+    stage_rows_async(scratch[i & 1][warp], xh + row0 * x_row_stride, x_row_stride, (int)min((long)T, S - row0), lane);
+    async_commit();
+  };
+  if (tile0 < ntiles) fetch(0);
   for (int i = 0; i < ENC_TILES_PER_WARP; i++) {
-    const int tile = tile0 + i * ENC_WARPS + warp;
+    const int tile = tile0 + i * ENC_WARPS;
     if (tile >= ntiles) break;                       // warp-uniform
+    const bool more = i + 1 < ENC_TILES_PER_WARP && tile + ENC_WARPS < ntiles;
+    __syncwarp();                                    // the other scratch was read by the tile before this one
+    if (more) { fetch(i + 1); async_wait<1>(); } else async_wait<0>();
+    WarpScratch& ws = scratch[i & 1][warp];
     const long row0 = (long)tile * T;
     const int nvalid = (int)min((long)T, S - row0);
-    stage_rows(ws, x + h * x_head_stride + row0 * x_row_stride, x_row_stride, nvalid, lane);
     LaneTile lt;
     const int total = encode_tile_warp<KIND_V>(ws, nvalid, b3w, b4w, lane, lt);
     const long trow = h * S_pad + row0;

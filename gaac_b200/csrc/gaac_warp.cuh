@@ -50,6 +50,21 @@ __device__ __forceinline__ void stage_rows(WarpScratch& ws, const uint16_t* src,
   }
 }
 
+// The same staging with asynchronous 16-byte copies (rows >= nvalid are zero-filled by the copy unit): the caller commits the
+// group and waits for it before encode_tile_warp, so the rows of the next tile travel while the current one is encoded.
+__device__ __forceinline__ void stage_rows_async(WarpScratch& ws, const uint16_t* src, long row_stride, int nvalid, int lane) {
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    const int c = lane + 32 * k, row = c >> 4, col = (c & 15) * 8;
+    const bool live = row < nvalid;
+    const uint16_t* g = src + (live ? (long)row * row_stride + col : 0);
+    const unsigned d = (unsigned)__cvta_generic_to_shared(&ws.xs[row * XS_STRIDE + col]);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(g), "r"(live ? 16 : 0) : "memory");
+  }
+}
+__device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
 // Encode the staged tile.  Rows >= nvalid become empty rows (sm = 0, codes = 0, tag word 0).  On return every lane holds
 // its share in `lt`, ws.fl / ws.rowoff are filled and the tile's escape byte count is returned (same in all lanes).
 template <int KIND_V>
