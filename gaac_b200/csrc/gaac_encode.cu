@@ -377,7 +377,7 @@ extern "C" size_t gaac_cache_prefill_scratch_bytes(int64_t L, int n_kv) {
 extern "C" int gaac_cache_prefill(const gaac_store* K, const gaac_store* V, const void* k_tok, const void* v_tok, int64_t L, int64_t row_stride, int slot,
                                   int n_kv, int32_t* tail_len, int32_t* seq_len, int64_t S_cap, int64_t ovf_cap, int n_base_rows, uint8_t* scratch,
                                   size_t scratch_bytes, int32_t* status, int copy_only, void* stream) {
-  if (!K || !V || !tail_len || !seq_len || !scratch || !status || (L > 0 && (!k_tok || !v_tok))) return GAAC_E_ARG;
+  if (!K || !V || !tail_len || !seq_len || !scratch || !status || (!copy_only && L > 0 && (!k_tok || !v_tok))) return GAAC_E_ARG;
   if (L < 0 || L > S_cap || S_cap % T || row_stride < (int64_t)n_kv * D || slot < 0 || n_kv <= 0 || n_kv > 256 || ovf_cap <= CACHE_READ_PAD ||
       n_base_rows <= 0 || n_base_rows % n_kv)
     return GAAC_E_ARG;
@@ -385,7 +385,7 @@ extern "C" int gaac_cache_prefill(const gaac_store* K, const gaac_store* V, cons
     if (!s->sm || !s->codes || !s->flags || !s->tile_off || !s->ovf || !s->ovf_used || !s->tail || !s->base3 || !s->base4) return GAAC_E_ARG;
     if (!aligned16(s->sm) || !aligned16(s->codes) || !aligned16(s->tail)) return GAAC_E_ALIGN;
   }
-  if (!aligned16(k_tok) || !aligned16(v_tok) || (row_stride * 2) % 16) return GAAC_E_ALIGN;
+  if (!copy_only && (!aligned16(k_tok) || !aligned16(v_tok) || (row_stride * 2) % 16)) return GAAC_E_ALIGN;
   if (scratch_bytes < gaac_cache_prefill_scratch_bytes(L, n_kv)) return GAAC_E_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   const long h0 = (long)slot * n_kv;

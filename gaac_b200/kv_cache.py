@@ -86,7 +86,9 @@ class CompressedKVCache:
         self.tail_len = torch.zeros(self.H, dtype=torch.int32, device=device)                    # tokens in the raw tail, per head
         self.append_errors = torch.zeros(1, dtype=torch.int32, device=device)                    # tiles an append refused for lack of escape room
         self._scratch = None                                                                     # escape slots of the prefill in flight (grown on demand)
-        self._prefill_status = torch.zeros(4, dtype=torch.int32, device=device)
+        self._slot_status = torch.zeros(n_slots, 4, dtype=torch.int32, device=device)           # per slot: what its last prefill reported
+        self._pending, self._pending_bytes = {}, 0                                                # prefills whose host check is still due: slot -> (tokens, escape slots)
+        self.pending_scratch_limit = 1 << 30                                                      # bytes of escape slots kept for unchecked prefills before a check is forced
         self.growable = True                                                                     # False: the buffers may not move (their addresses are baked into CUDA graphs)
 
     @staticmethod
@@ -106,13 +108,17 @@ class CompressedKVCache:
         return slice(slot * self.n_kv, (slot + 1) * self.n_kv)
 
     # ------------------------------------------------------------------ prefill
-    def prefill(self, slot: int, k: torch.Tensor, v: torch.Tensor):
+    def prefill(self, slot: int, k: torch.Tensor, v: torch.Tensor, check: bool = True):
         """Put a prompt's K and V ([L, n_kv, 128] bf16, one row per token as the model produces them) into `slot`: whole tiles
         compressed, the remainder into the tail.  Replaces whatever the slot held.  (gaac/kv_cache.py:149-169)
         One library call (encode of both kinds straight from the token-major rows, offsets, the copy into the heads' escape
         streams, tails, counters) and ONE host read afterwards (the status words): the copy never writes past a head's share, so
         the check can follow it.  Only when a head's stream was too small are the streams enlarged and the copy (not the
-        encode) repeated."""
+        encode) repeated.
+        check=False puts the host read off: the call returns as soon as its kernels are queued and keeps the prompt's escape
+        slots (160 B per token and kv head) until settle_prefills() - which append, attention, decompress, check_capacity
+        and stats call first - reads the status words of all such prefills in one go and repairs the slots whose streams were
+        too small.  A step that prefills several prompts then waits for the GPU once, not once per prompt."""
         L = k.shape[0]
         assert L <= self.cap, f"sequence of {L} tokens exceeds the cache capacity {self.cap}"
         assert 0 <= slot < self.n_slots
@@ -122,24 +128,54 @@ class CompressedKVCache:
             for st, x in ((self.k, k), (self.v, v)):
                 rows = x if x.is_contiguous() else x.contiguous()                                 # the histogram reads [L, n_kv * 128] rows
                 st.base3[hs], st.base4[hs] = bases_from_hist(exponent_hist(rows, self.n_kv), self.n_kv)
-        L_ = _lib.lib()
-        need = L_.gaac_cache_prefill_scratch_bytes(L, self.n_kv)
-        if self._scratch is None or self._scratch.numel() < need:
-            self._scratch = torch.empty(need, dtype=torch.uint8, device=k.device)
-
-        def launch(copy_only: int):
-            _lib.check(L_.gaac_cache_prefill(self.k.c_store(), self.v.c_store(), k.data_ptr(), v.data_ptr(), L, k.stride(0), slot, self.n_kv,
-                                             self.tail_len.data_ptr(), self.S.data_ptr(), self.cap, self.k.ovf_cap, self.k.base3.shape[0],
-                                             self._scratch.data_ptr(), self._scratch.numel(), self._prefill_status.data_ptr(), copy_only,
-                                             _lib.stream_ptr(k.device)), "gaac_cache_prefill")
-        launch(0)
-        short_k, used_k, short_v, used_v = self._prefill_status.tolist()                           # the one host synchronisation
+        need = _lib.lib().gaac_cache_prefill_scratch_bytes(L, self.n_kv)
+        if check:
+            self.settle_prefills()
+            if self._scratch is None or self._scratch.numel() < need:
+                self._scratch = torch.empty(need, dtype=torch.uint8, device=k.device)
+            scratch, status = self._scratch, self._slot_status[slot]
+        else:
+            old = self._pending.pop(slot, None)
+            if old is not None:
+                self._pending_bytes -= old[1].numel()
+            if self._pending_bytes + need > self.pending_scratch_limit:
+                self.settle_prefills()
+            scratch, status = torch.empty(need, dtype=torch.uint8, device=k.device), self._slot_status[slot]
+        self._prefill_launch(slot, L, k, v, scratch, status, copy_only=0)
+        if not check:
+            self._pending[slot] = (L, scratch)
+            self._pending_bytes += need
+            return
+        short_k, used_k, short_v, used_v = status.tolist()                                         # the one host synchronisation
         # room for these tiles and for one more worst-case tile, which an append may add before the next check_capacity
         wanted = max(used_k, used_v) + TILE_MAX_ESC + _OVER_READ
         if wanted > self.k.ovf_cap:
             self._grow(wanted)
         if short_k or short_v:
-            launch(1)
+            self._prefill_launch(slot, L, None, None, scratch, status, copy_only=1)
+
+    def _prefill_launch(self, slot, L, k, v, scratch, status, copy_only: int):
+        dev = self.S.device
+        _lib.check(_lib.lib().gaac_cache_prefill(self.k.c_store(), self.v.c_store(), _lib.ptr(k), _lib.ptr(v), L, k.stride(0) if k is not None else self.n_kv * D,
+                                                 slot, self.n_kv, self.tail_len.data_ptr(), self.S.data_ptr(), self.cap, self.k.ovf_cap, self.k.base3.shape[0],
+                                                 scratch.data_ptr(), scratch.numel(), status.data_ptr(), copy_only, _lib.stream_ptr(dev)), "gaac_cache_prefill")
+
+    def settle_prefills(self):
+        """Host check of every prefill made with check=False: one read of their status words; the escape streams grow when one
+        of them (plus a worst-case tile) no longer fits, and the slots whose escape bytes did not fit get theirs copied again
+        from the escape slots kept since the prefill."""
+        if not self._pending:
+            return
+        pending, self._pending, self._pending_bytes = self._pending, {}, 0
+        slots = list(pending)
+        words = self._slot_status[torch.tensor(slots, dtype=torch.long, device=self.S.device)].tolist()
+        wanted = max(max(w[1], w[3]) for w in words) + TILE_MAX_ESC + _OVER_READ
+        if wanted > self.k.ovf_cap:
+            self._grow(wanted)
+        for slot, w in zip(slots, words):
+            if w[0] or w[2]:
+                L, scratch = pending[slot]
+                self._prefill_launch(slot, L, None, None, scratch, self._slot_status[slot], copy_only=1)
 
     @staticmethod
     def _token_rows(x: torch.Tensor) -> torch.Tensor:
@@ -160,6 +196,7 @@ class CompressedKVCache:
         B = slots.numel()
         if B == 0:
             return
+        self.settle_prefills()
         k, v = k.contiguous(), v.contiguous()
         rc = _lib.lib().gaac_append_kv(self.k.c_store(), self.v.c_store(), k.data_ptr(), v.data_ptr(), slots.data_ptr(), B, self.n_kv,
                                        self.tail_len.data_ptr(), self.S.data_ptr(), self.cap, self.k.ovf_cap, self.k.base3.shape[0],
@@ -171,6 +208,7 @@ class CompressedKVCache:
         zeros.  max_len (longest sequence in the batch, the capacity when omitted) only steers the split count.
         (gaac/kv_cache.py:183-192)"""
         B, n_q, _ = q.shape
+        self.settle_prefills()
         if nsplit is None:
             nsplit = choose_nsplit_sm100(B, self.n_kv, max_len or self.cap)
         K, V = self.k, self.v
@@ -189,6 +227,7 @@ class CompressedKVCache:
         """Keep one worst-case tile of escape room free in every head.  A head completes at most one tile per 16 decode steps, so
         calling this every 16 steps (or more often) means an append never runs out of room.  `used`: the caller's own reading of
         max_escape_bytes(), to save the device read.  (gaac/kv_cache.py:198-203)"""
+        self.settle_prefills()
         if used is None:
             used = int(self.max_escape_bytes())
         wanted = used + TILE_MAX_ESC + _OVER_READ
@@ -206,6 +245,7 @@ class CompressedKVCache:
     def decompress(self, slot: int) -> tuple[torch.Tensor, torch.Tensor]:
         """The slot's K and V back as BF16 [L, n_kv, 128], bit for bit what went in: decoded tiles followed by the tail.
         (gaac/kv_cache.py:211-226)"""
+        self.settle_prefills()
         hs = self._heads(slot)
         n_comp, n_tail = int(self.S[hs.start]), int(self.tail_len[hs.start])
         result = []
@@ -224,6 +264,7 @@ class CompressedKVCache:
     def stats(self) -> dict:
         """Bytes the stored tokens occupy (tiles, escapes, tag words, tile offsets, raw tails) against their size as plain BF16.
         (gaac/kv_cache.py:228-234)"""
+        self.settle_prefills()
         comp_tokens, tail_tokens = int(self.S.sum()), int(self.tail_len.sum())                 # summed over heads
         escapes = int(self.k.ovf_used.sum()) + int(self.v.ovf_used.sum())
         per_kind = comp_tokens * (D + CB + 4) + (comp_tokens // T) * 4 + tail_tokens * D * 2

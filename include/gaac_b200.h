@@ -262,7 +262,8 @@ int gaac_append_kv(const gaac_store* K, const gaac_store* V, const void* k_new, 
  *     not fit ovf_cap: the escape bytes of the tiles that did not fit were NOT written (nothing is written outside a head's
  *     share); tile_off and ovf_used are exact all the same; [1] = largest ovf_used among the slot's K heads; [2], [3]: same for V.
  *   copy_only != 0: after the caller has enlarged the escape streams (new K->ovf / V->ovf, new ovf_cap), repeat only the copy of
- *     the escape bytes from the scratch of the previous call with the same L and slot; status[0] and status[2] are rewritten.
+ *     the escape bytes from the scratch of the previous call with the same L and slot (k_tok / v_tok are not read and may be
+ *     NULL); status[0] and status[2] are rewritten.
  * Base row of head slot*n_kv + h: (slot*n_kv + h) % n_base_rows, as in gaac_append_kv. */
 size_t gaac_cache_prefill_scratch_bytes(int64_t L, int n_kv);
 int gaac_cache_prefill(const gaac_store* K, const gaac_store* V, const void* k_tok, const void* v_tok, int64_t L, int64_t row_stride, int slot,

@@ -215,3 +215,37 @@ def test_prefill_reads_token_major_rows_in_place(static_bases):
     # an empty prompt empties the slot
     cache.prefill(2, kd[:0], vd[:0])
     assert int(cache.S[2 * N_KV]) == 0 and int(cache.tail_len[2 * N_KV]) == 0 and int(cache.k.ovf_used[2 * N_KV]) == 0
+
+
+def test_unchecked_prefills_are_settled_in_one_go():
+    """prefill(check=False) for a batch of prompts, among them one whose escape bytes overflow the heads' streams (random bit
+    patterns: every group raw): nothing is read back until the first call that needs the cache (here attention), which grows
+    the streams once and repairs the overflowed slot from the escape slots kept since its prefill."""
+    from gaac_b200 import CompressedKVCache
+    import torch
+    cache = CompressedKVCache(n_slots=5, n_kv=N_KV, capacity=512, bases=_bases(12), ovf_bytes_per_tile=64)
+    cap0 = cache.k.ovf_cap
+    rng = np.random.default_rng(8)
+    hist = {}
+    for s, L in ((0, 100), (1, 512), (3, 17)):
+        k, v = _tok(O.kv_like(N_KV, L, 80 + s)), _tok(O.kv_like(N_KV, L, 90 + s))
+        cache.prefill(s, to_bf16_cuda(k), to_bf16_cuda(v), check=False); hist[s] = (k, v)
+    junk_k = rng.integers(0, 1 << 16, (300, N_KV, 128)).astype(np.uint16); junk_k[(junk_k & 0x7F80) == 0x7F80] = 0      # no Inf / NaN patterns
+    junk_v = rng.integers(0, 1 << 16, (300, N_KV, 128)).astype(np.uint16); junk_v[(junk_v & 0x7F80) == 0x7F80] = 0
+    cache.prefill(2, to_bf16_cuda(junk_k), to_bf16_cuda(junk_v), check=False)
+    k, v = _tok(O.kv_like(N_KV, 40, 85)), _tok(O.kv_like(N_KV, 40, 95))
+    cache.prefill(3, to_bf16_cuda(k), to_bf16_cuda(v), check=False); hist[3] = (k, v)       # the same slot again before any check
+    assert len(cache._pending) == 4 and cache.k.ovf_cap == cap0
+    q16 = O.f32_to_bf16((rng.standard_normal((3, N_KV * G, 128)) * 0.1).astype(np.float32))
+    _check(cache, hist, [0, 1, 3], q16)                                     # attention settles the pending prefills first
+    assert not cache._pending and cache.k.ovf_cap > cap0
+    dk, dv = cache.decompress(2)
+    assert np.array_equal(bits(dk), junk_k) and np.array_equal(bits(dv), junk_v)
+    # a checked prefill and appends afterwards behave as ever
+    slots = torch.tensor([0, 2], dtype=torch.int32, device="cuda")
+    k1 = O.f32_to_bf16((rng.standard_normal((2, N_KV, 128)) * 0.5).astype(np.float32)); v1 = O.f32_to_bf16((rng.standard_normal((2, N_KV, 128)) * 0.5).astype(np.float32))
+    cache.append(slots, to_bf16_cuda(k1), to_bf16_cuda(v1))
+    hist[0] = (np.concatenate([hist[0][0], k1[0:1]]), np.concatenate([hist[0][1], v1[0:1]]))
+    dk, dv = cache.decompress(0)
+    assert np.array_equal(bits(dk), hist[0][0]) and np.array_equal(bits(dv), hist[0][1])
+    assert int(cache.append_errors) == 0
