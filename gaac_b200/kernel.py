@@ -162,6 +162,12 @@ def attention(q, kp, vp, scale=None, nsplit=None, out_f32=None, out=None):
 def _page_side(pg) -> _lib.Side:
     """The gaac_side descriptor of a Page, built once and kept on the Page object (rebuilt when its escape stream was replaced)."""
     sd = getattr(pg, "_attn_side", None)
+    if pg.S == 0:                                  # a Page without tokens (a rank past the end of a short context): nothing is read through
+        if sd is None:                             # these pointers, but the library wants them non-null, so they point at a small zero buffer
+            z = torch.zeros(256, dtype=torch.uint8, device=pg.base3.device)
+            sd = _side(z, z, z, z, z, pg.ovf_head_start, pg.base3, pg.base4, None)
+            pg._attn_side, pg._attn_keep = sd, z
+        return sd
     if sd is None or sd.ovf != pg.ovf.data_ptr() or sd.sm != pg.sm.data_ptr():
         sd = _side(pg.sm, pg.codes, pg.flags, pg.tile_off, pg.ovf, pg.ovf_head_start, pg.base3, pg.base4, None)
         pg._attn_side = sd
@@ -176,7 +182,7 @@ def _pages_call(q, kp, vp, B, n_q, n_kv, scale, nsplit, out=None, out_f32=None, 
     q2 = q.reshape(B * n_q, 128)
     if not q2.is_contiguous(): q2 = q2.contiguous()
     ws = workspace(dev, B, n_q, nsplit)
-    _lib.check(_lib.lib().gaac_decode_attn_pages(_page_side(kp), _page_side(vp), q2.data_ptr(), B, n_q, n_kv, kp.S, kp.sm.shape[1] // 128,
+    _lib.check(_lib.lib().gaac_decode_attn_pages(_page_side(kp), _page_side(vp), q2.data_ptr(), B, n_q, n_kv, kp.S, max(16, kp.sm.shape[1] // 128),
                                                  float(scale if scale is not None else 128 ** -0.5), int(nsplit), kp.base3.size(0),
                                                  ws.data_ptr(), ws.numel(), _lib.ptr(out), _lib.ptr(out_f32), _lib.ptr(part), exchange,
                                                  1 if fused else 0, _lib.stream_ptr(dev)), "gaac_decode_attn_pages")

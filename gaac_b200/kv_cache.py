@@ -171,7 +171,11 @@ class CompressedKVCache:
         words = self._slot_status[torch.tensor(slots, dtype=torch.long, device=self.S.device)].tolist()
         wanted = max(max(w[1], w[3]) for w in words) + TILE_MAX_ESC + _OVER_READ
         if wanted > self.k.ovf_cap:
-            self._grow(wanted)
+            try:
+                self._grow(wanted)
+            except RuntimeError:                     # the streams may not move: the prefills stay unsettled, and every later call says so again
+                self._pending, self._pending_bytes = pending, sum(p[1].numel() for p in pending.values())
+                raise
         for slot, w in zip(slots, words):
             if w[0] or w[2]:
                 L, scratch = pending[slot]

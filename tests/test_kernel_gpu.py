@@ -182,6 +182,52 @@ def test_peer_exchange_two_ranks_on_one_gpu():
     assert int(xs[0]._state[0]) == 4 and int(xs[1]._state[0]) == 4               # both ranks counted four exchanges
 
 
+@pytest.mark.parametrize("world", [4, 8])
+def test_peer_exchange_many_ranks_on_one_gpu(world):
+    """The same stream-ordered emulation with 4 and 8 ranks, uneven context parts (the last rank gets the remainder, one rank an
+    empty part): ranks 0..world-2 push only, the last rank runs the fused launch after them (all rows are there already), the
+    others merge with the separate kernel.  Every rank must produce the same output, bit for bit."""
+    import torch
+    from gaac_b200 import Codec, TileEncoder
+    from gaac_b200.kernel import _pages_call
+    from gaac_b200.dist import PeerExchange
+    n_kv, G, S = 2, 4, 16 * 131
+    n_q = n_kv * G
+    k16, v16 = O.synth_kv("k", n_kv, S, 21), O.synth_kv("v", n_kv, S, 21)
+    k, v = to_bf16_cuda(k16), to_bf16_cuda(v16)
+    ck, cv = Codec(n_kv).calibrate(k), Codec(n_kv).calibrate(v)
+    cuts = [0] + [16 * int(round(131 * (r + 1) / world * (0.7 if r % 2 else 1.2))) for r in range(world - 1)]
+    cuts = sorted(min(c, S) for c in cuts) + [S]
+    cuts[2] = cuts[1]                                                            # rank 1 holds no tokens at all
+    parts = []
+    for r in range(world):
+        lo, hi = cuts[r], cuts[r + 1]
+        if hi > lo:
+            parts.append((TileEncoder("k").encode(ck, k[:, lo:hi].contiguous()), TileEncoder("v").encode(cv, v[:, lo:hi].contiguous())))
+        else:
+            parts.append(None)
+    bufs = [PeerExchange.local_buffer(world, n_q, "cuda", groups=n_kv) for _ in range(world)]
+    xs = [PeerExchange.local(bufs, r, n_q, groups=n_kv) for r in range(world)]
+    rng = np.random.default_rng(9)
+    empty = (TileEncoder("k").encode(ck, k[:, :0].contiguous()), TileEncoder("v").encode(cv, v[:, :0].contiguous()))
+    for step in range(3):
+        q16 = O.f32_to_bf16(rng.standard_normal((1, n_q, 128)).astype(np.float32))
+        q = to_bf16_cuda(q16)
+        o32 = [torch.empty(n_q, 128, dtype=torch.float32, device="cuda") for _ in range(world)]
+        for r in range(world):
+            kp, vp = parts[r] if parts[r] is not None else empty
+            if r < world - 1:
+                _pages_call(q, kp, vp, 1, n_q, n_kv, SCALE, 3, exchange=xs[r].x)
+            else:
+                _pages_call(q, kp, vp, 1, n_q, n_kv, SCALE, 3, out=torch.empty(n_q, 128, dtype=torch.bfloat16, device="cuda"), out_f32=o32[r], exchange=xs[r].x, fused=True)
+        for r in range(world - 1):
+            xs[r].merge(n_kv, out_f32=o32[r], n_heads=n_q)
+        assert_attention_close(o32[0].cpu().numpy(), q16[0], k16.transpose(1, 0, 2), v16.transpose(1, 0, 2), SCALE, step)
+        for r in range(world):
+            assert not xs[r].error()
+            assert torch.equal(o32[r], o32[0]), (step, r)
+
+
 def test_peer_exchange_wait_runs_out():
     """A merge whose peers never push gives up after its bounded wait: error flag set, output zero, GPU still usable; and the
     exchange after it works again (flags carry the exchange number, so a lost exchange does not shift the later ones)."""
