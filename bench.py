@@ -642,7 +642,8 @@ def run_paged16(args):
     n_q, TS = n_kv * G, OVF_OFF + ovf_slot
     rng = np.random.default_rng(0)
     lens_all = [int(l) // 16 * 16 + int(t) for l, t in zip(rng.integers(4096, 65537, B_all), rng.integers(0, 16, B_all))]
-    mine = shard_sequences(lens_all, world)[rank]
+    shard_world, shard_rank = (int(x) for x in args.shard.split("/")[::-1]) if args.shard else (world, rank)
+    mine = shard_sequences(lens_all, shard_world)[shard_rank]
     lens0 = [lens_all[i] for i in mine]
     B = len(lens0)
     warm = max(3, args.warmup)
@@ -678,7 +679,7 @@ def run_paged16(args):
     freeq = torch.empty(max(B, 1) * 2 * n_kv, dtype=torch.int32, device=dev)
     q = torch.randn(max(B, 1), n_q, 128, device=dev).to(torch.bfloat16)
     out = torch.empty(max(B, 1), n_q * 128, dtype=torch.bfloat16, device=dev)
-    ns = choose_nsplit_sm100(max(B, 1), n_kv, max(lens0 + [16]), ragged=True, total_tokens=sum(lens0))
+    ns = args.nsplit or choose_nsplit_sm100(max(B, 1), n_kv, max(lens0 + [16]), ragged=True, total_tokens=sum(lens0))
 
     def attend(s):
         paged_attention(q, out, buf, st.raw, st.mt, btd, sl_d[s], st.bases, TS, n_q, n_kv, ns)
@@ -942,6 +943,8 @@ def main():
     ap.add_argument("--no-side", action="store_true", help="skip the side measurements (CPU baseline, encoder, library decode, reference kernel)")
     ap.add_argument("--profile", action="store_true", help="ctx64k / ctx128k / paged16: only the warm-up and --steps eager steps (no graphs, no preload, no e2e, no side measurements): the command to run under ncu")
     ap.add_argument("--profile-encode", action="store_true", help="only the block encoder on [8, 65536, 128] K and V, --steps times each: the command to run under ncu")
+    ap.add_argument("--nsplit", type=int, default=0, help="paged16: split count instead of the heuristic's")
+    ap.add_argument("--shard", default="", help="paged16, single process: run the sequences rank r of n ranks would get, as 'r/n'")
     ap.add_argument("--pool-blocks", type=int, default=1 << 20, help="paged16: blocks of the paged pool over all ranks (3008 B x 16 tile slots each)")
     ap.add_argument("--prefill-layers", type=int, default=8, help="batch64: layers of the prefill-encode pass that are timed (scaled to 64)")
     args = ap.parse_args()
