@@ -53,13 +53,22 @@ __device__ __forceinline__ void stage_rows(WarpScratch& ws, const uint16_t* src,
 // The same staging with asynchronous 16-byte copies (rows >= nvalid are zero-filled by the copy unit): the caller commits the
 // group and waits for it before encode_tile_warp, so the rows of the next tile travel while the current one is encoded.
 __device__ __forceinline__ void stage_rows_async(WarpScratch& ws, const uint16_t* src, long row_stride, int nvalid, int lane) {
+  // piece k of a lane: row 2k + (lane >> 4), columns 8 * (lane & 15) .. +7: one source and one destination address per lane, a
+  // fixed step per piece
+  const int r0 = lane >> 4, col = (lane & 15) * 8;
+  const uint16_t* g = src + (long)r0 * row_stride + col;
+  const unsigned d = (unsigned)__cvta_generic_to_shared(&ws.xs[r0 * XS_STRIDE + col]);
+  const long step = 2 * row_stride;
+  if (nvalid == T) {
 #pragma unroll
-  for (int k = 0; k < 8; k++) {
-    const int c = lane + 32 * k, row = c >> 4, col = (c & 15) * 8;
-    const bool live = row < nvalid;
-    const uint16_t* g = src + (live ? (long)row * row_stride + col : 0);
-    const unsigned d = (unsigned)__cvta_generic_to_shared(&ws.xs[row * XS_STRIDE + col]);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(g), "r"(live ? 16 : 0) : "memory");
+    for (int k = 0; k < 8; k++)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d + k * (2 * XS_STRIDE * 2)), "l"(g + k * step) : "memory");
+  } else {
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+      const bool live = 2 * k + r0 < nvalid;
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d + k * (2 * XS_STRIDE * 2)), "l"(live ? g + k * step : src), "r"(live ? 16 : 0) : "memory");
+    }
   }
 }
 __device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
