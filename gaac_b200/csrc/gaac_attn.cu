@@ -79,6 +79,9 @@ namespace gaac {
 #ifndef GAAC_DEEP
 #define GAAC_DEEP 0
 #endif
+#ifndef GAAC_CTAS_PER_SM
+#define GAAC_CTAS_PER_SM 1
+#endif
 constexpr int ATT_WARPS = GAAC_WARPS;
 constexpr int ATT_THREADS = ATT_WARPS * 32;
 constexpr int NSTAGE = 2;
@@ -622,7 +625,7 @@ __device__ __forceinline__ float x_merge_rows(const float* base, int world, long
 }
 
 template <bool PAGED, bool DUMP>
-__global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(ATT_THREADS, GAAC_CTAS_PER_SM) decode_attn_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ int s_next, s_last;
   const int bh = blockIdx.x, split = blockIdx.y, tid = threadIdx.x, lane = tid & 31, j = lane & 3, r = lane >> 2;
@@ -780,12 +783,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
     const int brow = PAGED ? kvh : ch % p.n_base_rows;
     const uint8_t* b3k = (PAGED ? p.b3k : p.K.base3) + brow * D; const uint8_t* b4k = (PAGED ? p.b4k : p.K.base4) + brow * D;
     const uint8_t* b3v = (PAGED ? p.b3v : p.V.base3) + brow * D; const uint8_t* b4v = (PAGED ? p.b4v : p.V.base4) + brow * D;
-    if (tid >= 256 && tid < 272) {                    // K: lane class jj, group gg -> words 2gg, 2gg+1
-      const int t = tid - 256, jj = t >> 2, gg = t & 3; u32 w3[8], w4[8];
+    constexpr int KB_T0 = ATT_THREADS >= 320 ? 256 : 0, VB_T0 = KB_T0 + 32;       // which threads build the base words (beside the escape-byte table when the CTA is small)
+    if (tid >= KB_T0 && tid < KB_T0 + 16) {           // K: lane class jj, group gg -> words 2gg, 2gg+1
+      const int t = tid - KB_T0, jj = t >> 2, gg = t & 3; u32 w3[8], w4[8];
       k_base_words(b3k, jj, w3); k_base_words(b4k, jj, w4);
       *reinterpret_cast<u32x4*>(smem + TB_KB + 16 * t) = u32x4{w3[2 * gg], w3[2 * gg + 1], w4[2 * gg] - w3[2 * gg], w4[2 * gg + 1] - w3[2 * gg + 1]};
-    } else if (tid >= 288 && tid < 304) {             // V: lane class rr, group gg
-      const int t = tid - 288, rr = t >> 1, gg = t & 1; u32 w3[4], w4[4];
+    } else if (tid >= VB_T0 && tid < VB_T0 + 16) {    // V: lane class rr, group gg
+      const int t = tid - VB_T0, rr = t >> 1, gg = t & 1; u32 w3[4], w4[4];
       v_base_words(b3v, rr, w3); v_base_words(b4v, rr, w4);
       *reinterpret_cast<u32x4*>(smem + TB_VB + 16 * t) = u32x4{w3[2 * gg], w3[2 * gg + 1], w4[2 * gg] - w3[2 * gg], w4[2 * gg + 1] - w3[2 * gg + 1]};
     }
@@ -1089,7 +1093,7 @@ constexpr int TABLE256_BYTES = T256_XCH + (ATT_WARPS / 2) * 2 * XCH_PAR_BYTES;
 constexpr int ATT256_SMEM = TABLE256_BYTES + ATT_WARPS * WARP_SMEM;
 static_assert(TB_KB == 2048 && TB_VB == 2048 + 256 && TABLE256_BYTES % 16 == 0 && ATT256_SMEM + 64 <= 232448, "table layout shared with the 128-dim kernel; one CTA per SM");
 
-__global__ void __launch_bounds__(ATT_THREADS, 1) paged256_attn_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(ATT_THREADS, GAAC_CTAS_PER_SM) paged256_attn_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ int s_next;
   const int bh = blockIdx.x, split = blockIdx.y, tid = threadIdx.x, lane = tid & 31, j = lane & 3, r = lane >> 2;
@@ -1137,13 +1141,14 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) paged256_attn_kernel(const __g
 #endif
   {   // tables of both halves; exchange slots start out zero
     if (tid < 256) { fill_lutx(reinterpret_cast<u32x2*>(smem + TB_LUTX), tid); fill_lutx(reinterpret_cast<u32x2*>(smem + T256_HALF + TB_LUTX), tid); }
-    if (tid >= 256 && tid < 288) {                    // K: half, lane class jj, group gg
-      const int t = tid - 256, h2 = t >> 4, jj = (t >> 2) & 3, gg = t & 3; u32 w3[8], w4[8];
+    constexpr int KB_T0 = ATT_THREADS >= 320 ? 256 : 0, VB_T0 = KB_T0 + 32;
+    if (tid >= KB_T0 && tid < KB_T0 + 32) {           // K: half, lane class jj, group gg
+      const int t = tid - KB_T0, h2 = t >> 4, jj = (t >> 2) & 3, gg = t & 3; u32 w3[8], w4[8];
       const int row = 2 * kvh + h2;
       k_base_words(p.b3k + row * D, jj, w3); k_base_words(p.b4k + row * D, jj, w4);
       *reinterpret_cast<u32x4*>(smem + h2 * T256_HALF + TB_KB + 16 * (t & 15)) = u32x4{w3[2 * gg], w3[2 * gg + 1], w4[2 * gg] - w3[2 * gg], w4[2 * gg + 1] - w3[2 * gg + 1]};
-    } else if (tid >= 288 && tid < 320) {             // V: half, lane class rr, group gg
-      const int t = tid - 288, h2 = t >> 4, rr = (t >> 1) & 7, gg = t & 1; u32 w3[4], w4[4];
+    } else if (tid >= VB_T0 && tid < VB_T0 + 32) {    // V: half, lane class rr, group gg
+      const int t = tid - VB_T0, h2 = t >> 4, rr = (t >> 1) & 7, gg = t & 1; u32 w3[4], w4[4];
       const int row = 2 * kvh + h2;
       v_base_words(p.b3v + row * D, rr, w3); v_base_words(p.b4v + row * D, rr, w4);
       *reinterpret_cast<u32x4*>(smem + h2 * T256_HALF + TB_VB + 16 * (t & 15)) = u32x4{w3[2 * gg], w3[2 * gg + 1], w4[2 * gg] - w3[2 * gg], w4[2 * gg + 1] - w3[2 * gg + 1]};
