@@ -43,7 +43,8 @@ namespace gaac {
 #define GAAC_SPLIT_P 1
 #endif
 // Build-time knobs of the experiments that shaped the kernel (the defaults are what ships):
-//   GAAC_WARPS    warps per CTA (one CTA per SM; the register budget per thread follows from it)
+//   GAAC_WARPS    warps per CTA (one CTA per SM; the register budget per thread follows from it).  Only 16 is tested for results;
+//                 12 and 18 were timing experiments, 8 is known to give wrong output
 //   GAAC_ESC_WIN  escape bytes staged per tile and kind
 //   GAAC_QSMEM    1: the query fragments live in a shared-memory table read once per K group instead of 16 registers per lane
 #ifndef GAAC_WARPS
@@ -78,9 +79,6 @@ namespace gaac {
 //                 for instruction issue, not for memory
 #ifndef GAAC_DEEP
 #define GAAC_DEEP 0
-#endif
-#ifndef GAAC_CTAS_PER_SM
-#define GAAC_CTAS_PER_SM 1
 #endif
 constexpr int ATT_WARPS = GAAC_WARPS;
 constexpr int ATT_THREADS = ATT_WARPS * 32;
@@ -625,7 +623,7 @@ __device__ __forceinline__ float x_merge_rows(const float* base, int world, long
 }
 
 template <bool PAGED, bool DUMP>
-__global__ void __launch_bounds__(ATT_THREADS, GAAC_CTAS_PER_SM) decode_attn_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ int s_next, s_last;
   const int bh = blockIdx.x, split = blockIdx.y, tid = threadIdx.x, lane = tid & 31, j = lane & 3, r = lane >> 2;
@@ -1093,7 +1091,7 @@ constexpr int TABLE256_BYTES = T256_XCH + (ATT_WARPS / 2) * 2 * XCH_PAR_BYTES;
 constexpr int ATT256_SMEM = TABLE256_BYTES + ATT_WARPS * WARP_SMEM;
 static_assert(TB_KB == 2048 && TB_VB == 2048 + 256 && TABLE256_BYTES % 16 == 0 && ATT256_SMEM + 64 <= 232448, "table layout shared with the 128-dim kernel; one CTA per SM");
 
-__global__ void __launch_bounds__(ATT_THREADS, GAAC_CTAS_PER_SM) paged256_attn_kernel(const __grid_constant__ AttnParams p) {
+__global__ void __launch_bounds__(ATT_THREADS, 1) paged256_attn_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ int s_next;
   const int bh = blockIdx.x, split = blockIdx.y, tid = threadIdx.x, lane = tid & 31, j = lane & 3, r = lane >> 2;
