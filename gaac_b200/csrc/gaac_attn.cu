@@ -951,17 +951,18 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       p.pa[pidx * D + d] = Ac;
     }
   }
-  // ---- the last CTA of this (row, kv head) merges the splits
-  __threadfence();
+  // ---- the last CTA of this (row, kv head) merges the splits.  The ticket is taken with an acquire-release atomic at GPU scope
+  // by one thread between two CTA barriers: the barrier before it orders every thread's partial stores before the release, the
+  // barrier after it orders the acquire before every thread's loads of the other CTAs' partials - no per-thread fence is needed.
   __syncthreads();
   if (tid == 0) {
-    const int ticket = atomicAdd(&p.counters[bh], 1);
+    int ticket;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(ticket) : "l"(p.counters + bh) : "memory");
     s_last = (ticket == NS - 1);
     if (s_last) p.counters[bh] = 0;                 // leave the counter ready for the next call
   }
   __syncthreads();
   if (!s_last) return;
-  __threadfence();
   // All loads below are independent of one another (no per-split dependent chain): scale factors first, then the weighted sum
   // with one warp per split and 16-byte loads, then a cross-warp sum in shared memory.
   {
@@ -1038,13 +1039,12 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       }
     }
     if (p.x_recv) {
-      // The rows of all ranks are written first; then ONE fence per flag writer makes them visible system-wide (the barrier
-      // orders the other threads' stores before it), and this rank's flag of the group is set to the exchange number on
-      // every rank.  Flags carry the number instead of counting arrivals, so the set of groups may differ between
+      // The rows of all ranks are written first; the barrier orders every thread's stores before the flag writers' release
+      // stores (system scope, cumulative over the barrier), which set this rank's flag of the group to the exchange number on
+      // every rank.  (A separate system-scope fence in front of the release store cost 3 us per layer and added nothing.)  Flags carry the number instead of counting arrivals, so the set of groups may differ between
       // exchanges and a lost exchange does not shift the later ones.
       __syncthreads();
       if (tid < p.x_world) {
-        __threadfence_system();
         asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.x_flags[tid] + (long)bh * p.x_world + p.x_rank), "r"(x_ep + 1) : "memory");
       }
       if (!p.x_fused) return;                        // the wait-and-merge runs as its own launch (gaac_exchange_merge)
