@@ -33,8 +33,7 @@ class Paged(C.Structure):
 
 class Exchange(C.Structure):
     """gaac_exchange"""
-    _fields_ = [("recv", vp), ("flags", vp), ("epoch", vp), ("ticket", vp), ("err", vp), ("rank", i32), ("world", i32),
-                ("rows_cap", i32), ("groups_cap", i32)]
+    _fields_ = [("recv", vp), ("epoch", vp), ("ticket", vp), ("err", vp), ("rank", i32), ("world", i32), ("rows_cap", i32)]
 
 
 _SIGNATURES = {
@@ -60,7 +59,7 @@ _SIGNATURES = {
     "gaac_combine": (i32, [vp, vp, vp, i64, i32, vp, vp, vp]),
     "gaac_combine_parts": (i32, [vp, i64, i32, vp, vp, vp]),
     "gaac_decode_attn_push": (i32, [C.POINTER(Side), C.POINTER(Side), vp, vp, i32, i32, i32, vp, i64, f32, i32, vp, i32, i32, vp, sz, C.POINTER(Exchange), vp]),
-    "gaac_exchange_merge": (i32, [C.POINTER(Exchange), i64, i32, vp, vp, vp]),
+    "gaac_exchange_merge": (i32, [C.POINTER(Exchange), i64, vp, vp, vp]),
     "gaac_append_kv": (i32, [C.POINTER(Store), C.POINTER(Store), vp, vp, vp, i32, i32, vp, vp, i64, i64, i32, vp, vp]),
     "gaac_cache_prefill_scratch_bytes": (C.c_size_t, [i64, i32]),
     "gaac_cache_prefill": (i32, [C.POINTER(Store), C.POINTER(Store), vp, vp, i64, i64, i32, i32, vp, vp, i64, i64, i32, vp, C.c_size_t, vp, i32, vp]),
@@ -74,7 +73,7 @@ _SIGNATURES = {
     "gaac_static_workspace_error": (i32, [vp, i32, vp]),
 }
 EXPORTS = tuple(_SIGNATURES)
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 
 def lib():

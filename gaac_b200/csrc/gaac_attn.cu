@@ -115,6 +115,7 @@ static_assert(TABLE_BYTES % 16 == 0 && STAGE_BYTES % 16 == 0 && ST_KSM % 16 == 0
               ST_VSM % 16 == 0 && ST_VCD % 16 == 0 && ST_VFL % 16 == 0 && ST_VESC % 16 == 0 && ESC_COPY % 16 == 0 && ST_MBAR % 8 == 0 && SM_ROW % 16 == 0,
               "bulk copies need 16-byte aligned shared-memory destinations and sizes");
 static_assert(ATT_SMEM + 64 <= 232448, "one CTA per SM: at most 227 KB of shared memory, static part included");
+static_assert(ATT_THREADS / 128 * 2 >= 8, "the fused exchange keeps at most two merged heads per thread");
 constexpr unsigned FULLM = 0xffffffffu;
 constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
 
@@ -133,7 +134,7 @@ struct AttnParams {
   // cross-GPU exchange (x_recv == NULL: unused): the partial of every query head is stored into every rank's receive
   // buffer, then this rank's arrival flag of the (row, kv head) group on every rank is set to the exchange number; with
   // x_fused the same CTA then waits (bounded) for the other ranks' flags, merges all ranks' rows and writes the output
-  float* const* x_recv; int* const* x_flags; int* x_epoch; int* x_ticket; int* x_err; int x_rank, x_world, x_rows_cap, x_fused;
+  unsigned long long* const* x_recv; int* x_epoch; int* x_ticket; int* x_err; int x_rank, x_world, x_rows_cap, x_fused;
   // debug instantiation only: the rebuilt BF16 K / V rows are written to [B*n_kv, dump_S, 128] (row = token of the head)
   uint16_t* dump_k; uint16_t* dump_v; long dump_S;
 };
@@ -595,31 +596,43 @@ __device__ __forceinline__ void raw_accum(WarpAcc& A, const uint16_t* vraw, int 
   }
 }
 
-// ---- cross-GPU exchange helpers.  Every wait is bounded: after X_WAIT_LIMIT polls (about a second) the waiter gives up, so a
-// missing peer never hangs the GPU.  Flags are compared as wrapping differences, so the exchange number may wrap around.
+// ---- cross-GPU exchange helpers.  A receive buffer holds 8-byte entries: the low word is an fp32 value, the high word the
+// number of the exchange it belongs to.  An entry is written with ONE 64-bit store and read with one 64-bit load, so a reader
+// that sees the right number has the value that came with it: no flag, no fence and no second trip over NVLink is needed to
+// know that a row has arrived.  Every wait is bounded: after X_WAIT_LIMIT polls (about a second) the reader gives up, so a
+// missing peer never hangs the GPU.
 constexpr int X_WAIT_LIMIT = 1000000;
-__device__ __forceinline__ bool x_wait_flag(const int* f, int want) {
+__device__ __forceinline__ void x_store(unsigned long long* p, float v, u32 tag) {
+  const unsigned long long e = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+  asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(e) : "memory");
+}
+__device__ __forceinline__ bool x_load(const unsigned long long* p, u32 tag, float& v) {
   for (int it = 0; it < X_WAIT_LIMIT; it++) {
-    int v;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-    if ((int)((unsigned)v - (unsigned)want) >= 0) return true;
+    unsigned long long e;
+    asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(e) : "l"(p) : "memory");
+    if ((u32)(e >> 32) == tag) { v = __uint_as_float((u32)e); return true; }
     if (it > 64) __nanosleep(100);
   }
+  v = 0.f;
   return false;
 }
-// Merge the rows of all ranks for query head qh, element d: base = this exchange's half of the receive buffer,
-// [world][rows_cap][130] floats of (m in natural-log units, l, acc[128]); same algebra as the split merge.
-__device__ __forceinline__ float x_merge_rows(const float* base, int world, long rows_cap, long qh, int d) {
+// Wait for and merge the rows of all ranks for query head qh, element d: base = this exchange's half of the receive buffer,
+// [world][rows_cap][130] entries of (m in natural-log units, l, acc[128]); same algebra as the split merge.  Returns false when
+// a row did not arrive in time.
+__device__ __forceinline__ bool x_merge_rows(const unsigned long long* base, int world, long rows_cap, long qh, int d, u32 tag, float& out) {
   float M = -CUDART_INF_F;
-  for (int s = 0; s < world; s++) M = fmaxf(M, __ldcg(base + (s * rows_cap + qh) * 130));
+  bool ok = true;
+  for (int s = 0; s < world && ok; s++) { float m; ok = x_load(base + (s * rows_cap + qh) * 130, tag, m); M = fmaxf(M, m); }   // one bound in all: stop at the first row that does not come
   float L = 0.f, Ac = 0.f;
-  for (int s = 0; s < world; s++) {
-    const float* pp = base + (s * rows_cap + qh) * 130;
-    const float ms = __ldcg(pp);
+  for (int s = 0; s < world && ok; s++) {
+    const unsigned long long* pp = base + (s * rows_cap + qh) * 130;
+    float ms, l, a;
+    ok &= x_load(pp, tag, ms) & x_load(pp + 1, tag, l) & x_load(pp + 2 + d, tag, a);
     const float f = (ms == -CUDART_INF_F) ? 0.f : __expf(ms - M);
-    L += __ldcg(pp + 1) * f; Ac += __ldcg(pp + 2 + d) * f;
+    L += l * f; Ac += a * f;
   }
-  return L > 0.f ? Ac / L : 0.f;
+  out = (ok && L > 0.f) ? Ac / L : 0.f;
+  return ok;
 }
 
 template <bool PAGED, bool DUMP>
@@ -1024,9 +1037,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       if (p.x_recv) {                                // the same partial, pushed to every rank's receive buffer over NVLink
         const long row = ((long)((x_ep & 1) * p.x_world + p.x_rank) * p.x_rows_cap + qh) * 130;
         for (int rk = 0; rk < p.x_world; rk++) {
-          float* o = p.x_recv[rk] + row;
-          if (d == 0) { o[0] = M * LN2; o[1] = L; }
-          o[2 + d] = Ac;
+          unsigned long long* o = p.x_recv[rk] + row;
+          if (d == 0) { x_store(o, M * LN2, (u32)x_ep + 1u); x_store(o + 1, L, (u32)x_ep + 1u); }
+          x_store(o + 2 + d, Ac, (u32)x_ep + 1u);
         }
       } else if (p.part) {                           // un-normalised partial for a cross-GPU merge: m in natural-log units
         float* o = p.part + qh * 130;
@@ -1039,28 +1052,21 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
       }
     }
     if (p.x_recv) {
-      // The rows of all ranks are written first; the barrier orders every thread's stores before the flag writers' release
-      // stores (system scope, cumulative over the barrier), which set this rank's flag of the group to the exchange number on
-      // every rank.  (A separate system-scope fence in front of the release store cost 3 us per layer and added nothing.)  Flags carry the number instead of counting arrivals, so the set of groups may differ between
-      // exchanges and a lost exchange does not shift the later ones.
-      __syncthreads();
-      if (tid < p.x_world) {
-        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.x_flags[tid] + (long)bh * p.x_world + p.x_rank), "r"(x_ep + 1) : "memory");
-      }
+      // Every entry carries the exchange number, so nothing else announces the rows (see x_store / x_load).
       if (!p.x_fused) return;                        // the wait-and-merge runs as its own launch (gaac_exchange_merge)
       // ---- fused: wait (bounded) for the rows of this group from every rank, merge them, write the output
-      __shared__ int s_xok;
-      if (tid == 0) s_xok = 1;
-      __syncthreads();
-      if (tid < p.x_world && !x_wait_flag(p.x_flags[p.x_rank] + (long)bh * p.x_world + tid, x_ep + 1)) { s_xok = 0; atomicExch(p.x_err, 1); }
-      __syncthreads();
-      const bool ok = s_xok != 0;
-      const float* base = p.x_recv[p.x_rank] + (long)(x_ep & 1) * p.x_world * p.x_rows_cap * 130;
-      for (int g = tid >> 7; g < G; g += ATT_THREADS / 128) {
+      const unsigned long long* base = p.x_recv[p.x_rank] + (long)(x_ep & 1) * p.x_world * p.x_rows_cap * 130;
+      float v[2] = {0.f, 0.f};
+      int bad = 0;
+      for (int g = tid >> 7, i = 0; g < G; g += ATT_THREADS / 128, i++)
+        bad |= !x_merge_rows(base, p.x_world, p.x_rows_cap, qh0 + g, d, (u32)x_ep + 1u, v[i]);
+      const int any_bad = __syncthreads_or(bad);     // a group whose rows did not all arrive is reported and comes back as zeros
+      if (any_bad && tid == 0) atomicExch(p.x_err, 1);
+      for (int g = tid >> 7, i = 0; g < G; g += ATT_THREADS / 128, i++) {
         const long qh = qh0 + g;
-        const float v = ok ? x_merge_rows(base, p.x_world, p.x_rows_cap, qh, d) : 0.f;
-        if (p.out) p.out[qh * D + d] = __bfloat16_as_ushort(__float2bfloat16(v));
-        if (p.out_f32) p.out_f32[qh * D + d] = v;
+        const float o = any_bad ? 0.f : v[i];
+        if (p.out) p.out[qh * D + d] = __bfloat16_as_ushort(__float2bfloat16(o));
+        if (p.out_f32) p.out_f32[qh * D + d] = o;
       }
       // the exchange number advances when every group of this launch is through (each has read it by then)
       __syncthreads();
@@ -1247,20 +1253,17 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) paged256_attn_kernel(const __g
 
 // Second half of the cross-GPU exchange as a launch of its own (the attention kernel was launched push-only): wait until
 // every rank's rows of this exchange have arrived in this GPU's receive buffer, merge them, and advance the exchange number.
-// One CTA per query head; heads_per_group consecutive query heads share the flags of one (row, kv head) group.  After
-// X_WAIT_LIMIT polls the kernel sets *err, writes zeros and returns.
-__global__ void __launch_bounds__(128) exchange_merge_kernel(float* const* x_recv, int* const* x_flags, int* epoch, int* ticket, int* err, int rank, int world,
-                                                              int heads_per_group, long rows_cap, uint16_t* __restrict__ out, float* __restrict__ out_f32) {
-  __shared__ int ok_s;
+// One CTA per query head.  A row that has not arrived after X_WAIT_LIMIT polls sets *err and the head comes back as zeros.
+__global__ void __launch_bounds__(128) exchange_merge_kernel(unsigned long long* const* x_recv, int* epoch, int* ticket, int* err, int rank, int world,
+                                                              long rows_cap, uint16_t* __restrict__ out, float* __restrict__ out_f32) {
   const long qh = blockIdx.x; const int d = threadIdx.x;
   asm volatile("griddepcontrol.wait;" ::: "memory");                   // resident early, runs after the attention kernel has completed
   asm volatile("griddepcontrol.launch_dependents;" ::);
   const int ep = __ldcg(epoch);                                         // advanced only after every CTA has taken its ticket
-  if (d == 0) ok_s = 1;
-  __syncthreads();
-  if (d < world && !x_wait_flag(x_flags[rank] + (qh / heads_per_group) * world + d, ep + 1)) { ok_s = 0; atomicExch(err, 1); }
-  __syncthreads();
-  const float v = ok_s ? x_merge_rows(x_recv[rank] + (long)(ep & 1) * world * rows_cap * 130, world, rows_cap, qh, d) : 0.f;
+  float v;
+  const int bad = !x_merge_rows(x_recv[rank] + (long)(ep & 1) * world * rows_cap * 130, world, rows_cap, qh, d, (u32)ep + 1u, v);
+  const int any_bad = __syncthreads_or(bad);
+  if (any_bad) { v = 0.f; if (d == 0) atomicExch(err, 1); }
   if (out) out[qh * D + d] = __bfloat16_as_ushort(__float2bfloat16(v));
   if (out_f32) out_f32[qh * D + d] = v;
   __syncthreads();
@@ -1353,8 +1356,7 @@ static int sm_count_of_current_device() {
 }
 
 static bool exchange_ok(const gaac_exchange* x) {
-  return x && x->recv && x->flags && x->epoch && x->ticket && x->err && x->world >= 1 && x->world <= 64 && x->rank >= 0 && x->rank < x->world &&
-         x->rows_cap > 0 && x->groups_cap > 0;
+  return x && x->recv && x->epoch && x->ticket && x->err && x->world >= 1 && x->world <= 64 && x->rank >= 0 && x->rank < x->world && x->rows_cap > 0;
 }
 
 // What the slot-layout entry points differ in.
@@ -1373,7 +1375,7 @@ static int slot_attn(const gaac_side* K, const gaac_side* V, const void* q, cons
   if (B <= 0 || n_q <= 0 || n_kv <= 0 || nsplit <= 0 || nsplit > 1024 || S_pad <= 0 || S_pad % T || n_base_rows <= 0) return GAAC_E_ARG;
   if (!seq_len && (S_uniform < 0 || S_uniform > S_pad)) return GAAC_E_ARG;
   if (n_q % n_kv || n_q / n_kv < 1 || n_q / n_kv > 8) return GAAC_E_UNSUPPORTED;
-  if (x && ((int64_t)B * n_q > x->rows_cap || (int64_t)B * n_kv > x->groups_cap)) return GAAC_E_ARG;
+  if (x && (int64_t)B * n_q > x->rows_cap) return GAAC_E_ARG;
   // fused exchange: a CTA per (row, kv head) waits for the other GPUs inside the kernel, so every CTA of the grid must be
   // resident at once (one CTA per SM); larger grids use the push + gaac_exchange_merge pair
   if (x && o.fused && (int64_t)B * n_kv * nsplit > sm_count_of_current_device()) return GAAC_E_UNSUPPORTED;
@@ -1390,7 +1392,7 @@ static int slot_attn(const gaac_side* K, const gaac_side* V, const void* q, cons
   p.q = (const uint16_t*)q; p.B = B; p.n_q = n_q; p.n_kv = n_kv; p.G = n_q / n_kv; p.scale_log2 = scale * LOG2E; p.nsplit = nsplit;
   p.out = (uint16_t*)o.out; p.out_f32 = o.out_f32; p.part = o.part;
   if (x) {
-    p.x_recv = x->recv; p.x_flags = x->flags; p.x_epoch = x->epoch; p.x_ticket = x->ticket; p.x_err = x->err;
+    p.x_recv = x->recv; p.x_epoch = x->epoch; p.x_ticket = x->ticket; p.x_err = x->err;
     p.x_rank = x->rank; p.x_world = x->world; p.x_rows_cap = x->rows_cap; p.x_fused = o.fused ? 1 : 0;
   }
   if (int e = carve_workspace(ws, ws_bytes, B, n_q, nsplit, p)) return e;
@@ -1484,15 +1486,15 @@ extern "C" int gaac_decode_attn_exchange(const gaac_side* K, const gaac_side* V,
   return slot_attn(K, V, q_bf16, slot, B, n_q, n_kv, seq_len, 0, S_pad, scale, nsplit, tail_len, tail_cap, n_base_rows, workspace, workspace_bytes, o, stream);
 }
 
-extern "C" int gaac_exchange_merge(const gaac_exchange* x, int64_t n_heads, int groups, void* out_bf16, float* out_f32, void* stream) {
+extern "C" int gaac_exchange_merge(const gaac_exchange* x, int64_t n_heads, void* out_bf16, float* out_f32, void* stream) {
   if (!exchange_ok(x)) return GAAC_E_ARG;
-  if (n_heads <= 0 || groups <= 0 || n_heads % groups || n_heads > x->rows_cap || groups > x->groups_cap || (!out_bf16 && !out_f32)) return GAAC_E_ARG;
+  if (n_heads <= 0 || n_heads > x->rows_cap || (!out_bf16 && !out_f32)) return GAAC_E_ARG;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)n_heads); cfg.blockDim = dim3(128); cfg.stream = (cudaStream_t)stream;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = g_launch_overlap;
   cfg.attrs = at; cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, exchange_merge_kernel, x->recv, x->flags, x->epoch, x->ticket, x->err, x->rank, x->world, (int)(n_heads / groups),
+  if (cudaLaunchKernelEx(&cfg, exchange_merge_kernel, x->recv, x->epoch, x->ticket, x->err, x->rank, x->world,
                          (long)x->rows_cap, (uint16_t*)out_bf16, out_f32) != cudaSuccess) { cudaGetLastError(); return GAAC_E_LAUNCH; }
   return launch_status();
 }

@@ -265,4 +265,4 @@ extern "C" const char* gaac_status_string(int status) {
   }
 }
 
-extern "C" int gaac_abi_version(void) { return 3; }
+extern "C" int gaac_abi_version(void) { return 4; }

@@ -58,12 +58,13 @@ def merge_partials(part: torch.Tensor, group=None, combine_fn=None, out_f32: tor
 
 
 class PeerExchange:
-    """Receive buffers and arrival flags of all ranks, mapped into every rank (peer memory over NVLink), for the fused
-    partial exchange: the attention kernel stores its partial rows into every rank's buffer, sets its flag there, and either
+    """Receive buffers of all ranks, mapped into every rank (peer memory over NVLink), for the fused partial exchange: the
+    attention kernel stores its partial rows into every rank's buffer as 8-byte entries (value + exchange number), and either
     the same launch (fused) or gaac_exchange_merge waits for all ranks' rows and merges them.  Built on torch's symmetric
     memory (one rendezvous at construction) with NVLink multicast binding switched off (plain peer loads and stores only);
     raises when the mapping is unavailable, and the caller falls back to the NCCL all-gather.
-    n_heads = B * n_q rows per exchange at most, groups = B * n_kv flag groups at most."""
+    n_heads = B * n_q rows per exchange at most.  (`groups` is accepted for callers written against the flag-based exchange
+    and ignored.)"""
 
     def __init__(self, n_heads: int, device, group=None, groups: int | None = None):
         import os
@@ -71,29 +72,26 @@ class PeerExchange:
         import torch.distributed._symmetric_memory as symm
         group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        self.n_heads, self.groups = n_heads, groups if groups is not None else n_heads
-        self._flag_off, nbytes = self._layout(self.world, self.n_heads, self.groups)
-        self._buf = symm.empty(nbytes, dtype=torch.uint8, device=device)
+        self.n_heads = n_heads
+        self._buf = symm.empty(self._layout(self.world, self.n_heads), dtype=torch.uint8, device=device)
         self._buf.zero_()
         self._hdl = symm.rendezvous(self._buf, group)
         ptrs = [int(p) for p in self._hdl.buffer_ptrs]
         self._setup(ptrs, device)
         torch.cuda.synchronize(device)
-        dist.barrier(group)                                     # every rank's flags are zero before anyone pushes
+        dist.barrier(group)                                     # every rank's buffer is zero before anyone pushes
 
     @staticmethod
-    def _layout(world: int, n_heads: int, groups: int) -> tuple[int, int]:
-        """(byte offset of the flags, total bytes): 2 x world x n_heads rows of 130 floats, then groups x world int32 flags."""
-        flag_off = (2 * world * n_heads * 130 * 4 + 255) // 256 * 256
-        return flag_off, flag_off + (groups * world * 4 + 255) // 256 * 256
+    def _layout(world: int, n_heads: int) -> int:
+        """Bytes of a receive buffer: 2 x world x n_heads rows of 130 eight-byte entries."""
+        return (2 * world * n_heads * 130 * 8 + 255) // 256 * 256
 
     def _setup(self, ptrs, device):
         from . import _lib
         self._recv = torch.tensor(ptrs, dtype=torch.int64, device=device)
-        self._flags = torch.tensor([p + self._flag_off for p in ptrs], dtype=torch.int64, device=device)
         self._state = torch.zeros(3, dtype=torch.int32, device=device)                     # exchange number, ticket, err
-        self.x = _lib.Exchange(self._recv.data_ptr(), self._flags.data_ptr(), self._state.data_ptr(), self._state.data_ptr() + 4,
-                               self._state.data_ptr() + 8, self.rank, self.world, self.n_heads, self.groups)
+        self.x = _lib.Exchange(self._recv.data_ptr(), self._state.data_ptr(), self._state.data_ptr() + 4,
+                               self._state.data_ptr() + 8, self.rank, self.world, self.n_heads)
 
     @classmethod
     def local(cls, bufs, rank: int, n_heads: int, groups: int | None = None):
@@ -101,22 +99,21 @@ class PeerExchange:
         one after the other in stream order.  Only the last rank to push may use the fused launch (everything it waits for is
         there already); the others push and merge with separate launches."""
         self = cls.__new__(cls)
-        self.world, self.rank, self.n_heads, self.groups = len(bufs), rank, n_heads, groups if groups is not None else n_heads
-        self._flag_off, _ = cls._layout(self.world, self.n_heads, self.groups)
+        self.world, self.rank, self.n_heads = len(bufs), rank, n_heads
         self._buf = bufs[rank]
         self._setup([b.data_ptr() for b in bufs], bufs[rank].device)
         return self
 
     @classmethod
     def local_buffer(cls, world: int, n_heads: int, device, groups: int | None = None) -> torch.Tensor:
-        return torch.zeros(cls._layout(world, n_heads, groups if groups is not None else n_heads)[1], dtype=torch.uint8, device=device)
+        return torch.zeros(cls._layout(world, n_heads), dtype=torch.uint8, device=device)
 
-    def merge(self, groups: int, out_f32: torch.Tensor | None = None, n_heads: int | None = None) -> torch.Tensor:
+    def merge(self, groups: int | None = None, out_f32: torch.Tensor | None = None, n_heads: int | None = None) -> torch.Tensor:
         """Launch the wait-and-merge kernel on the current stream (after a push-only launch); returns [n_heads, 128] bf16."""
         from . import _lib
         n_heads = self.n_heads if n_heads is None else n_heads
         out = torch.empty(n_heads, 128, dtype=torch.bfloat16, device=self._state.device)
-        _lib.check(_lib.lib().gaac_exchange_merge(self.x, n_heads, groups, out.data_ptr(), _lib.ptr(out_f32),
+        _lib.check(_lib.lib().gaac_exchange_merge(self.x, n_heads, out.data_ptr(), _lib.ptr(out_f32),
                                                   _lib.stream_ptr(self._state.device)), "gaac_exchange_merge")
         return out
 

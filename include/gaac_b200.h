@@ -174,41 +174,39 @@ int gaac_decode_attn_partial(const gaac_side* K, const gaac_side* V, const void*
                              int n_base_rows, void* workspace, size_t workspace_bytes, float* part, void* stream);
 
 /* Cross-GPU context split without a collective library on the data path: one process per GPU, every rank's receive buffer
- * and arrival flags mapped into every rank's address space (peer memory over NVLink).  No counterpart in the reference,
- * which is single-GPU.
- *   recv[r]  : rank r's receive buffer, 2 * world * rows_cap * 130 floats (two exchanges deep, indexed by the parity of the
- *              exchange number, then by sending rank, then by query-head row b*n_q + head)
- *   flags[r] : rank r's arrival flags, int[groups_cap * world], zero before the first exchange: flag (g, s) holds the number
- *              of the last exchange for which rank s delivered the rows of (row, kv head) group g.  Flags carry numbers, they
- *              do not count, so B and n_kv may change from one exchange to the next (within rows_cap / groups_cap), and an
- *              exchange that timed out leaves the following ones intact
+ * mapped into every rank's address space (peer memory over NVLink).  No counterpart in the reference, which is single-GPU.
+ *   recv[r]  : rank r's receive buffer, 2 * world * rows_cap * 130 entries of 8 bytes, zero before the first exchange (two
+ *              exchanges deep, indexed by the parity of the exchange number, then by sending rank, then by query-head row
+ *              b*n_q + head).  An entry = fp32 value in the low word, number of the exchange it belongs to in the high word,
+ *              written with one 64-bit store and read with one 64-bit load: a reader that finds the expected number has the
+ *              value that came with it, so no flag, fence or second trip over NVLink announces a row.  Numbers are compared for
+ *              equality, so B and n_kv may change from one exchange to the next (within rows_cap), and an exchange that
+ *              timed out leaves the following ones intact
  *   epoch, ticket, err : this rank's own device ints, zero before the first exchange; epoch = number of finished exchanges
  *              and must advance in step on all ranks (every rank makes the same sequence of calls); err becomes 1 when a
  *              wait ran out
- * recv and flags are DEVICE arrays of `world` pointers.  Buffers are two exchanges deep, which is enough as long as
- * consecutive exchanges use the same B, n_q and n_kv; ranks that change the shape synchronise with one another first. */
+ * recv is a DEVICE array of `world` pointers.  Buffers are two exchanges deep, which is enough as long as consecutive
+ * exchanges use the same B, n_q and n_kv; ranks that change the shape synchronise with one another first. */
 typedef struct {
-  float* const* recv;
-  int32_t* const* flags;
+  unsigned long long* const* recv;
   int32_t* epoch;
   int32_t* ticket;
   int32_t* err;
   int rank, world;
-  int rows_cap, groups_cap;
+  int rows_cap;
 } gaac_exchange;
 
 /* gaac_decode_attn_partial whose last CTA of every (row, kv head) stores its partial rows straight into every rank's
- * receive buffer (plain stores over NVLink, one system-scope fence, then this rank's flag of the group is set on every
- * rank): the exchange rides on the attention kernel's epilogue, there is no separate send.  Finish with
- * gaac_exchange_merge on the same stream. */
+ * receive buffer (64-bit stores over NVLink, each carrying the exchange number): the exchange rides on the attention
+ * kernel's epilogue, there is no separate send.  Finish with gaac_exchange_merge on the same stream. */
 int gaac_decode_attn_push(const gaac_side* K, const gaac_side* V, const void* q_bf16, const int32_t* slot, int B, int n_q, int n_kv,
                           const int32_t* seq_len, int64_t S_pad, float scale, int nsplit, const int32_t* tail_len, int tail_cap,
                           int n_base_rows, void* workspace, size_t workspace_bytes, const gaac_exchange* x, void* stream);
 
 /* Wait (bounded: about one second, then *err = 1 and a zero output) until the partials of all ranks for the current
- * exchange have arrived, merge them as gaac_combine does and advance the exchange number.  n_heads = B * n_q,
- * groups = B * n_kv of the matching gaac_decode_attn_push.  Launch it on the stream of the push, after it. */
-int gaac_exchange_merge(const gaac_exchange* x, int64_t n_heads, int groups, void* out_bf16, float* out_f32, void* stream);
+ * exchange have arrived, merge them as gaac_combine does and advance the exchange number.  n_heads = B * n_q of the matching
+ * gaac_decode_attn_push.  Launch it on the stream of the push, after it. */
+int gaac_exchange_merge(const gaac_exchange* x, int64_t n_heads, void* out_bf16, float* out_f32, void* stream);
 
 /* Push, wait and merge in ONE launch: the CTA that pushed the rows of a (row, kv head) group goes on to wait (same bound)
  * for the other ranks' rows of that group, merges them and writes out [B, n_q, 128] (out_f32 optional); the exchange number

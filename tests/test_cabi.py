@@ -25,7 +25,7 @@ def test_status_strings(lib):
     assert lib.gaac_status_string(0) == b"ok"
     for s in range(1, 6):
         assert len(lib.gaac_status_string(s)) > 4
-    assert lib.gaac_abi_version() == 3
+    assert lib.gaac_abi_version() == 4
 
 
 def test_bad_arguments_are_rejected_before_any_launch(lib):
@@ -54,14 +54,15 @@ def test_bad_arguments_are_rejected_before_any_launch(lib):
     assert lib.gaac_attn_workspace_header_bytes(4096, 8) > 65536
     assert lib.gaac_attn_workspace_bytes(2, 8, 3) == 65536 + 2 * 256 + 48 * 128 * 4
     # the Pages entry wants exactly one destination; the fused exchange wants an output
-    x = _lib.Exchange(0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0, 2, 64, 8)
+    x = _lib.Exchange(0x1000, 0x1000, 0x1000, 0x1000, 0, 2, 64)
     assert lib.gaac_decode_attn_pages(side, side, fake, 1, 8, 2, 16, 16, 0.1, 1, 2, fake, 1 << 20, None, None, None, None, 0, None) == 1
     assert lib.gaac_decode_attn_pages(side, side, fake, 1, 8, 2, 16, 16, 0.1, 1, 2, fake, 1 << 20, fake, None, fake, None, 0, None) == 1
     assert lib.gaac_decode_attn_pages(side, side, fake, 1, 8, 2, 16, 16, 0.1, 1, 2, fake, 1 << 20, None, None, None, x, 1, None) == 1
     assert lib.gaac_decode_attn_pages(side, side, fake, 1, 8, 2, 32, 16, 0.1, 1, 2, fake, 1 << 20, fake, None, None, None, 0, None) == 1     # S > S_pad
-    small = _lib.Exchange(0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0, 2, 4, 8)                                      # rows_cap 4 < B*n_q
+    small = _lib.Exchange(0x1000, 0x1000, 0x1000, 0x1000, 0, 2, 4)                                                  # rows_cap 4 < B*n_q
     assert lib.gaac_decode_attn_pages(side, side, fake, 1, 8, 2, 16, 16, 0.1, 1, 2, fake, 1 << 20, None, None, None, small, 0, None) == 1
-    assert lib.gaac_exchange_merge(x, 8, 3, fake, None, None) == 1                                                   # heads not a multiple of groups
+    assert lib.gaac_exchange_merge(x, 65, fake, None, None) == 1                                                     # more heads than rows_cap
+    assert lib.gaac_exchange_merge(x, 8, None, None, None) == 1                                                      # no output
     assert lib.gaac_debug_decode_attn_rebuild(side, side, fake, None, 1, 8, 2, None, 16, 16, 0.1, 1, None, 0, 2, fake, 1 << 20, fake, None, None, fake, 32, None) == 1
     pg = _lib.Paged(0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 0x1000, 2, 3000, 120)
     assert lib.gaac_paged_decode_attn(pg, fake, 4, fake, fake, 1, 8, 0.1, 1, fake, 1 << 20, fake, None, None) == 2     # TS % 16
