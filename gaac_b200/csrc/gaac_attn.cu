@@ -134,6 +134,8 @@ struct AttnParams {
   // cross-GPU exchange (x_recv == NULL: unused): the partial of every query head is stored into every rank's receive
   // buffer, then this rank's arrival flag of the (row, kv head) group on every rank is set to the exchange number; with
   // x_fused the same CTA then waits (bounded) for the other ranks' flags, merges all ranks' rows and writes the output
+  const int2* row_order;                            // paged layout, optional: {batch row, its token count}, longest row first
+  int2* order_buf;                                  // room for B entries of it in the workspace
   unsigned long long* const* x_recv; int* x_epoch; int* x_ticket; int* x_err; int x_rank, x_world, x_rows_cap, x_fused;
   // debug instantiation only: the rebuilt BF16 K / V rows are written to [B*n_kv, dump_S, 128] (row = token of the head)
   uint16_t* dump_k; uint16_t* dump_v; long dump_S;
@@ -639,10 +641,9 @@ template <bool PAGED, bool DUMP>
 __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ __align__(16) uint8_t smem[];
   __shared__ int s_next, s_last;
-  const int bh = blockIdx.x, split = blockIdx.y, tid = threadIdx.x, lane = tid & 31, j = lane & 3, r = lane >> 2;
+  const int tid = threadIdx.x, lane = tid & 31, j = lane & 3, r = lane >> 2;
   const int warp = __shfl_sync(FULLM, tid >> 5, 0);   // the same value, but known to the compiler to be uniform across the warp
-  const int b = bh / p.n_kv, kvh = bh % p.n_kv, G = p.G;
-
+  const int G = p.G;
   // ---- programmatic dependent launch: the grid is launched with stream serialisation relaxed, so its CTAs can be made
   // resident while the previous kernel of the stream is still finishing (its split merge runs on a few SMs only).  Nothing
   // is read before that kernel has completed; the next kernel of the stream may be staged behind this one right away (it
@@ -650,11 +651,23 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::);
 
+  // Which (row, kv head, split) this CTA works on.  Normally the grid says so.  With a row order (ragged paged batches) the CTAs
+  // are numbered in the order the hardware hands them out (x fastest) and that number walks the rows from the longest to the
+  // shortest, all CTAs of a row together: the big CTAs start first and the small ones fill the SMs at the end.
+  int bh = blockIdx.x, split = blockIdx.y, S_ordered = 0;
+  if (PAGED && p.row_order) {
+    const int linear = blockIdx.y * gridDim.x + blockIdx.x, per_row = p.n_kv * p.nsplit;
+    const int rr = linear / per_row, rem = linear - rr * per_row;
+    const int2 e = p.row_order[rr];
+    bh = e.x * p.n_kv + rem / p.nsplit; split = rem % p.nsplit; S_ordered = e.y;
+  }
+  const int b = bh / p.n_kv, kvh = bh % p.n_kv;
+
   // ---- which cache head, how many tokens, this CTA's tile range [tlo, thi)
   // (without a slot map row b reads slot b; without a length table every head holds S_uniform tokens: the two dependent
   // loads at the head of the prologue disappear for callers whose heads are all alike, which is what two Pages are)
   int S, ch = 0, TL = 0, ohk = 0, ohv = 0;
-  if (PAGED) { S = p.seq_len[b]; }
+  if (PAGED) { S = p.row_order ? S_ordered : p.seq_len[b]; }
   else {
     const int sl = p.slot ? p.slot[b] : b;
     ch = (sl < 0 ? 0 : sl) * p.n_kv + kvh;
@@ -1309,6 +1322,21 @@ __global__ void __launch_bounds__(128) combine_parts_kernel(const float* __restr
   if (out_f32) out_f32[qh * D + d] = v;
 }
 
+// Rows of a ragged batch from the longest to the shortest (ties by index): entry k = {row, its token count}.  One CTA; every
+// thread finds the place of its own row by counting the rows that come before it.
+constexpr int ORDER_MAX_ROWS = 1024;
+__global__ void __launch_bounds__(ORDER_MAX_ROWS) row_order_kernel(const int* __restrict__ seq_lens, int B, int2* __restrict__ order) {
+  __shared__ int len_s[ORDER_MAX_ROWS];
+  const int t = threadIdx.x;
+  if (t < B) len_s[t] = seq_lens[t];
+  __syncthreads();
+  if (t >= B) return;
+  const int mine = len_s[t];
+  int before = 0;
+  for (int i = 0; i < B; i++) before += (len_s[i] > mine) || (len_s[i] == mine && i < t);
+  order[before] = make_int2(t, mine);
+}
+
 static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 // Workspace = header | pm | pl | pa.  Header: the error word at byte 0, the split counters from byte 256.  The header has a
 // fixed size for every B*n_q up to 16320, so the partials of a call never lie where the counters of a call of another shape
@@ -1317,7 +1345,7 @@ constexpr size_t WS_COUNTERS_OFF = 256, WS_MIN_HEADER = 64 << 10;
 static size_t ws_header_bytes(int B, int n_q) { return std::max(WS_MIN_HEADER, WS_COUNTERS_OFF + align256(4 * (size_t)B * n_q)); }
 static size_t ws_bytes_needed(int B, int n_q, int nsplit) {
   const size_t n = (size_t)B * n_q * nsplit;
-  return ws_header_bytes(B, n_q) + align256(4 * n) * 2 + align256(4 * n * D);
+  return ws_header_bytes(B, n_q) + align256(4 * n) * 2 + align256(4 * n * D) + align256(sizeof(int2) * (size_t)B);     // header | pm | pl | pa | row order
 }
 static int carve_workspace(void* ws, size_t ws_bytes, int B, int n_q, int nsplit, AttnParams& p) {
   const size_t n = (size_t)B * n_q * nsplit;
@@ -1327,7 +1355,8 @@ static int carve_workspace(void* ws, size_t ws_bytes, int B, int n_q, int nsplit
   p.err = (int*)w; p.counters = (int*)(w + WS_COUNTERS_OFF); w += ws_header_bytes(B, n_q);
   p.pm = (float*)w; w += align256(4 * n);
   p.pl = (float*)w; w += align256(4 * n);
-  p.pa = (float*)w;
+  p.pa = (float*)w; w += align256(4 * n * D);
+  p.order_buf = (int2*)w;
   return GAAC_OK;
 }
 
@@ -1419,6 +1448,12 @@ static int paged_attn(const gaac_paged* st, const int32_t* bt, int64_t bt_stride
   if (dump_k) {
     p.dump_k = (uint16_t*)dump_k; p.dump_v = (uint16_t*)dump_v; p.dump_S = dump_S;
     return launch_attn<true, true>(p, (cudaStream_t)stream);
+  }
+  // ragged batches: CTAs are handed out longest row first (one small launch sorts the rows; its output is read by the attention
+  // kernel after its dependency wait)
+  if (B > 1 && B <= ORDER_MAX_ROWS && (int64_t)B * st->n_kv * nsplit > sm_count_of_current_device()) {
+    row_order_kernel<<<1, ORDER_MAX_ROWS, 0, (cudaStream_t)stream>>>(seq_lens, B, p.order_buf);
+    p.row_order = p.order_buf;
   }
   return launch_attn<true, false>(p, (cudaStream_t)stream);
 }

@@ -52,7 +52,7 @@ def test_bad_arguments_are_rejected_before_any_launch(lib):
     # workspace layout: a 64 KiB header whatever the shape, so calls of different shapes can share one workspace
     assert lib.gaac_attn_workspace_header_bytes(1, 32) == lib.gaac_attn_workspace_header_bytes(64, 64) == 65536
     assert lib.gaac_attn_workspace_header_bytes(4096, 8) > 65536
-    assert lib.gaac_attn_workspace_bytes(2, 8, 3) == 65536 + 2 * 256 + 48 * 128 * 4
+    assert lib.gaac_attn_workspace_bytes(2, 8, 3) == 65536 + 2 * 256 + 48 * 128 * 4 + 256           # header, pm, pl, pa, row order
     # the Pages entry wants exactly one destination; the fused exchange wants an output
     x = _lib.Exchange(0x1000, 0x1000, 0x1000, 0x1000, 0, 2, 64)
     assert lib.gaac_decode_attn_pages(side, side, fake, 1, 8, 2, 16, 16, 0.1, 1, 2, fake, 1 << 20, None, None, None, None, 0, None) == 1

@@ -116,6 +116,29 @@ def test_paged_attention_matches_oracle(n_kv, G, adv):
             assert np.abs(out[b].view(n_q, 128).float().cpu().numpy() - ref).max() <= 2e-2 * mag + 1e-3
 
 
+def test_paged_attention_rows_handed_out_longest_first():
+    """Grids larger than the GPU (here 7 rows x 4 kv heads x 8 splits = 224 CTAs) number their CTAs by row length, longest row
+    first (a small sort launch in front of the attention kernel): ragged lengths with ties, a one-token row and the longest row
+    last in batch order must give the same results as ever; a second call with other lengths reuses the workspace."""
+    import torch
+    from gaac_b200.vllm.paged_kernel import paged_attention
+    n_kv, G = 4, 2
+    seq_lens = [300, 16, 1, 300, 47, 640, 1500]
+    st, buf, bt, ks, vs = _build_paged(seq_lens, n_kv, 512, seed=77, adversarial_every=4)
+    assert int(st.err) == 0
+    B, n_q = len(seq_lens), n_kv * G
+    rng = np.random.default_rng(2)
+    for lens in (seq_lens, [250, 16, 1, 300, 30, 100, 777]):              # the second set: prefixes of the stored sequences
+        q16 = O.f32_to_bf16((rng.standard_normal((B, n_q, 128)) * 0.3).astype(np.float32))
+        sl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+        out = torch.empty(B, n_q * 128, dtype=torch.bfloat16, device="cuda")
+        o32 = torch.empty(B, n_q, 128, dtype=torch.float32, device="cuda")
+        paged_attention(to_bf16_cuda(q16), out, buf, st.raw, st.mt, bt, sl, st.bases, st.TS, n_q, n_kv, 8, out_f32=o32)
+        for b in range(B):
+            assert_attention_close(o32[b].cpu().numpy(), q16[b], ks[b][:lens[b]], vs[b][:lens[b]], 128 ** -0.5, (b, lens[b]))
+        assert torch.equal(out.view(B, n_q, 128), o32.to(torch.bfloat16))
+
+
 def test_paged_incremental_decode_steps():
     """Append one token per sequence per step through the store (finalising blocks that fill) and attend after each step."""
     import torch
