@@ -97,6 +97,18 @@ def check(status: int, what: str):
         raise RuntimeError(f"{what}: {lib().gaac_status_string(status).decode()} (status {status})")
 
 
+def row_stride(t) -> int:
+    """Stride of dim 0 in elements as the library wants it.  torch is free to report anything for a dimension of size 1 (a
+    one-row tensor often comes back with the stride of its second dimension), and the library checks the stride against the row
+    width: a tensor with at most one row gets the width of a packed row instead."""
+    if t.shape[0] > 1:
+        return t.stride(0)
+    n = 1
+    for s in t.shape[1:]:
+        n *= s
+    return max(n, 1)
+
+
 def ptr(t):
     """Device pointer of a tensor (None -> NULL)."""
     return None if t is None else t.data_ptr()

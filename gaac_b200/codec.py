@@ -161,7 +161,7 @@ class Codec:
         if nb != page.n_kv:                          # one base row per head (per-sequence calibration)
             bidx = (torch.arange(H, device=sm.device, dtype=torch.int32) % nb).contiguous()
         _lib.check(_lib.lib().gaac_decode_page(
-            page.sm.data_ptr(), page.codes.data_ptr(), page.flags.data_ptr(), page.tile_off.data_ptr(), page.tile_off.stride(0),
+            page.sm.data_ptr(), page.codes.data_ptr(), page.flags.data_ptr(), page.tile_off.data_ptr(), _lib.row_stride(page.tile_off),
             page.ovf.data_ptr(), page.ovf_head_start.data_ptr(), page.base3.data_ptr(), page.base4.data_ptr(), _lib.ptr(bidx),
             page.n_kv, 0 if page.kind == "k" else 1, H, S, S_pad, out.data_ptr(), _lib.stream_ptr(sm.device)), "gaac_decode_page")
         return out

@@ -51,16 +51,24 @@ def choose_nsplit_sm100(B: int, n_kv: int, S: int, sm_count: int = SM_COUNT_B200
     over the counts that leave every warp at least min_tiles_per_warp 16-token tiles.  Tile time: 4.5 us for a tile whose
     metadata is staged, 5.2 us beyond; fixed cost (prologue, warp merge, split merge): 10 us.  Few rows end up with one wave that
     fills the SMs, many rows with ranges of at most 512 tiles in several waves.
-    Ragged lengths (ragged=True, S is the longest row, total_tokens the sum over the batch rows when known, else rows are taken
-    to average 55 % of the longest): every row gets the same split count, so the longest row's chunks must be small against an
-    SM's share of the whole batch for the block scheduler to even the SMs out: a third of that share, and at most 512 tiles."""
+    Ragged lengths (ragged=True, S is the longest row; total_tokens is accepted and unused): every row gets the same split count;
+    see the comment in the code."""
     rows = max(1, B * n_kv)
     ntiles = max(1, (S + 15) // 16)
     most = max(1, ntiles // (ATT_WARPS * min_tiles_per_warp))
-    if ragged:
-        mean_tiles = (total_tokens / max(1, B) / 16.0) if total_tokens else 0.55 * ntiles
-        per_sm = max(1.0, rows * mean_tiles / sm_count)
-        return max(1, min(most, max(-(-ntiles // 512), int(-(-3 * ntiles // per_sm)))))
+    if ragged and B > 1:
+        # CTAs are handed out longest row first, so the end of the launch is filled by the small ones and what remains is a
+        # trade between the per-CTA fixed cost (grows with the split count) and the last chunks of the longest row (shrink with
+        # it): the measured optimum follows sqrt(1.8 x longest row's tiles / rows).  Near it, a count whose CTAs fill whole waves
+        # is preferred while the launch is only a few waves long.
+        star = (1.8 * ntiles / rows) ** 0.5
+        lo, hi = max(1, -(-ntiles // 512)), max(most, 1)
+        first = min(max(lo, int(0.6 * star)), hi)
+        last = max(first, min(hi, int(1.5 * star) + 1))
+        def waste(ns):
+            w = rows * ns / sm_count
+            return 0.0 if w >= 4 else 1.0 - w / -(-w // 1)
+        return min(range(first, last + 1), key=lambda ns: (waste(ns) > 0.1, abs(ns - star)))
     tile_us, tile_far_us, fixed_us, staged = 4.5, 5.2, 10.0, 512
     best, best_t = 1, None
     for ns in range(1, min(most, 2 * sm_count) + 1):

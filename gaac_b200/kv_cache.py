@@ -156,7 +156,7 @@ class CompressedKVCache:
 
     def _prefill_launch(self, slot, L, k, v, scratch, status, copy_only: int):
         dev = self.S.device
-        _lib.check(_lib.lib().gaac_cache_prefill(self.k.c_store(), self.v.c_store(), _lib.ptr(k), _lib.ptr(v), L, k.stride(0) if k is not None else self.n_kv * D,
+        _lib.check(_lib.lib().gaac_cache_prefill(self.k.c_store(), self.v.c_store(), _lib.ptr(k), _lib.ptr(v), L, _lib.row_stride(k) if k is not None else self.n_kv * D,
                                                  slot, self.n_kv, self.tail_len.data_ptr(), self.S.data_ptr(), self.cap, self.k.ovf_cap, self.k.base3.shape[0],
                                                  scratch.data_ptr(), scratch.numel(), status.data_ptr(), copy_only, _lib.stream_ptr(dev)), "gaac_cache_prefill")
 

@@ -31,6 +31,6 @@ def paged_attention(q, out, buf, raw, mt, bt, seq_lens, bases, TS, n_q, n_kv, ns
     st = _lib.Paged(buf.data_ptr(), raw.data_ptr(), mt.data_ptr(), None, None, None,
                     bases[0].data_ptr(), bases[1].data_ptr(), bases[2].data_ptr(), bases[3].data_ptr(), n_kv, TS, TS - 2880)
     ws = workspace(q.device, B, n_q, nsplit)
-    _lib.check(_lib.lib().gaac_paged_decode_attn(st, bt.data_ptr(), bt.stride(0), seq_lens.data_ptr(), q.data_ptr(), B, n_q, 1.0 / (D ** 0.5), int(nsplit),
+    _lib.check(_lib.lib().gaac_paged_decode_attn(st, bt.data_ptr(), _lib.row_stride(bt), seq_lens.data_ptr(), q.data_ptr(), B, n_q, 1.0 / (D ** 0.5), int(nsplit),
                                                  ws.data_ptr(), ws.numel(), out.data_ptr(), _lib.ptr(out_f32), _lib.stream_ptr(q.device)), "gaac_paged_decode_attn")
     return out

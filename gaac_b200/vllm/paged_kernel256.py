@@ -26,7 +26,7 @@ def paged_attention256(q, out, buf, raw, mt, bt, seq_lens, bases, TS, n_q, n_kv,
     st = _lib.Paged(buf.data_ptr(), raw.data_ptr(), mt.data_ptr(), None, None, None,
                     bases[0].data_ptr(), bases[1].data_ptr(), bases[2].data_ptr(), bases[3].data_ptr(), 2 * n_kv, TS, TS - 2880)
     ws = workspace(q.device, B, 2 * n_q, nsplit)
-    _lib.check(_lib.lib().gaac_paged_decode_attn256(st, bt.data_ptr(), bt.stride(0), seq_lens.data_ptr(), q.data_ptr(), B, n_q,
+    _lib.check(_lib.lib().gaac_paged_decode_attn256(st, bt.data_ptr(), _lib.row_stride(bt), seq_lens.data_ptr(), q.data_ptr(), B, n_q,
                                                     float(scale) if scale is not None else 256 ** -0.5, int(nsplit), ws.data_ptr(), ws.numel(),
                                                     out.data_ptr(), _lib.ptr(out_f32), _lib.stream_ptr(q.device)), "gaac_paged_decode_attn256")
     return out

@@ -54,7 +54,7 @@ class LayerState:
         if E == 0: return
         assert key.stride(-1) == 1 and value.stride(-1) == 1
         assert (key.shape[1] == 1 or key.stride(1) == D) and (value.shape[1] == 1 or value.stride(1) == D)
-        _lib.check(_lib.lib().gaac_paged_store(self.c_state(buf), key.data_ptr(), value.data_ptr(), key.stride(0), value.stride(0),
+        _lib.check(_lib.lib().gaac_paged_store(self.c_state(buf), key.data_ptr(), value.data_ptr(), _lib.row_stride(key), _lib.row_stride(value),
                                                ent.data_ptr(), E, freeq.data_ptr(), _lib.stream_ptr(buf.device)), "gaac_paged_store")
 
     def decode_blocks(self, buf: torch.Tensor, pairs: torch.Tensor, sk: torch.Tensor, sv: torch.Tensor):
@@ -62,8 +62,8 @@ class LayerState:
         (gaac/vllm/store.py:215-221)"""
         P = pairs.shape[0]
         if P == 0: return
-        assert sk.stride(0) == self.n_kv * D and sv.stride(0) == self.n_kv * D
-        _lib.check(_lib.lib().gaac_paged_decode_blocks(self.c_state(buf), pairs.data_ptr(), P, sk.data_ptr(), sv.data_ptr(), sk.stride(0),
+        assert _lib.row_stride(sk) == self.n_kv * D and _lib.row_stride(sv) == self.n_kv * D
+        _lib.check(_lib.lib().gaac_paged_decode_blocks(self.c_state(buf), pairs.data_ptr(), P, sk.data_ptr(), sv.data_ptr(), _lib.row_stride(sk),
                                                        _lib.stream_ptr(buf.device)), "gaac_paged_decode_blocks")
 
     def release_blocks(self, blocks: torch.Tensor):

@@ -189,7 +189,7 @@ def test_prefill_reads_token_major_rows_in_place(static_bases):
     from gaac_b200 import CompressedKVCache
     import torch
     cap = 256
-    cache = CompressedKVCache(n_slots=6, n_kv=N_KV, capacity=cap, bases=_bases(11) if static_bases else None)
+    cache = CompressedKVCache(n_slots=7, n_kv=N_KV, capacity=cap, bases=_bases(11) if static_bases else None)
     lens = [5, 16, 33, cap]
     total = sum(lens)
     k_all, v_all = _tok(O.kv_like(N_KV, total, 71)), _tok(O.kv_like(N_KV, total, 72))
@@ -206,12 +206,15 @@ def test_prefill_reads_token_major_rows_in_place(static_bases):
     # a head-major tensor viewed token-major (strides the library does not read directly)
     k6, v6 = O.kv_like(N_KV, 21, 75), O.kv_like(N_KV, 21, 76)
     cache.prefill(5, to_bf16_cuda(k6).transpose(0, 1), to_bf16_cuda(v6).transpose(0, 1)); hist[5] = (_tok(k6), _tok(v6))
+    # a one-token prompt: torch reports an arbitrary stride for its only row
+    k7, v7 = _tok(O.kv_like(N_KV, 1, 78)), _tok(O.kv_like(N_KV, 1, 79))
+    cache.prefill(6, to_bf16_cuda(k7), to_bf16_cuda(v7)); hist[6] = (k7, v7)
     for s, (k, v) in hist.items():
         dk, dv = cache.decompress(s)
         assert np.array_equal(bits(dk), k) and np.array_equal(bits(dv), v), s
     rng = np.random.default_rng(3)
-    q16 = O.f32_to_bf16((rng.standard_normal((6, N_KV * G, 128)) * 0.1).astype(np.float32))
-    _check(cache, hist, [0, 1, 2, 3, 4, 5], q16)
+    q16 = O.f32_to_bf16((rng.standard_normal((7, N_KV * G, 128)) * 0.1).astype(np.float32))
+    _check(cache, hist, [0, 1, 2, 3, 4, 5, 6], q16)
     # an empty prompt empties the slot
     cache.prefill(2, kd[:0], vd[:0])
     assert int(cache.S[2 * N_KV]) == 0 and int(cache.tail_len[2 * N_KV]) == 0 and int(cache.k.ovf_used[2 * N_KV]) == 0
