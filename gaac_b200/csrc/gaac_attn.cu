@@ -654,12 +654,19 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
   // Which (row, kv head, split) this CTA works on.  Normally the grid says so.  With a row order (ragged paged batches) the CTAs
   // are numbered in the order the hardware hands them out (x fastest) and that number walks the rows from the longest to the
   // shortest, all CTAs of a row together: the big CTAs start first and the small ones fill the SMs at the end.
-  int bh = blockIdx.x, split = blockIdx.y, S_ordered = 0;
-  if (PAGED && p.row_order) {
-    const int linear = blockIdx.y * gridDim.x + blockIdx.x, per_row = p.n_kv * p.nsplit;
-    const int rr = linear / per_row, rem = linear - rr * per_row;
-    const int2 e = p.row_order[rr];
-    bh = e.x * p.n_kv + rem / p.nsplit; split = rem % p.nsplit; S_ordered = e.y;
+  int bh = blockIdx.x, split = blockIdx.y, S_paged = 0;
+  if (PAGED) {
+    // the row's token count for the grid's own numbering; the loads of the row order travel at the same time, so a batch whose
+    // order is not used pays no extra latency for having one
+    S_paged = p.seq_len[bh / p.n_kv];
+    if (p.row_order) {
+      const int linear = blockIdx.y * gridDim.x + blockIdx.x, per_row = p.n_kv * p.nsplit;
+      const int rr = linear / per_row, rem = linear - rr * per_row;
+      const int2 e = p.row_order[rr], use = p.row_order[p.B];
+      if (use.x) { bh = e.x * p.n_kv + rem / p.nsplit; split = rem % p.nsplit; S_paged = e.y; }
+      // the numbers came out of memory: tell the compiler that they are the same in every lane (see below)
+      bh = __shfl_sync(FULLM, bh, 0); split = __shfl_sync(FULLM, split, 0);
+    }
   }
   const int b = bh / p.n_kv, kvh = bh % p.n_kv;
 
@@ -667,7 +674,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) decode_attn_kernel(const __gri
   // (without a slot map row b reads slot b; without a length table every head holds S_uniform tokens: the two dependent
   // loads at the head of the prologue disappear for callers whose heads are all alike, which is what two Pages are)
   int S, ch = 0, TL = 0, ohk = 0, ohv = 0;
-  if (PAGED) { S = p.row_order ? S_ordered : p.seq_len[b]; }
+  if (PAGED) { S = S_paged; }
   else {
     const int sl = p.slot ? p.slot[b] : b;
     ch = (sl < 0 ? 0 : sl) * p.n_kv + kvh;
@@ -1322,19 +1329,32 @@ __global__ void __launch_bounds__(128) combine_parts_kernel(const float* __restr
   if (out_f32) out_f32[qh * D + d] = v;
 }
 
-// Rows of a ragged batch from the longest to the shortest (ties by index): entry k = {row, its token count}.  One CTA; every
-// thread finds the place of its own row by counting the rows that come before it.
+// Rows of a batch from the longest to the shortest (ties by index): entry k = {row, its token count}, k < B.  Entry B says whether
+// the order is worth using: {1, -} when the shortest non-empty row has less than 7/8 of the longest row's tokens, else {0, -}
+// (rows of about equal length keep the grid's own numbering, which costs nothing).  One CTA; every thread finds the place of its
+// own row by counting the rows that come before it.
 constexpr int ORDER_MAX_ROWS = 1024;
-__global__ void __launch_bounds__(ORDER_MAX_ROWS) row_order_kernel(const int* __restrict__ seq_lens, int B, int2* __restrict__ order) {
+__global__ void __launch_bounds__(ORDER_MAX_ROWS) row_order_kernel(const int* __restrict__ seq_lens, const int* __restrict__ slot, int n_kv, int B,
+                                                                   int2* __restrict__ order) {
   __shared__ int len_s[ORDER_MAX_ROWS];
+  __shared__ int mx_s, mn_s;
   const int t = threadIdx.x;
-  if (t < B) len_s[t] = seq_lens[t];
+  asm volatile("griddepcontrol.wait;" ::: "memory");                   // resident early behind the previous kernel, as the attention kernels are
+  asm volatile("griddepcontrol.launch_dependents;" ::);
+  if (t == 0) { mx_s = 0; mn_s = 0x7fffffff; }
+  // paged layout: seq_lens[row]; slot layout: the tokens of the row's first head, seq_lens[slot[row] * n_kv] (0 for a padding row)
+  if (t < B) len_s[t] = slot ? (slot[t] < 0 ? 0 : seq_lens[(long)slot[t] * n_kv]) : seq_lens[t];
   __syncthreads();
-  if (t >= B) return;
-  const int mine = len_s[t];
-  int before = 0;
-  for (int i = 0; i < B; i++) before += (len_s[i] > mine) || (len_s[i] == mine && i < t);
-  order[before] = make_int2(t, mine);
+  if (t < B) {
+    const int mine = len_s[t];
+    atomicMax(&mx_s, mine);
+    if (mine > 0) atomicMin(&mn_s, mine);
+    int before = 0;
+    for (int i = 0; i < B; i++) before += (len_s[i] > mine) || (len_s[i] == mine && i < t);
+    order[before] = make_int2(t, mine);
+  }
+  __syncthreads();
+  if (t == 0) order[B] = make_int2(mn_s < mx_s - (mx_s >> 3) ? 1 : 0, 0);
 }
 
 static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
@@ -1345,7 +1365,7 @@ constexpr size_t WS_COUNTERS_OFF = 256, WS_MIN_HEADER = 64 << 10;
 static size_t ws_header_bytes(int B, int n_q) { return std::max(WS_MIN_HEADER, WS_COUNTERS_OFF + align256(4 * (size_t)B * n_q)); }
 static size_t ws_bytes_needed(int B, int n_q, int nsplit) {
   const size_t n = (size_t)B * n_q * nsplit;
-  return ws_header_bytes(B, n_q) + align256(4 * n) * 2 + align256(4 * n * D) + align256(sizeof(int2) * (size_t)B);     // header | pm | pl | pa | row order
+  return ws_header_bytes(B, n_q) + align256(4 * n) * 2 + align256(4 * n * D) + align256(sizeof(int2) * ((size_t)B + 1));     // header | pm | pl | pa | row order
 }
 static int carve_workspace(void* ws, size_t ws_bytes, int B, int n_q, int nsplit, AttnParams& p) {
   const size_t n = (size_t)B * n_q * nsplit;
@@ -1362,6 +1382,15 @@ static int carve_workspace(void* ws, size_t ws_bytes, int B, int n_q, int nsplit
 
 // Programmatic dependent launch of the attention and merge kernels (see gaac_set_launch_overlap); on unless switched off.
 static int g_launch_overlap = 1;
+
+static void launch_row_order(const int* seq_lens, const int* slot, int n_kv, int B, int2* order, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1); cfg.blockDim = dim3(ORDER_MAX_ROWS); cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[0].val.programmaticStreamSerializationAllowed = g_launch_overlap;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, row_order_kernel, seq_lens, slot, n_kv, B, order) != cudaSuccess) cudaGetLastError();     // the attention launch that follows reports
+}
 
 template <bool PAGED, bool DUMP>
 static int launch_attn(const AttnParams& p, cudaStream_t st) {
@@ -1452,7 +1481,7 @@ static int paged_attn(const gaac_paged* st, const int32_t* bt, int64_t bt_stride
   // ragged batches: CTAs are handed out longest row first (one small launch sorts the rows; its output is read by the attention
   // kernel after its dependency wait)
   if (B > 1 && B <= ORDER_MAX_ROWS && (int64_t)B * st->n_kv * nsplit > sm_count_of_current_device()) {
-    row_order_kernel<<<1, ORDER_MAX_ROWS, 0, (cudaStream_t)stream>>>(seq_lens, B, p.order_buf);
+    launch_row_order(seq_lens, nullptr, 0, B, p.order_buf, (cudaStream_t)stream);
     p.row_order = p.order_buf;
   }
   return launch_attn<true, false>(p, (cudaStream_t)stream);

@@ -297,7 +297,8 @@ int gaac_paged_decode_blocks(const gaac_paged* st, const int32_t* pairs, int P, 
 
 /* Fused decode attention over the paged buffer: q [B, n_q, 128] bf16, out [B, n_q*128] bf16, bt [B, bt_stride] block
  * table, seq_lens [B] tokens per sequence (including the filling block).  Replaces gaac_vpaged_launch = gaac_vpaged<G> +
- * gaac_combine2<128> (gaac/vllm/paged_kernel.py:42-276). */
+ * gaac_combine2<128> (gaac/vllm/paged_kernel.py:42-276).  When 1 < B <= 1024 and B*n_kv*nsplit exceeds the SM count a one-CTA
+ * launch in front of the attention kernel sorts the rows by length, and the CTAs are handed out longest row first. */
 int gaac_paged_decode_attn(const gaac_paged* st, const int32_t* bt, int64_t bt_stride, const int32_t* seq_lens, const void* q_bf16,
                            int B, int n_q, float scale, int nsplit, void* workspace, size_t workspace_bytes,
                            void* out_bf16, float* out_f32, void* stream);

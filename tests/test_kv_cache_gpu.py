@@ -252,3 +252,28 @@ def test_unchecked_prefills_are_settled_in_one_go():
     dk, dv = cache.decompress(0)
     assert np.array_equal(bits(dk), hist[0][0]) and np.array_equal(bits(dv), hist[0][1])
     assert int(cache.append_errors) == 0
+
+
+def test_ragged_slots_in_a_grid_larger_than_the_gpu():
+    """Seven batch rows over slots of very different lengths (one padding row, two equal ones) with 8 splits: 7 x 4 x 8 = 224
+    CTAs, more than the GPU holds at once, so late CTAs start while early ones are merging.  A second call with another row-to-slot
+    map reuses the workspace."""
+    from gaac_b200 import CompressedKVCache
+    import torch
+    cache = CompressedKVCache(n_slots=6, n_kv=N_KV, capacity=1024, bases=_bases(13))
+    lens = {0: 37, 1: 500, 2: 16, 3: 1000, 4: 500, 5: 5}
+    hist = {}
+    for s, L in lens.items():
+        k, v = _tok(O.kv_like(N_KV, L, 120 + s)), _tok(O.kv_like(N_KV, L, 140 + s))
+        cache.prefill(s, to_bf16_cuda(k), to_bf16_cuda(v), check=False); hist[s] = (k, v)
+    rng = np.random.default_rng(4)
+    for slots_l in ([5, 3, -1, 0, 1, 4, 2], [3, 3, 1, -1, 5, 0, 4]):
+        slots = torch.tensor(slots_l, dtype=torch.int32, device="cuda")
+        q16 = O.f32_to_bf16((rng.standard_normal((7, N_KV * G, 128)) * 0.1).astype(np.float32))
+        o32 = torch.empty(7, N_KV * G, 128, dtype=torch.float32, device="cuda")
+        out = cache.attention(to_bf16_cuda(q16), slots, SCALE, nsplit=8, out_f32=o32)
+        for b, s in enumerate(slots_l):
+            if s < 0:
+                assert out[b].abs().max().item() == 0
+                continue
+            assert_attention_close(o32[b].cpu().numpy(), q16[b], hist[s][0], hist[s][1], SCALE, (b, s))
