@@ -33,7 +33,7 @@ LAYERS_PER_STEP = 32               # a decode step of a 32-layer model
 LAYERS_PER_GRAPH = 16              # layers captured in one CUDA graph; a step replays two of them
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_attn_kernel launch at the 65536-token workload, from the ncu capture
 # summarised in profiles/ (scaled by tokens for other context lengths: the traffic is proportional to the tiles read)
-NCU_TRAFFIC_BYTES_64K = 197.9e6
+NCU_TRAFFIC_BYTES_64K = 197.1e6
 
 
 def workload_text(ctx: int) -> str:
